@@ -1,0 +1,303 @@
+// Compute entry points (include/htp_ops_b200.h): argument checks in the reference's order
+// (src/dsp/ops/mat_mul.c:878-892), kernel selection, launch.
+#include "htp_ops_b200.h"
+
+#include <atomic>
+#include <cstring>
+#include <map>
+#include <mutex>
+
+#include "aux_kernels.h"
+#include "device_ctx.h"
+#include "gemv_mma.h"
+
+namespace htp {
+
+int g_opt_pdl           = 1;
+int g_opt_force_generic = 0;
+
+namespace {
+std::mutex                                            g_mu;
+std::map<int, DeviceCtx>                              g_devices;
+std::map<std::pair<int, cudaStream_t>, StreamScratch> g_scratch;
+std::atomic<uint64_t>                                 g_launches{ 0 };
+}  // namespace
+
+void count_launch(int n) {
+  g_launches.fetch_add((uint64_t) n, std::memory_order_relaxed);
+}
+
+DeviceCtx *current_device_ctx() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto                        it = g_devices.find(dev);
+  if (it != g_devices.end()) {
+    return &it->second;
+  }
+  DeviceCtx c;
+  c.device = dev;
+  if (cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&c.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return &(g_devices[dev] = c);
+}
+
+StreamScratch *stream_scratch(DeviceCtx *ctx, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto                        key = std::make_pair(ctx->device, stream);
+  auto                        it  = g_scratch.find(key);
+  if (it != g_scratch.end()) {
+    return &it->second;
+  }
+  StreamScratch s;
+  const size_t  pbytes = (size_t) kGemvMaxGrid * 2 * 256 * sizeof(float);
+  const size_t  cbytes = (size_t) kGemvMaxGrid * sizeof(unsigned);
+  uint8_t      *base   = nullptr;
+  if (cudaMalloc(&base, pbytes + cbytes + 256) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (cudaMemset(base, 0, pbytes + cbytes + 256) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(base);
+    return nullptr;
+  }
+  s.partials = reinterpret_cast<float *>(base);
+  s.counters = reinterpret_cast<unsigned *>(base + pbytes);
+  s.err      = reinterpret_cast<int *>(base + pbytes + cbytes);
+  return &(g_scratch[key] = s);
+}
+
+void release_all_scratch() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  int                         cur = -1;
+  cudaGetDevice(&cur);
+  for (auto &kv : g_scratch) {
+    cudaSetDevice(kv.first.first);
+    cudaFree(kv.second.partials);
+  }
+  g_scratch.clear();
+  if (cur >= 0) {
+    cudaSetDevice(cur);
+  }
+}
+
+namespace {
+
+inline bool aligned128(const void *p) {
+  return (reinterpret_cast<uintptr_t>(p) & 127u) == 0;
+}
+
+inline int wt_index(int weight_type) {
+  return weight_type == 2 ? 0 : (weight_type == 8 ? 1 : -1);
+}
+
+// Decode path: M <= 8 rows of activations per launch, K split into launches whose activation
+// fragments fit in shared memory next to at least three pipeline stages.
+int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int m, int k, int n, int wt, bool a16,
+             cudaStream_t stream, bool pdl) {
+  StreamScratch *sc = stream_scratch(ctx, stream);
+  if (!sc) {
+    return -2;
+  }
+  const int bb      = wt == 0 ? 18 : 34;
+  const int kb_all  = k / 32;
+  const int periods = kb_all / 8;
+  const int stage   = kGemvTileRows * gemv_row_pitch(wt);
+  const int budget  = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
+  const int asz     = a16 ? 2 : 4;
+
+  for (int m0 = 0; m0 < m; m0 += 8) {
+    const int mm   = (m - m0) < 8 ? (m - m0) : 8;
+    const int mpad = mm <= 1 ? 1 : (mm <= 2 ? 2 : (mm <= 4 ? 4 : 8));
+    int       nchunks = 1, chunk_periods = periods, nst = 0;
+    for (;; ++nchunks) {
+      chunk_periods     = (periods + nchunks - 1) / nchunks;
+      const size_t frag = gemv_frag_bytes(wt, a16, mpad, chunk_periods * 8);
+      const long   room = (long) budget - kGemvSmemHeader - (long) frag;
+      nst               = room > 0 ? (int) (room / stage) : 0;
+      if (nst > kGemvMaxStages) {
+        nst = kGemvMaxStages;
+      }
+      if (nst >= 4 || (nst >= 2 && chunk_periods == 1)) {
+        break;
+      }
+      if (chunk_periods == 1) {
+        return -2;  // cannot happen on a device with >= 96 KiB of shared memory
+      }
+    }
+    for (int c = 0; c * chunk_periods < periods; ++c) {
+      const int p0  = c * chunk_periods;
+      const int pn  = (periods - p0) < chunk_periods ? (periods - p0) : chunk_periods;
+      GemvArgs  a   = {};
+      a.y           = dst + (size_t) m0 * n;
+      a.x           = static_cast<const uint8_t *>(act) + (size_t) m0 * k * asz;
+      a.w           = w;
+      a.w_row_bytes = (long long) kb_all * bb;
+      a.w_k_off_bytes = (long long) p0 * 8 * bb;
+      a.x_k_off       = p0 * 256;
+      a.x_stride      = k;
+      a.M             = mm;
+      a.N             = n;
+      a.kblocks       = pn * 8;
+      a.accumulate    = c > 0;
+      a.stages_per_tile = (a.kblocks + kGemvStageBlocks - 1) / kGemvStageBlocks;
+      a.total_items     = (long long) (n / kGemvTileRows) * a.stages_per_tile;
+      const size_t frag = gemv_frag_bytes(wt, a16, mpad, a.kblocks);
+      // ring depth: never more stages than the busiest CTA has items
+      long long grid = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
+      if (grid > a.total_items) {
+        grid = a.total_items;
+      }
+      const long long per_cta = (a.total_items + grid - 1) / grid;
+      a.n_stages              = nst;
+      if (a.n_stages > per_cta) {
+        a.n_stages = (int) (per_cta < 2 ? 2 : per_cta);
+      }
+      a.partials = sc->partials;
+      a.counters = sc->counters;
+      a.err      = sc->err;
+      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) a.n_stages * stage;
+      if (gemv_mma_launch(a, wt, a16, mpad, (int) grid, smem, stream, pdl) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
+      }
+      count_launch();
+    }
+  }
+  return 0;
+}
+
+}  // namespace
+}  // namespace htp
+
+using namespace htp;
+
+namespace htp {
+
+int mul_mat_checked(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                    int act_type, cudaStream_t st, bool allow_pdl) {
+  if (!dst || !activation || !weight || m <= 0 || n <= 0 || k <= 0) {
+    return -1;
+  }
+  if (k % 32 != 0 || n % 32 != 0) {
+    return -1;
+  }
+  if (!aligned128(dst) || !aligned128(activation) || !aligned128(weight)) {
+    return -1;
+  }
+  const int wt = wt_index(weight_type);
+  if (wt < 0 || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
+    return -1;
+  }
+  DeviceCtx *ctx = current_device_ctx();
+  if (!ctx) {
+    return -2;
+  }
+  const bool a16 = act_type == HTP_B200_ACT_F16;
+  if (g_opt_force_generic || k % 256 != 0) {
+    if (mul_mat_generic_launch(static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n,
+                               wt, a16, st) != cudaSuccess) {
+      return -2;
+    }
+    count_launch();
+    return 0;
+  }
+  return run_gemv(ctx, static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n, wt, a16,
+                  st, allow_pdl && g_opt_pdl != 0);
+}
+
+}  // namespace htp
+
+extern "C" {
+
+int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                     int act_type, void *stream) {
+  return mul_mat_checked(dst, activation, weight, m, k, n, weight_type, act_type, static_cast<cudaStream_t>(stream),
+                         true);
+}
+
+int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream) {
+  const int wt = wt_index(weight_type);
+  if (!weight || !s || !t || n_blocks < 0 || wt < 0 || (reinterpret_cast<uintptr_t>(weight) & 1u)) {
+    return -1;
+  }
+  if (!current_device_ctx()) {
+    return -2;
+  }
+  if (block_sums_launch(static_cast<const uint8_t *>(weight), s, t, n_blocks, wt, static_cast<cudaStream_t>(stream)) !=
+      cudaSuccess) {
+    return -2;
+  }
+  if (n_blocks > 0) {
+    count_launch();
+  }
+  return 0;
+}
+
+size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n) {
+  const int wt = wt_index(weight_type);
+  if (wt < 0 || k <= 0 || n <= 0 || k % 32 != 0) {
+    return 0;
+  }
+  return (size_t) n * (size_t) (k / 32) * (wt == 0 ? 18u : 34u);
+}
+
+int htp_b200_stream_status(void *stream) {
+  DeviceCtx *ctx = current_device_ctx();
+  if (!ctx) {
+    return -2;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaStreamSynchronize(st) != cudaSuccess) {
+    return -2;
+  }
+  StreamScratch *sc = stream_scratch(ctx, st);
+  if (!sc) {
+    return -2;
+  }
+  int code = 0;
+  if (cudaMemcpy(&code, sc->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    return -2;
+  }
+  if (code != 0) {
+    cudaMemset(sc->err, 0, sizeof(int));
+    // a kernel that gave up may have left arrival counters behind
+    cudaMemset(sc->counters, 0, (size_t) kGemvMaxGrid * sizeof(unsigned));
+  }
+  return code;
+}
+
+int htp_b200_set_option(const char *name, int value) {
+  if (!name) {
+    return -1;
+  }
+  int *slot = nullptr;
+  if (!strcmp(name, "pdl")) {
+    slot = &g_opt_pdl;
+  } else if (!strcmp(name, "force_generic")) {
+    slot = &g_opt_force_generic;
+  }
+  if (!slot) {
+    return -1;
+  }
+  const int old = *slot;
+  *slot         = value;
+  return old;
+}
+
+uint64_t htp_b200_launch_count(void) {
+  return g_launches.load(std::memory_order_relaxed);
+}
+
+const char *htp_b200_version(void) {
+  return "htp-ops-lib_b200 0.1 (sm_100a)";
+}
+
+}  // extern "C"

@@ -1,0 +1,40 @@
+// Per-device state shared by the compute entry points: SM count and, per stream, the small
+// scratch area the mat-vec kernel finishes boundary tiles through.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace htp {
+
+struct StreamScratch {
+  float    *partials = nullptr;  // [kGemvMaxGrid][2][256]
+  unsigned *counters = nullptr;  // [kGemvMaxGrid], zero between launches
+  int      *err      = nullptr;  // first kernel error code
+};
+
+struct DeviceCtx {
+  int device   = -1;
+  int sm_count = 0;
+  int max_smem = 0;
+};
+
+// Context of the current device (created on first use).  nullptr when no device is usable.
+DeviceCtx *current_device_ctx();
+
+// Scratch bound to (current device, stream); allocated on first use.  nullptr on failure.
+StreamScratch *stream_scratch(DeviceCtx *ctx, cudaStream_t stream);
+
+// Frees every scratch area (used at session close).
+void release_all_scratch();
+
+// The checked matmul behind htp_b200_mul_mat.  allow_pdl = false forces plain stream ordering for
+// this launch (needed when the weight buffer may still be written by earlier work on the stream).
+int mul_mat_checked(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                    int act_type, cudaStream_t stream, bool allow_pdl);
+
+extern int      g_opt_pdl;
+extern int      g_opt_force_generic;
+void            count_launch(int n = 1);
+
+}  // namespace htp

@@ -1,0 +1,492 @@
+// K1 - decode-side quantised mat-vec (M <= 8 tokens): y[M][N] = x[M][K] . W[N][K]^T.
+//
+// Replaces the reference's DMA -> HVX dequantise -> HMX tile -> store schedule
+// (src/dsp/ops/mat_mul.c:928-1005) for small M.  The kernel is HBM-bound by design:
+//
+//   * One persistent CTA per SM.  The work is the list of (32-row tile, 1024-weight K stage)
+//     items in tile-major order; CTA c owns the contiguous item range [T c / G, T (c+1) / G), so
+//     every SM streams the same number of bytes whatever N is.  A tile cut by a range boundary is
+//     finished through a small scratch area: each part is written in a fixed slot, the last CTA to
+//     arrive adds the parts in ascending order (bit-reproducible, no floating-point atomics).
+//   * A producer warp streams the raw 18-/34-byte blocks with one bulk async copy per weight row
+//     and stage into a shared-memory ring (mbarrier full/empty pairs, L2 evict-first).  Rows are
+//     padded to an odd multiple of 16 bytes so the fragment reads below are bank-conflict-free.
+//   * Eight consumer warps split a stage along K.  Quants stay INTEGERS: a lane turns one 32-bit
+//     word of nibbles/bytes into fp16 pairs (unpack.cuh) that are the A fragment of a warp MMA
+//     (m16n8k16, fp32 accumulate) whose B fragment holds the activations.  The block scale is
+//     applied to the 32-weight partial sum in fp32, i.e. sum_k (q_k x_k) * d - the same value as
+//     dequantise-then-dot, without rounding q*d to fp16.
+//   * fp32 activations are split as x = hi + lo with hi = fp16(x), lo = fp16(x - hi), so the
+//     product is exact to ~2^-22; hi and lo occupy separate MMA columns (M <= 4) or two chained
+//     MMAs (M <= 8).  Tokens whose |x| reaches 2^15 are pre-scaled by a power of two.
+//   * The activation fragments for the whole K range live in shared memory, built once per CTA.
+//   * Programmatic dependent launch: the weight prefetch starts before the previous kernel in
+//     the stream has finished; activations are read, and outputs written, only after it has.
+//
+// Every mbarrier wait is bounded; a wait that runs out stores an error code and the CTA leaves.
+#include "gemv_mma.h"
+
+#include <cuda_runtime.h>
+
+#include "ptx.cuh"
+#include "unpack.cuh"
+
+namespace htp {
+
+namespace {
+
+constexpr int kConsumerWarps   = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads         = kConsumerThreads + 32;
+
+template <int WT, bool A16, int MPAD>
+struct Cfg {
+  static constexpr int  BB       = BlockTraits<WT>::kBytes;
+  static constexpr int  CH       = (!A16 && MPAD == 8) ? 2 : 1;           // chained MMAs per k-step
+  static constexpr int  NC       = A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD);  // MMA columns in use
+  static constexpr bool SPLITCOL = (!A16 && MPAD < 8);                    // column = 2 m + piece
+  static constexpr int  PSTRIDE  = gemv_row_pitch(WT);
+  static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
+  static constexpr int  FRAG_U2  = 2 * CH * NC * 4;  // uint2 entries per block
+};
+
+struct Smem {
+  uint64_t full[kGemvMaxStages];
+  uint64_t empty[kGemvMaxStages];
+  float    tok_scale[8];
+  float    tok_inv[8];
+  int      tok_amax_bits[8];
+  int      last_flag;
+  int      abort_flag;
+  int      pad[6];
+  float    red[kConsumerWarps][256];
+};
+static_assert(sizeof(Smem) % 128 == 0, "keep the regions after the header 128-byte aligned");
+static_assert(sizeof(Smem) == kGemvSmemHeader, "host-side size computation must match");
+
+__device__ __forceinline__ void record_error(const GemvArgs &p, int code) {
+  atomicCAS(p.err, 0, code);
+}
+
+__device__ __forceinline__ uint32_t lds32(const uint8_t *p) {
+  return *reinterpret_cast<const uint32_t *>(p);
+}
+__device__ __forceinline__ float lds_scale(const uint8_t *p) {
+  return __half2float(*reinterpret_cast<const __half *>(p));
+}
+
+// owner CTA of item i when T items are dealt to G CTAs as [T c / G, T (c+1) / G)
+__device__ __forceinline__ long long item_owner(long long i, long long T, long long G) {
+  return ((i + 1) * G - 1) / T;
+}
+
+// ------------------------------------------------------------------ activation fragments
+
+template <int WT, bool A16, int MPAD>
+__device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
+  using C = Cfg<WT, A16, MPAD>;
+  if constexpr (!A16) {
+    // per-token power-of-two pre-scale so that fp16(x) cannot overflow
+    if (tid < 8) {
+      sm->tok_amax_bits[tid] = 0;
+    }
+    named_bar_sync(1, kConsumerThreads);
+    const float *x    = static_cast<const float *>(p.x);
+    const int    klen = p.kblocks * 32;
+    for (int m = 0; m < p.M; ++m) {
+      float a = 0.0f;
+      for (int k = tid; k < klen; k += kConsumerThreads) {
+        a = fmaxf(a, fabsf(x[(long long) m * p.x_stride + p.x_k_off + k]));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+      }
+      if ((tid & 31) == 0) {
+        atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
+      }
+    }
+    named_bar_sync(1, kConsumerThreads);
+    if (tid < 8) {
+      const int bits = sm->tok_amax_bits[tid];
+      const int e    = ((bits >> 23) & 0xff) - 127;  // floor(log2(amax))
+      int       sh   = e - 14;
+      sh             = sh < 0 ? 0 : (sh > 100 ? 100 : sh);
+      sm->tok_scale[tid] = __int_as_float((127 - sh) << 23);
+      sm->tok_inv[tid]   = __int_as_float((127 + sh) << 23);
+    }
+    named_bar_sync(1, kConsumerThreads);
+  }
+
+  const int n_units = p.kblocks * 8;  // (block, mma j, t)
+  for (int u = tid; u < n_units; u += kConsumerThreads) {
+    const int b = u >> 3, j = (u >> 2) & 1, t = u & 3;
+    // the four activations this lane position multiplies: block elements
+    // mma_frag_elem(j, t, hi, s) for (hi, s) in {0,1}^2; they always lie in one aligned group of 4
+    const int e00 = mma_frag_elem<WT>(j, t, 0, 0);
+    const int k0  = b * 32 + (e00 & ~3);
+    const int i00 = e00 & 3;
+    const int i01 = mma_frag_elem<WT>(j, t, 0, 1) & 3;
+    const int i10 = mma_frag_elem<WT>(j, t, 1, 0) & 3;
+    const int i11 = mma_frag_elem<WT>(j, t, 1, 1) & 3;
+    uint2    *dst = frags + (size_t) (b * 2 + j) * C::CH * C::NC * 4;
+    for (int m = 0; m < MPAD; ++m) {
+      if constexpr (A16) {
+        __half v[4] = { __half(0.f), __half(0.f), __half(0.f), __half(0.f) };
+        if (m < p.M) {
+          const __half *x = static_cast<const __half *>(p.x) + (long long) m * p.x_stride + p.x_k_off + k0;
+          const uint2   r = *reinterpret_cast<const uint2 *>(x);
+          *reinterpret_cast<uint2 *>(v) = r;
+        }
+        uint2 f;
+        f.x = h2_as_u32(__halves2half2(v[i00], v[i01]));
+        f.y = h2_as_u32(__halves2half2(v[i10], v[i11]));
+        dst[m * 4 + t] = f;
+      } else {
+        float v[4] = { 0.f, 0.f, 0.f, 0.f };
+        if (m < p.M) {
+          const float *x = static_cast<const float *>(p.x) + (long long) m * p.x_stride + p.x_k_off + k0;
+          const float4 r = *reinterpret_cast<const float4 *>(x);
+          const float  s = sm->tok_scale[m];
+          v[0] = r.x * s, v[1] = r.y * s, v[2] = r.z * s, v[3] = r.w * s;
+        }
+        __half hi[4], lo[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          hi[i] = __float2half_rn(v[i]);
+          lo[i] = __float2half_rn(v[i] - __half2float(hi[i]));
+        }
+        uint2 fh, fl;
+        fh.x = h2_as_u32(__halves2half2(hi[i00], hi[i01]));
+        fh.y = h2_as_u32(__halves2half2(hi[i10], hi[i11]));
+        fl.x = h2_as_u32(__halves2half2(lo[i00], lo[i01]));
+        fl.y = h2_as_u32(__halves2half2(lo[i10], lo[i11]));
+        if constexpr (C::SPLITCOL) {
+          dst[(2 * m) * 4 + t]     = fh;
+          dst[(2 * m + 1) * 4 + t] = fl;
+        } else {
+          dst[m * 4 + t]             = fh;  // chain 0
+          dst[C::NC * 4 + m * 4 + t] = fl;  // chain 1
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ one block x 16 rows
+
+template <int WT, bool A16, int MPAD, bool EVEN>
+__device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf)[2][2], int t, float (&acc)[4]) {
+  using C = Cfg<WT, A16, MPAD>;
+  // ra: this lane's row g of the 16-row group, at the block's first byte; row g+8 is 8 pitches on
+  const uint8_t *rb = ra + 8 * C::PSTRIDE;
+  uint32_t       a0[4], a1[4];  // A fragments of MMA 0 and 1: {row g lo, row g+8 lo, row g hi, row g+8 hi}
+  if constexpr (WT == kQ4) {
+    uint32_t qa, qb;
+    if constexpr (EVEN) {  // quants start 2 bytes past a word boundary
+      qa = __byte_perm(lds32(ra + 4 * t), lds32(ra + 4 * t + 4), 0x5432);
+      qb = __byte_perm(lds32(rb + 4 * t), lds32(rb + 4 * t + 4), 0x5432);
+    } else {  // block starts 2 bytes past a word boundary, quants are word aligned
+      qa = lds32(ra + 2 + 4 * t);
+      qb = lds32(rb + 2 + 4 * t);
+    }
+    uint32_t ha[4], hb[4];
+    q4_0_unpack_word(qa, ha);
+    q4_0_unpack_word(qb, hb);
+    a0[0] = ha[0], a0[1] = hb[0], a0[2] = ha[1], a0[3] = hb[1];
+    a1[0] = ha[2], a1[1] = hb[2], a1[2] = ha[3], a1[3] = hb[3];
+  } else {
+    uint32_t qa0, qa1, qb0, qb1;
+    if constexpr (EVEN) {
+      qa0 = __byte_perm(lds32(ra + 4 * t), lds32(ra + 4 * t + 4), 0x5432);
+      qa1 = __byte_perm(lds32(ra + 4 * t + 16), lds32(ra + 4 * t + 20), 0x5432);
+      qb0 = __byte_perm(lds32(rb + 4 * t), lds32(rb + 4 * t + 4), 0x5432);
+      qb1 = __byte_perm(lds32(rb + 4 * t + 16), lds32(rb + 4 * t + 20), 0x5432);
+    } else {
+      qa0 = lds32(ra + 2 + 4 * t);
+      qa1 = lds32(ra + 2 + 4 * t + 16);
+      qb0 = lds32(rb + 2 + 4 * t);
+      qb1 = lds32(rb + 2 + 4 * t + 16);
+    }
+    uint32_t ha0[2], ha1[2], hb0[2], hb1[2];
+    q8_0_unpack_word(qa0, ha0);
+    q8_0_unpack_word(qa1, ha1);
+    q8_0_unpack_word(qb0, hb0);
+    q8_0_unpack_word(qb1, hb1);
+    a0[0] = ha0[0], a0[1] = hb0[0], a0[2] = ha0[1], a0[3] = hb0[1];
+    a1[0] = ha1[0], a1[1] = hb1[0], a1[2] = ha1[1], a1[3] = hb1[1];
+  }
+  const float da = lds_scale(ra);
+  const float db = lds_scale(rb);
+
+  float c[4] = { 0.f, 0.f, 0.f, 0.f };
+#pragma unroll
+  for (int ch = 0; ch < C::CH; ++ch) {
+    mma_16816(c, a0, bf[0][ch].x, bf[0][ch].y);
+    mma_16816(c, a1, bf[1][ch].x, bf[1][ch].y);
+  }
+  acc[0] = fmaf(da, c[0], acc[0]);
+  acc[1] = fmaf(da, c[1], acc[1]);
+  acc[2] = fmaf(db, c[2], acc[2]);
+  acc[3] = fmaf(db, c[3], acc[3]);
+}
+
+// ------------------------------------------------------------------ tile completion
+
+template <int WT, bool A16, int MPAD>
+__device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long long it0, long long it1, int S,
+                           float (&acc)[2][4], int tid) {
+  using C = Cfg<WT, A16, MPAD>;
+  const int warp = tid >> 5, lane = tid & 31;
+#pragma unroll
+  for (int rg = 0; rg < 2; ++rg) {
+    *reinterpret_cast<float4 *>(&sm->red[warp][rg * 128 + lane * 4]) =
+      make_float4(acc[rg][0], acc[rg][1], acc[rg][2], acc[rg][3]);
+  }
+  named_bar_sync(1, kConsumerThreads);
+  float v = 0.f;
+#pragma unroll
+  for (int w = 0; w < kConsumerWarps; ++w) {
+    v += sm->red[w][tid];
+  }
+  named_bar_sync(1, kConsumerThreads);  // red may be rewritten by the next flush
+
+  const long long first = tile * S, last = first + S - 1;
+  bool            write_out = true;
+  if (first < it0 || last >= it1) {
+    // this CTA holds only part of the tile
+    const long long T = p.total_items, G = gridDim.x;
+    const int       c_first = (int) item_owner(first, T, G);
+    const int       c_last  = (int) item_owner(last, T, G);
+    const int       slot    = (first < it0) ? 0 : 1;
+    float          *mine    = p.partials + ((size_t) blockIdx.x * 2 + slot) * 256;
+    __stcg(mine + tid, v);
+    __threadfence();
+    named_bar_sync(1, kConsumerThreads);
+    if (tid == 0) {
+      const unsigned old  = atomicAdd(p.counters + c_first, 1u);
+      const int      done = (old == (unsigned) (c_last - c_first));
+      if (done) {
+        p.counters[c_first] = 0;  // ready for the next launch
+      }
+      sm->last_flag = done;
+    }
+    named_bar_sync(1, kConsumerThreads);
+    write_out = sm->last_flag != 0;
+    if (write_out) {
+      __threadfence();
+      v = 0.f;
+      for (int c = c_first; c <= c_last; ++c) {
+        const int s = (c == c_first) ? 1 : 0;
+        v += __ldcg(p.partials + ((size_t) c * 2 + s) * 256 + tid);
+      }
+    }
+    named_bar_sync(1, kConsumerThreads);  // last_flag may be rewritten by the next flush
+  }
+  if constexpr (C::SPLITCOL) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);  // hi-piece column + lo-piece column
+  }
+  if (!write_out) {
+    return;
+  }
+  const int i = tid & 3, t = (tid >> 2) & 3, g = (tid >> 4) & 7, rg = tid >> 7;
+  const int row = rg * 16 + g + 8 * (i >> 1);
+  int       m;
+  if constexpr (C::SPLITCOL) {
+    if (i & 1) {
+      return;
+    }
+    m = t;
+  } else {
+    m = 2 * t + (i & 1);
+  }
+  if (m >= p.M) {
+    return;
+  }
+  if constexpr (!A16) {
+    v *= sm->tok_inv[m];
+  }
+  float *dst = p.y + (long long) m * p.N + tile * kGemvTileRows + row;
+  *dst       = p.accumulate ? (*dst + v) : v;
+}
+
+// ------------------------------------------------------------------ the kernel
+
+template <int WT, bool A16, int MPAD>
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p) {
+  using C = Cfg<WT, A16, MPAD>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Smem    *sm     = reinterpret_cast<Smem *>(smem_raw);
+  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + sizeof(Smem));
+  uint8_t *stages = smem_raw + sizeof(Smem) + (((size_t) p.kblocks * C::FRAG_U2 * 8 + 127) & ~(size_t) 127);
+
+  const int       warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int       S   = p.stages_per_tile;
+  const int       NST = p.n_stages;
+  const long long T = p.total_items, G = gridDim.x;
+  const long long it0 = T * blockIdx.x / G, it1 = T * (blockIdx.x + 1) / G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], kConsumerWarps);
+    }
+    sm->abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer: weights only, may run ahead of the previous kernel's completion
+    const uint64_t pol = l2_policy_evict_first();
+    int            li  = 0;
+    for (long long it = it0; it < it1; ++it, ++li) {
+      const int slot = li % NST, ph = (li / NST) & 1;
+      if (!mbar_wait(&sm->empty[slot], ph ^ 1)) {
+        record_error(p, kGemvErrProducerWait);
+        break;
+      }
+      const long long tile  = it / S;
+      const int       st    = (int) (it - tile * S);
+      const int       nblk  = min(kGemvStageBlocks, p.kblocks - st * kGemvStageBlocks);
+      const uint32_t  bytes = (uint32_t) nblk * C::BB;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(&sm->full[slot], bytes * kGemvTileRows);
+      }
+      __syncwarp();
+      const uint8_t *src = p.w + (tile * kGemvTileRows + lane) * p.w_row_bytes + p.w_k_off_bytes +
+                           (long long) st * kGemvStageBlocks * C::BB;
+      bulk_g2s(stages + (size_t) slot * C::STAGE + lane * C::PSTRIDE, src, bytes, &sm->full[slot], pol);
+    }
+  } else {
+    // ---------------- consumers
+    const int tid = threadIdx.x;
+    const int g = lane >> 2, t = lane & 3;
+    pdl_wait_prior_grids();  // activations and outputs belong to the stream order
+    build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
+    named_bar_sync(1, kConsumerThreads);
+
+    float acc[2][4];
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[rg][i] = 0.f;
+      }
+    }
+    long long cur_tile = it0 / S;
+    int       li       = 0;
+    bool      ok       = true;
+    for (long long it = it0; it < it1; ++it, ++li) {
+      const long long tile = it / S;
+      const int       st   = (int) (it - tile * S);
+      if (tile != cur_tile) {
+        flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid);
+        cur_tile = tile;
+#pragma unroll
+        for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[rg][i] = 0.f;
+          }
+        }
+      }
+      const int slot = li % NST, ph = (li / NST) & 1;
+      if (!mbar_wait(&sm->full[slot], ph)) {
+        record_error(p, kGemvErrConsumerWait);
+        ok = false;
+        break;
+      }
+      const int nblk = min(kGemvStageBlocks, p.kblocks - st * kGemvStageBlocks);
+      const int bl0  = warp * 4;
+      if (bl0 < nblk) {
+        const uint8_t *sb = stages + (size_t) slot * C::STAGE + g * C::PSTRIDE;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int    bl = bl0 + i;
+          const uint2 *fp = frags + (size_t) ((st * kGemvStageBlocks + bl) * 2) * C::CH * C::NC * 4;
+          uint2        bf[2][2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+              bf[j][ch] = make_uint2(0u, 0u);
+              if (ch < C::CH && g < C::NC) {
+                bf[j][ch] = fp[(j * C::CH + ch) * C::NC * 4 + g * 4 + t];
+              }
+            }
+          }
+#pragma unroll
+          for (int rg = 0; rg < 2; ++rg) {
+            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + bl * C::BB;
+            if ((i & 1) == 0) {
+              block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
+            } else {
+              block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
+            }
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sm->empty[slot]);
+      }
+    }
+    if (ok && it1 > it0) {
+      flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid);
+    }
+  }
+}
+
+template <int WT, bool A16, int MPAD>
+cudaError_t launch_one(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+  auto        kern = gemv_mma_kernel<WT, A16, MPAD>;
+  cudaError_t e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
+  if (e != cudaSuccess) {
+    return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(grid);
+  cfg.blockDim           = dim3(kThreads);
+  cfg.dynamicSmemBytes   = smem;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs                                          = attr;
+  cfg.numAttrs                                       = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args);
+}
+
+template <int WT, bool A16>
+cudaError_t launch_mpad(const GemvArgs &a, int mpad, int grid, size_t smem, cudaStream_t s, bool pdl) {
+  switch (mpad) {
+    case 1: return launch_one<WT, A16, 1>(a, grid, smem, s, pdl);
+    case 2: return launch_one<WT, A16, 2>(a, grid, smem, s, pdl);
+    case 4: return launch_one<WT, A16, 4>(a, grid, smem, s, pdl);
+    default: return launch_one<WT, A16, 8>(a, grid, smem, s, pdl);
+  }
+}
+
+}  // namespace
+
+size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
+  (void) wt;
+  const int ch = (!a16 && mpad == 8) ? 2 : 1;
+  const int nc = a16 ? mpad : (mpad == 8 ? 8 : 2 * mpad);
+  size_t    b  = (size_t) kblocks * 2 * ch * nc * 4 * 8;
+  return (b + 127) & ~(size_t) 127;
+}
+
+cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
+                            cudaStream_t stream, bool pdl) {
+  if (wt == kQ4) {
+    return a16 ? launch_mpad<kQ4, true>(args, mpad, grid, smem, stream, pdl)
+               : launch_mpad<kQ4, false>(args, mpad, grid, smem, stream, pdl);
+  }
+  return a16 ? launch_mpad<kQ8, true>(args, mpad, grid, smem, stream, pdl)
+             : launch_mpad<kQ8, false>(args, mpad, grid, smem, stream, pdl);
+}
+
+}  // namespace htp

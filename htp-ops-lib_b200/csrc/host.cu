@@ -1,0 +1,602 @@
+// Host layer: session, buffer table, operator dispatch and the message-channel servicer.
+//
+// Mirrors, over CUDA, what the reference spreads across src/host/session.c (session),
+// src/dsp/mmap_mgr.cc (handle -> pointer table), src/dsp/op_executor.cc (dispatch) and
+// src/dsp/commu.c (channel servicer and the remote-interface functions).  One process-global
+// session, one stream, one servicer thread; like the reference, the library is not re-entrant.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "device_ctx.h"
+#include "dsp/op_executor.h"
+#include "host/buffers.h"
+#include "host/op_export.h"
+#include "host/session.h"
+#include "htp_ops.h"
+#include "htp_ops_b200.h"
+#include "message.h"
+#include "op_reg.h"
+
+namespace {
+
+enum BufKind { kDeviceBuf = 0, kHostBuf = 1, kWrappedBuf = 2 };
+
+struct Buffer {
+  uint8_t *ptr  = nullptr;
+  size_t   size = 0;
+  int      kind = kDeviceBuf;
+};
+
+struct Range {
+  uintptr_t lo, hi;
+};
+
+struct Session {
+  std::mutex                      mu;  // buffer table and session fields
+  bool                            open    = false;
+  bool                            backend = false;
+  int                             device  = -1;
+  cudaStream_t                    stream  = nullptr;
+  std::unordered_map<int, Buffer> bufs;
+  int                             next_fd = 16;
+  // regions written by operators enqueued since the stream was last waited for; a weight buffer
+  // that overlaps one of them must not be prefetched ahead of stream order
+  std::vector<Range> pending_out;
+  // message channel
+  std::thread       servicer;
+  std::atomic<bool> stop{ false };
+  uint8_t          *msg        = nullptr;
+  size_t            max_msg    = 0;
+  int               chan_fd    = -1;
+};
+
+Session g;
+int     dummy_handle_target;
+
+remote_handle64 session_handle() {
+  return (remote_handle64) (uintptr_t) &dummy_handle_target;
+}
+
+bool set_session_device() {
+  return g.open && cudaSetDevice(g.device) == cudaSuccess;
+}
+
+bool lookup(int fd, Buffer *out) {
+  std::lock_guard<std::mutex> lk(g.mu);
+  auto                        it = g.bufs.find(fd);
+  if (it == g.bufs.end()) {
+    return false;
+  }
+  *out = it->second;
+  return true;
+}
+
+int register_buffer(const Buffer &b) {
+  std::lock_guard<std::mutex> lk(g.mu);
+  const int                   fd = g.next_fd++;
+  g.bufs[fd]                     = b;
+  return fd;
+}
+
+// handle + offset + size -> device address; nullptr when the handle is unknown, is a host
+// buffer, or the region does not fit (the reference resolves an unknown fd to NULL and lets the
+// operator's null check fail, op_executor.cc:57-61).
+uint8_t *resolve(const RpcmemBufAddr &a, size_t bytes) {
+  Buffer b;
+  if (!lookup(a.fd, &b) || b.kind == kHostBuf || a.offset < 0) {
+    return nullptr;
+  }
+  const size_t off = (size_t) a.offset;
+  if (off > b.size || bytes > b.size - off) {
+    return nullptr;
+  }
+  return b.ptr + off;
+}
+
+bool overlaps_pending(const uint8_t *p, size_t bytes) {
+  const uintptr_t lo = (uintptr_t) p, hi = lo + bytes;
+  for (const Range &r : g.pending_out) {
+    if (lo < r.hi && r.lo < hi) {
+      return true;
+    }
+  }
+  return false;
+}
+
+// Enqueue one operator on the session stream.  Returns the synchronous part of the result
+// (argument validation); kernel-side errors surface when the stream is waited for.
+int enqueue_op(const OpComputeRequest *req) {
+  if (!g.open || !g.backend) {
+    return -1;
+  }
+  uint32_t op;
+  memcpy(&op, &req->op, sizeof(op));
+  int weight_type, act_type;
+  switch (op) {
+    case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32: weight_type = 2, act_type = HTP_B200_ACT_F32; break;
+    case HTP_OPS_MAT_MUL_PERMUTED_W8D16A32: weight_type = 8, act_type = HTP_B200_ACT_F32; break;
+    case HTP_OPS_MAT_MUL_W4D16A16: weight_type = 2, act_type = HTP_B200_ACT_F16; break;
+    case HTP_OPS_MAT_MUL_W8D16A16: weight_type = 8, act_type = HTP_B200_ACT_F16; break;
+    default: return -1;  // unknown, or not built in this library
+  }
+  MatMulParams p;
+  memcpy(&p, req->payload, sizeof(p));
+  if (p.m <= 0 || p.k <= 0 || p.n <= 0 || p.k % 32 != 0) {
+    return -1;
+  }
+  // sizes as in op_executor.cc:124-126, in 64 bits
+  const size_t out_bytes = (size_t) p.m * (size_t) p.n * sizeof(float);
+  const size_t act_bytes = (size_t) p.m * (size_t) p.k * (act_type == HTP_B200_ACT_F16 ? 2 : 4);
+  const size_t w_bytes   = htp_b200_weight_bytes(weight_type, p.k, p.n);
+  uint8_t     *out = resolve(p.output, out_bytes);
+  uint8_t     *act = resolve(p.activation, act_bytes);
+  uint8_t     *w   = resolve(p.weight, w_bytes);
+  if (!out || !act || !w) {
+    return -1;
+  }
+  const bool pdl_ok = !overlaps_pending(w, w_bytes);
+  const int  rc     = htp::mul_mat_checked(out, act, w, p.m, p.k, p.n, weight_type, act_type, g.stream, pdl_ok);
+  if (rc == 0) {
+    g.pending_out.push_back({ (uintptr_t) out, (uintptr_t) out + out_bytes });
+  }
+  return rc;
+}
+
+int wait_stream() {
+  const int rc = htp_b200_stream_status(g.stream);
+  g.pending_out.clear();
+  return rc;
+}
+
+// ---------------------------------------------------------------- message channel servicer
+
+inline uint64_t load_acquire64(volatile uint64_t *p) {
+  return __atomic_load_n((uint64_t *) p, __ATOMIC_ACQUIRE);
+}
+inline void store_release64(volatile uint64_t *p, uint64_t v) {
+  __atomic_store_n((uint64_t *) p, v, __ATOMIC_RELEASE);
+}
+
+// Checks that the request table of a published message stays inside the buffer.
+bool message_is_sane(const MessageHeader *h, size_t max_msg) {
+  if (h->n_reqs < 0) {
+    return false;
+  }
+  const size_t hdr = sizeof(MessageHeader) + ((size_t) h->n_reqs + 1) * sizeof(int32_t);
+  if (hdr > max_msg) {
+    return false;
+  }
+  int32_t prev = (int32_t) hdr;
+  if (h->n_reqs > 0 && h->req_offsets[0] < prev) {
+    return false;
+  }
+  for (int i = 0; i <= h->n_reqs; ++i) {
+    const int32_t o = h->req_offsets[i];
+    if (o < prev || (size_t) o > max_msg) {
+      return false;
+    }
+    prev = o;
+  }
+  return true;
+}
+
+void servicer_loop() {
+  cudaSetDevice(g.device);
+  MessageHeader *hdr   = reinterpret_cast<MessageHeader *>(g.msg);
+  unsigned       idle  = 0;
+  while (!g.stop.load(std::memory_order_acquire)) {
+    const uint64_t d  = load_acquire64(&hdr->state.d);
+    const uint8_t  v0 = d & 0xff, v1 = (d >> 8) & 0xff;
+    if (v0 == 0 || v1 != 0) {
+      // nothing published, or the last message has not been taken back yet
+      if (++idle < 4096) {
+        __builtin_ia32_pause();
+      } else if (idle < 65536) {
+        std::this_thread::yield();
+      } else {
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+      }
+      continue;
+    }
+    idle = 0;
+    std::vector<int> enqueued;
+    if (message_is_sane(hdr, g.max_msg)) {
+      for (int i = 0; i < hdr->n_reqs; ++i) {
+        RequestHeader *rh    = message_header_get_request_ptr(hdr, i);
+        const size_t   rsize = message_header_get_request_size(hdr, i);
+        if (rsize < sizeof(RequestHeader)) {
+          continue;
+        }
+        switch (rh->type) {
+          case REQUEST_TYPE_OP_COMPUTE: {
+            if (rsize < sizeof(RequestHeader) + sizeof(OpComputeRequest) + sizeof(MatMulParams)) {
+              rh->state = -1;
+              break;
+            }
+            rh->state = enqueue_op(reinterpret_cast<OpComputeRequest *>(rh->data));
+            if (rh->state == 0) {
+              enqueued.push_back(i);
+            }
+          } break;
+          case REQUEST_TYPE_RPCMEM_MAP: {
+            // The reference drops its cached mapping of n_puts handles (commu.c:102-110);
+            // there is no mapping cache here, the handles stay valid until freed.
+            rh->state = 0;
+          } break;
+          default: break;
+        }
+      }
+    }
+    // (a message whose offset table leaves the buffer is not executed: the host sees "done"
+    // with untouched request states)
+    // all requests of a message complete before "done" is published (commu.c:91-126)
+    const int rc = wait_stream();
+    if (rc != 0) {
+      for (int i : enqueued) {
+        message_header_get_request_ptr(hdr, i)->state = rc;
+      }
+    }
+    store_release64(&hdr->state.d, (uint64_t) v0 | (1ull << 8));
+  }
+}
+
+void stop_channel() {
+  if (g.msg == nullptr) {
+    return;
+  }
+  g.stop.store(true, std::memory_order_release);
+  if (g.servicer.joinable()) {
+    g.servicer.join();
+  }
+  g.stop.store(false, std::memory_order_release);
+  g.msg     = nullptr;
+  g.max_msg = 0;
+  g.chan_fd = -1;
+}
+
+int pick_device(int domain_id) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (const char *env = getenv("HTP_OPS_CUDA_DEVICE")) {
+    const int d = atoi(env);
+    return (d >= 0 && d < count) ? d : -1;
+  }
+  return (domain_id >= 0 && domain_id < count) ? domain_id : 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- session
+
+int open_dsp_session(int domain_id, int unsigned_pd_enabled) {
+  (void) unsigned_pd_enabled;
+  if (g.open) {
+    return 0;
+  }
+  const int dev = pick_device(domain_id);
+  if (dev < 0) {
+    fprintf(stderr, "htp-ops-b200: no usable CUDA device (there is no CPU fallback)\n");
+    return -1;
+  }
+  if (cudaSetDevice(dev) != cudaSuccess || cudaFree(0) != cudaSuccess) {
+    cudaGetLastError();
+    fprintf(stderr, "htp-ops-b200: cannot initialise CUDA device %d\n", dev);
+    return -1;
+  }
+  g.device  = dev;
+  g.open    = true;
+  g.backend = false;
+  return 0;
+}
+
+void close_dsp_session(void) {
+  if (!g.open) {
+    return;
+  }
+  stop_channel();
+  cudaSetDevice(g.device);
+  if (g.stream) {
+    cudaStreamSynchronize(g.stream);
+  }
+  {
+    std::lock_guard<std::mutex> lk(g.mu);
+    for (auto &kv : g.bufs) {
+      if (kv.second.kind == kDeviceBuf) {
+        cudaFree(kv.second.ptr);
+      } else if (kv.second.kind == kHostBuf) {
+        cudaFreeHost(kv.second.ptr);
+      }
+    }
+    g.bufs.clear();
+  }
+  g.pending_out.clear();
+  htp::release_all_scratch();
+  if (g.stream) {
+    cudaStreamDestroy(g.stream);
+    g.stream = nullptr;
+  }
+  g.open    = false;
+  g.backend = false;
+  g.device  = -1;
+}
+
+remote_handle64 get_global_handle(void) {
+  return g.open ? session_handle() : (remote_handle64) -1;
+}
+
+void init_htp_backend(void) {
+  if (!set_session_device() || g.backend) {
+    return;
+  }
+  if (cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking) != cudaSuccess) {
+    cudaGetLastError();
+    g.stream = nullptr;
+    return;
+  }
+  htp::DeviceCtx *ctx = htp::current_device_ctx();
+  if (!ctx || !htp::stream_scratch(ctx, g.stream)) {
+    return;
+  }
+  g.backend = true;
+}
+
+int create_htp_message_channel(int fd, unsigned int max_msg_size) {
+  if (!g.open || !g.backend) {
+    return HTP_AEE_EFAILED;
+  }
+  if (g.msg != nullptr) {
+    return HTP_AEE_EALREADY;
+  }
+  Buffer b;
+  if (!lookup(fd, &b) || b.kind != kHostBuf || max_msg_size < sizeof(MessageHeader) + sizeof(int32_t) ||
+      max_msg_size > b.size) {
+    return HTP_AEE_EBADPARM;
+  }
+  memset(b.ptr, 0, max_msg_size);
+  g.msg     = b.ptr;
+  g.max_msg = max_msg_size;
+  g.chan_fd = fd;
+  g.stop.store(false);
+  g.servicer = std::thread(servicer_loop);
+  return 0;
+}
+
+// ---------------------------------------------------------------- remote-interface names
+
+AEEResult htp_ops_open(const char *uri, remote_handle64 *handle) {
+  int dom = 0;
+  if (uri) {
+    const char *e = uri + strlen(uri);
+    while (e > uri && e[-1] >= '0' && e[-1] <= '9') {
+      --e;
+    }
+    if (*e) {
+      dom = atoi(e);
+    }
+  }
+  if (open_dsp_session(dom, 1) != 0) {
+    return HTP_AEE_EFAILED;
+  }
+  if (handle) {
+    *handle = session_handle();
+  }
+  return HTP_AEE_SUCCESS;
+}
+
+AEEResult htp_ops_close(remote_handle64 handle) {
+  (void) handle;
+  close_dsp_session();
+  return HTP_AEE_SUCCESS;
+}
+
+AEEResult htp_ops_init_backend(remote_handle64 handle) {
+  (void) handle;
+  init_htp_backend();
+  return g.backend ? HTP_AEE_SUCCESS : HTP_AEE_EFAILED;
+}
+
+AEEResult htp_ops_create_channel(remote_handle64 handle, int32_t fd, uint32_t size) {
+  (void) handle;
+  return create_htp_message_channel(fd, size);
+}
+
+AEEResult htp_ops_destroy_channel(remote_handle64 handle) {
+  (void) handle;
+  stop_channel();
+  return HTP_AEE_SUCCESS;
+}
+
+AEEResult htp_ops_rms_norm_f32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1, int32_t offset1,
+                               int32_t ne0, int32_t ne1) {
+  (void) handle, (void) fd0, (void) offset0, (void) fd1, (void) offset1, (void) ne0, (void) ne1;
+  return HTP_AEE_EUNSUPPORTED;
+}
+
+AEEResult htp_ops_mat_mul_permuted_w16a32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1,
+                                          int32_t offset1, int32_t fd2, int32_t offset2, int32_t m, int32_t k,
+                                          int32_t n) {
+  (void) handle, (void) fd0, (void) offset0, (void) fd1, (void) offset1, (void) fd2, (void) offset2;
+  (void) m, (void) k, (void) n;
+  return HTP_AEE_EUNSUPPORTED;
+}
+
+AEEResult htp_ops_test_ops(remote_handle64 handle) {
+  (void) handle;
+  return HTP_AEE_SUCCESS;
+}
+
+int htp_ops_rpc_rms_norm_f32(int dst_fd, int dst_offset, int src_fd, int src_offset, int ne0, int ne1) {
+  return htp_ops_rms_norm_f32(get_global_handle(), dst_fd, dst_offset, src_fd, src_offset, ne0, ne1);
+}
+
+int htp_ops_rpc_mat_mul_permuted_w16a32(int output_fd, int output_offset, int activation_fd, int activation_offset,
+                                        int weight_fd, int weight_offset, int m, int k, int n) {
+  return htp_ops_mat_mul_permuted_w16a32(get_global_handle(), output_fd, output_offset, activation_fd,
+                                         activation_offset, weight_fd, weight_offset, m, k, n);
+}
+
+// ---------------------------------------------------------------- dispatch
+
+int execute_op_simple(struct OpComputeRequest *req) {
+  if (!req || !set_session_device() || !g.backend) {
+    return -1;
+  }
+  const int rc = enqueue_op(req);
+  if (rc != 0) {
+    return rc;
+  }
+  return wait_stream();
+}
+
+// ---------------------------------------------------------------- buffers
+
+int htp_buf_alloc(size_t size) {
+  if (!set_session_device() || size == 0) {
+    return -1;
+  }
+  Buffer b;
+  if (cudaMalloc(&b.ptr, size) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (cudaMemset(b.ptr, 0, size) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(b.ptr);
+    return -1;
+  }
+  b.size = size;
+  b.kind = kDeviceBuf;
+  return register_buffer(b);
+}
+
+int htp_buf_alloc_host(size_t size) {
+  if (!set_session_device() || size == 0) {
+    return -1;
+  }
+  Buffer b;
+  if (cudaHostAlloc(&b.ptr, size, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  memset(b.ptr, 0, size);
+  b.size = size;
+  b.kind = kHostBuf;
+  return register_buffer(b);
+}
+
+int htp_buf_wrap(void *device_ptr, size_t size) {
+  if (!g.open || !device_ptr || size == 0) {
+    return -1;
+  }
+  Buffer b;
+  b.ptr  = static_cast<uint8_t *>(device_ptr);
+  b.size = size;
+  b.kind = kWrappedBuf;
+  return register_buffer(b);
+}
+
+int htp_buf_free(int fd) {
+  Buffer b;
+  {
+    std::lock_guard<std::mutex> lk(g.mu);
+    auto                        it = g.bufs.find(fd);
+    if (it == g.bufs.end() || fd == g.chan_fd) {
+      return -1;  // unknown, or still the active message buffer
+    }
+    b = it->second;
+    g.bufs.erase(it);
+  }
+  if (!set_session_device()) {
+    return -1;
+  }
+  if (b.kind == kDeviceBuf) {
+    if (g.stream) {
+      cudaStreamSynchronize(g.stream);
+    }
+    cudaFree(b.ptr);
+  } else if (b.kind == kHostBuf) {
+    cudaFreeHost(b.ptr);
+  }
+  return 0;
+}
+
+static int copy_region(int fd, size_t offset, void *host, size_t size, bool upload) {
+  Buffer b;
+  if (!host || !lookup(fd, &b) || offset > b.size || size > b.size - offset) {
+    return -1;
+  }
+  if (size == 0) {
+    return 0;
+  }
+  if (b.kind == kHostBuf) {
+    if (upload) {
+      memcpy(b.ptr + offset, host, size);
+    } else {
+      memcpy(host, b.ptr + offset, size);
+    }
+    return 0;
+  }
+  if (!set_session_device()) {
+    return -1;
+  }
+  cudaError_t e = upload ? cudaMemcpyAsync(b.ptr + offset, host, size, cudaMemcpyHostToDevice, g.stream)
+                         : cudaMemcpyAsync(host, b.ptr + offset, size, cudaMemcpyDeviceToHost, g.stream);
+  if (e == cudaSuccess) {
+    e = cudaStreamSynchronize(g.stream);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 0;
+}
+
+int htp_buf_upload(int fd, size_t offset, const void *src, size_t size) {
+  return copy_region(fd, offset, const_cast<void *>(src), size, true);
+}
+
+int htp_buf_download(int fd, size_t offset, void *dst, size_t size) {
+  return copy_region(fd, offset, dst, size, false);
+}
+
+void *htp_buf_ptr(int fd) {
+  Buffer b;
+  return lookup(fd, &b) ? b.ptr : nullptr;
+}
+
+int htp_buf_is_host(int fd) {
+  Buffer b;
+  return lookup(fd, &b) ? (b.kind == kHostBuf ? 1 : 0) : -1;
+}
+
+size_t htp_buf_size(int fd) {
+  Buffer b;
+  return lookup(fd, &b) ? b.size : 0;
+}
+
+void *htp_session_stream(void) {
+  return g.open ? (void *) g.stream : nullptr;
+}
+
+int htp_session_synchronize(void) {
+  if (!set_session_device() || !g.backend) {
+    return -2;
+  }
+  return wait_stream();
+}
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+/*
+ * Compute entry points of the B200 library: raw device pointers, plain sizes, one CUDA stream.
+ * This is the C-ABI the host layer (session / message channel / execute_op_simple) is built on
+ * and the one a foreign-language binding would target for zero-copy use.
+ *
+ * All functions act on the CUDA device that is current on the calling thread and return
+ *   0   success (work is enqueued on `stream`, not necessarily finished),
+ *  -1   invalid arguments (the reference's only failure code, src/dsp/ops/mat_mul.c:878-892),
+ *  -2   a CUDA runtime call failed,
+ *  >0   (htp_b200_stream_status only) a kernel reported a bounded wait that ran out.
+ * There is no CPU fallback: without a usable CUDA device every call fails.
+ */
+#ifndef HTP_OPS_B200_H
+#define HTP_OPS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* activation element types */
+#define HTP_B200_ACT_F32 0
+#define HTP_B200_ACT_F16 1
+
+/*
+ * dst[m][n] (fp32) = activation[m][k] . weight[n][k]^T, weight in standard ggml Q4_0
+ * (weight_type 2) or Q8_0 (weight_type 8) blocks, n rows of k/32 blocks.
+ * Replaces hmx_mat_mul_permuted_qk_0_d16a32 (reference include/dsp/ops.h:19-20,
+ * src/dsp/ops/mat_mul.c:875-1153) and keeps its argument checks: non-null pointers, non-zero
+ * sizes, k % 32 == 0, n % 32 == 0, all three pointers 128-byte aligned; anything else -> -1.
+ * Unlike the reference neither activations nor outputs are rounded to fp16.
+ * `stream` is a cudaStream_t (NULL = the default stream).
+ */
+int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                     int act_type, void *stream);
+
+/*
+ * Integer probe of the block unpack: for each of n_blocks consecutive blocks writes
+ * s[b] = sum_i v_i and t[b] = sum_i (i + 1) * v_i (int32), v_i the block's 32 integer values in
+ * element order.  No counterpart in the reference (it has no integer path); exists so the
+ * unpack the matmul kernels use can be checked bit-exactly.
+ */
+int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream);
+
+/* Bytes of an n x k weight matrix; the size rule of the dispatcher (reference
+ * src/dsp/op_executor.cc:124-126) evaluated in 64 bits.  0 for an unknown type or k % 32 != 0. */
+size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
+
+/* Waits for `stream`, then returns and clears the first error code a kernel recorded on it
+ * (0 = none), or -2 when the stream itself is in error. */
+int htp_b200_stream_status(void *stream);
+
+/* Tuning / debugging switches: "pdl" (programmatic dependent launch, default 1),
+ * "force_generic" (route every matmul to the shape-agnostic kernel, default 0).  Returns the previous value,
+ * or -1 for an unknown name. */
+int htp_b200_set_option(const char *name, int value);
+
+/* Number of kernel launches this process has issued through the library (all devices). */
+uint64_t htp_b200_launch_count(void);
+
+const char *htp_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* HTP_OPS_B200_H */
