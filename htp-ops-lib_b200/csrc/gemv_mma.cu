@@ -18,7 +18,7 @@
 //     dequantise-then-dot, without rounding q*d to fp16.
 //   * fp32 activations are split as x = hi + lo with hi = fp16(x), lo = fp16(x - hi), so the
 //     product is exact to ~2^-22; hi and lo occupy separate MMA columns (M <= 4) or two chained
-//     MMAs (M <= 8).  Tokens whose |x| reaches 2^15 are pre-scaled by a power of two.
+//     MMAs (M <= 8).  Each token is normalised by a power of two first (undone on output).
 //   * The activation fragments for the whole K range live in shared memory, built once per CTA.
 //   * Programmatic dependent launch: the weight prefetch starts before the previous kernel in
 //     the stream has finished; activations are read, and outputs written, only after it has.
@@ -86,7 +86,8 @@ template <int WT, bool A16, int MPAD>
 __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
   using C = Cfg<WT, A16, MPAD>;
   if constexpr (!A16) {
-    // per-token power-of-two pre-scale so that fp16(x) cannot overflow
+    // per-token power-of-two normalisation: the largest |x| of a token lands in [2^14, 2^15), so
+    // fp16(x) neither overflows nor drops into the subnormal range for small-magnitude tokens
     if (tid < 8) {
       sm->tok_amax_bits[tid] = 0;
     }
@@ -111,7 +112,7 @@ __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid
       const int bits = sm->tok_amax_bits[tid];
       const int e    = ((bits >> 23) & 0xff) - 127;  // floor(log2(amax))
       int       sh   = e - 14;
-      sh             = sh < 0 ? 0 : (sh > 100 ? 100 : sh);
+      sh             = sh < -100 ? -100 : (sh > 100 ? 100 : sh);
       sm->tok_scale[tid] = __int_as_float((127 - sh) << 23);
       sm->tok_inv[tid]   = __int_as_float((127 + sh) << 23);
     }
