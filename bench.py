@@ -1,0 +1,515 @@
+"""Benchmark of the quantised MUL_MAT path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Headline workload (every N): the lm_head configuration - Q8_0 weights 128256 x 4096, fp16
+activations, M = 1 - the one configuration that is sharded by output rows over 1/2/4/8 GPUs with
+an NCCL all-gather of the fp32 logits.  One step = one pass: every rank runs the decode mat-vec on
+its row slab, then the slabs are gathered.  `value` = algorithmic bytes of the WHOLE matrix per
+step / max-over-ranks device time (strong scaling), inputs resident in HBM; `e2e` = the same
+through the message channel with host buffers (activation upload and logits download inside the
+timed region).  The other configurations are measured briefly on one GPU and reported under
+`configs` in the same JSON line (decode GB/s for configs 0, 1, 3; prefill TFLOP/s for configs 2
+and 4 at M = 256).
+
+Timing: CUDA events on the launching stream, >= 3 warm-up steps, max over ranks; decode weights are
+rotated through enough distinct copies that every pass reads from HBM, not L2; SM clocks and
+throttle reasons are sampled with nvidia-smi during the timed region.
+
+`--impl reference` times the CPU restatement of the reference's dequantise-then-dot semantics
+(oracle/, fp32, all host threads) on a bounded sample of the same workload: the reference's own
+implementation is Hexagon HVX/HMX code and cannot be built for a host CPU.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as entry  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def read_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]),
+                "tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def read_traffic(key: str):
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
+    p = ROOT / "profiles" / "ncu_traffic.json"
+    if p.exists():
+        return json.loads(p.read_text()).get(key)
+    return None
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self.proc = gpu_index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+
+def rows_of_rank(n: int, rank: int, world: int) -> tuple[int, int]:
+    from htp_ops_lib_b200 import sharding
+    return sharding.row_range(n, rank, world)
+
+
+def time_region(torch, fn, steps: int, stream) -> float:
+    """Milliseconds for `steps` calls of fn, CUDA events on `stream`, synchronised on both sides."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for i in range(steps):
+        fn(i)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def cpu_baseline(wl, cfg_name: str, m: int, seconds: float = 12.0, sample_rows: int = 8192):
+    """The CPU restatement (fp32, threaded) timed on a bounded row sample of the workload."""
+    import numpy as np
+    oracle = entry.load_oracle()
+    lib = None
+    try:  # a build tuned to this machine, outside the repository
+        tmp = Path(tempfile.mkdtemp(prefix="htp_oracle_native_"))
+        lib = oracle.load(oracle.build(tmp, arch="native"))
+        kind_note = "-O3 -march=native"
+    except Exception:  # noqa: BLE001
+        lib = oracle.load()
+        kind_note = "-O3 -march=x86-64-v3 (prebuilt)"
+    cfg = wl.CONFIGS[cfg_name]
+    op = cfg.ops[-1] if cfg_name == "cfg3" else cfg.ops[0]
+    rows = min(sample_rows, op.n)
+    wq = wl.make_weight(cfg, 0 if cfg_name != "cfg3" else len(cfg.ops) - 1, rows=(0, rows),
+                        quantizer=lambda w, t: oracle.quantize(w, t))
+    x = wl.make_activation(cfg, m, 0 if cfg_name != "cfg3" else len(cfg.ops) - 1)
+    cores = oracle.usable_cores()
+    oracle.mul_mat_f32(x, wq, rows, op.wtype, lib=lib)  # warm-up
+    t0, n = time.perf_counter(), 0
+    while True:
+        oracle.mul_mat_f32(x, wq, rows, op.wtype, lib=lib)
+        n += 1
+        dt = time.perf_counter() - t0
+        if dt >= seconds or n >= 100000:
+            break
+    per = dt / n
+    return {"seconds_per_sample": per, "rows": rows, "cores": cores, "op": op, "build": kind_note,
+            "gbps": wl.algorithmic_bytes(op, m, rows) / per / 1e9, "tflops": wl.flops(op, m, rows) / per / 1e12,
+            "iters": n}
+
+
+# ------------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    """CPU arm: rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    entry.load_package()
+    from htp_ops_lib_b200 import workloads as wl
+    steps, warm = args.steps, args.warmup
+    cfg_name, m = "cfg4", 1
+    secs = max(2.0, min(60.0, 0.5 * (steps + warm)))
+    b = cpu_baseline(wl, cfg_name, m, seconds=secs, sample_rows=16384)
+    line = {
+        "impl": "reference", "metric": "decode_GBps", "value": round(b["gbps"], 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(b["seconds_per_sample"] * 1e3, 4),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1 (CPU restatement of the "
+                               "reference's dequantise-then-dot; the reference's HVX/HMX code cannot be built here)"},
+        "cpu_baseline": {"value": round(b["gbps"], 3), "unit": "GB/s", "cores": b["cores"], "kind": "port",
+                         "sample": f"first {b['rows']} of 128256 weight rows per step, {b['iters']} steps, "
+                                   f"{b['build']}"},
+        "e2e": {"value": round(b["gbps"], 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bool):
+    """Configs 0-3 and config 4 at M = 256 on this GPU: brief, device-resident, rotating copies."""
+    out = {}
+    dev = torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream()
+
+    def run_case(name, cfg, op_idx, m, steps):
+        op = cfg.ops[op_idx]
+        slab = wl.weight_bytes(op.wtype, op.k, op.n)
+        copies = max(2, -(-L2_BYTES // slab) + 1) if m <= 8 else 1
+        w0 = wl.make_weight_torch(cfg, dev, op_idx)
+        ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+        x = torch.randn((m, op.k), device=dev, dtype=torch.float32)
+        x = x.to(torch.float16) if op.act_f16 else x
+        y = torch.empty((m, op.n), device=dev, dtype=torch.float32)
+        act_t = pkg.ACT_F16 if op.act_f16 else pkg.ACT_F32
+
+        def step(i):
+            rc = lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, op.k, op.n, op.wtype,
+                                      act_t, stream_ptr)
+            assert rc == 0
+        for i in range(3):
+            step(i)
+        ms = time_region(torch, step, steps, stream) / steps
+        assert lib.htp_b200_stream_status(stream_ptr) == 0
+        r = {"ms": round(ms, 5), "m": m, "k": op.k, "n": op.n, "weight_copies": copies}
+        if m <= 8:
+            gb = wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9
+            r.update(GBps=round(gb, 1), frac_of_hbm_peak=round(gb / peaks["hbm_gbs"], 4))
+        else:
+            tf = wl.flops(op, m) / (ms * 1e-3) / 1e12
+            r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
+        out[name] = r
+        del ws, w0
+
+    steps = 20 if quick else 100
+    run_case("cfg0_q4_0_gemv_4096x4096_m1", wl.CONFIGS["cfg0"], 0, 1, steps)
+    run_case("cfg1_q8_0_gemv_11008x4096_m1", wl.CONFIGS["cfg1"], 0, 1, steps)
+    run_case("cfg2_q4_0_prefill_14336x4096_m512", wl.CONFIGS["cfg2"], 0, 512, max(3, steps // 10))
+    run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(3, steps // 10))
+    out.update(measure_decoder_stack(torch, pkg, lib, wl, peaks, quick))
+    return out
+
+
+def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
+    """Config 3: 32 layers x 7 Q4_0 matmuls issued in order through the message channel (one message
+    of 224 requests per pass); 3.9 GB of weights per pass, so every pass streams from HBM."""
+    cfg = wl.CONFIGS["cfg3"]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    if lib.open_dsp_session(torch.cuda.current_device(), 1) != 0:
+        return {"cfg3": {"error": "open_dsp_session failed"}}
+    lib.init_htp_backend()
+    try:
+        layers = 32
+        # one distinct weight set per layer (generated once per matrix kind, then perturbed per layer
+        # by copying: the bytes differ in address, which is what matters for HBM traffic)
+        base = [wl.make_weight_torch(cfg, dev, i, 0) for i in range(len(cfg.ops))]
+        weights = [[b if l == 0 else b.clone() for b in base] for l in range(layers)]
+        wfd = [[lib.htp_buf_wrap(w.data_ptr(), w.numel()) for w in lw] for lw in weights]
+        total_w = sum(w.numel() for lw in weights for w in lw)
+        chan = pkg.MessageChannel(16384)
+        try:
+            for m in cfg.ms:
+                xs = [torch.randn((m, op.k), device=dev, dtype=torch.float32) for op in cfg.ops]
+                ys = [torch.empty((m, op.n), device=dev, dtype=torch.float32) for op in cfg.ops]
+                xfd = [lib.htp_buf_wrap(x.data_ptr(), x.numel() * 4) for x in xs]
+                yfd = [lib.htp_buf_wrap(y.data_ptr(), y.numel() * 4) for y in ys]
+                reqs = []
+                for l in range(layers):
+                    for i, op in enumerate(cfg.ops):
+                        reqs.append(pkg.pack_matmul_request(pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32, (yfd[i], 0),
+                                                            (xfd[i], 0), (wfd[l][i], 0), m, op.k, op.n))
+                for _ in range(2):
+                    st = chan.submit(reqs)
+                    assert all(s == 0 for s in st), st
+                n_pass = 5 if quick else 20
+                t0 = time.perf_counter()
+                for _ in range(n_pass):
+                    chan.submit(reqs)
+                ms = (time.perf_counter() - t0) / n_pass * 1e3
+                algo = total_w + layers * sum(m * op.k * 4 + m * op.n * 4 for op in cfg.ops)
+                gb = algo / (ms * 1e-3) / 1e9
+                out[f"cfg3_llama8b_stack_q4_0_m{m}"] = {
+                    "ms_per_pass": round(ms, 4), "ops_per_pass": len(reqs), "GBps": round(gb, 1),
+                    "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4),
+                    "timed": "host wall clock around message-channel round trips (224 requests per message)"}
+                for fd in xfd + yfd:
+                    lib.htp_buf_free(fd)
+        finally:
+            chan.close()
+    finally:
+        lib.close_dsp_session()
+    return out
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    pkg = entry.load_package()
+    from htp_ops_lib_b200 import sharding
+    from htp_ops_lib_b200 import workloads as wl
+    lib = pkg.load()  # raises if the CUDA library is not built: there is no fallback
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = read_peaks()
+    steps, warm = args.steps, max(3, args.warmup)
+
+    cfg = wl.CONFIGS["cfg4"]
+    op, m = cfg.ops[0], 1
+    r0, r1 = sharding.row_range(op.n, rank, world)
+    n_loc = r1 - r0
+    slab = wl.weight_bytes(op.wtype, op.k, n_loc)
+    copies = max(2, -(-L2_BYTES // slab) + 1)
+    w0 = wl.make_weight_torch(cfg, dev, rows=(r0, r1))
+    ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+    x_host = torch.randn((m, op.k), dtype=torch.float32).to(torch.float16).pin_memory()
+    x = x_host.to(dev)
+    logits = torch.empty((m, op.n), device=dev, dtype=torch.float32)  # every rank ends with all of it
+    y_loc = logits[:, r0:r1] if world == 1 else torch.empty((m, n_loc), device=dev, dtype=torch.float32)
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+
+    def kernel(i):
+        rc = lib.htp_b200_mul_mat(y_loc.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, op.k, n_loc,
+                                  op.wtype, pkg.ACT_F16, sp)
+        assert rc == 0
+
+    def step(i):
+        kernel(i)
+        if world > 1:
+            sharding.all_gather_logits(dist, logits, y_loc, m, op.n, world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(warm):
+        step(i)
+    barrier()
+    l0 = lib.htp_b200_launch_count()
+    with ClockSampler(local) as clk:
+        # repeat the timed region until it is long enough for nvidia-smi to see it (>= ~0.5 s)
+        reps, ms_total, k_total = 0, 0.0, 0
+        while True:
+            barrier()
+            ms_total += time_region(torch, step, steps, stream)
+            k_total += steps
+            reps += 1
+            if reps == 1:
+                first_ms, first_launches = ms_total, lib.htp_b200_launch_count() - l0
+            if ms_total >= 500.0 or reps >= 400:
+                break
+    barrier()
+    assert lib.htp_b200_stream_status(sp) == 0
+    t = torch.tensor([first_ms, ms_total / k_total * steps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t[0]) / steps  # EXACTLY `steps` steps, max over ranks
+    ms_step_long = float(t[1]) / steps
+    total_bytes = wl.algorithmic_bytes(op, m)
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # kernel alone (no gather) for the roofline of the dominant kernel
+    barrier()
+    k_ms = time_region(torch, kernel, steps, stream) / steps
+    t = torch.tensor([k_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    k_ms = float(t[0])
+    k_bytes = wl.algorithmic_bytes(op, m, n_loc)
+    achieved = k_bytes / (k_ms * 1e-3) / 1e9
+
+    # ---- end to end through the message channel with host buffers
+    e2e = None
+    if lib.open_dsp_session(local, 1) == 0:
+        lib.init_htp_backend()
+        chan = pkg.MessageChannel(4096)
+        try:
+            fx = lib.htp_buf_alloc(x.numel() * 2)
+            fw = [lib.htp_buf_wrap(w.data_ptr(), w.numel()) for w in ws]
+            fy = lib.htp_buf_wrap(y_loc.data_ptr(), m * n_loc * 4) if world > 1 else lib.htp_buf_wrap(
+                logits.data_ptr(), m * op.n * 4)
+            out_host = torch.empty((m, op.n), dtype=torch.float32).pin_memory()
+            reqs = [[pkg.pack_matmul_request(pkg.HTP_OPS_MAT_MUL_W8D16A16, (fy, 0), (fx, 0), (f, 0), m, op.k, n_loc)]
+                    for f in fw]
+
+            def e2e_step(i):
+                assert lib.htp_buf_upload(fx, 0, x_host.data_ptr(), x_host.numel() * 2) == 0
+                st = chan.submit(reqs[i % copies])
+                assert st == [0], st
+                if world > 1:
+                    sharding.all_gather_logits(dist, logits, y_loc, m, op.n, world)
+                out_host.copy_(logits, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+            for i in range(warm):
+                e2e_step(i)
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(steps):
+                e2e_step(i)
+            barrier()
+            dt = (time.perf_counter() - t0) / steps
+            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t[0])
+            e2e = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "ms_per_step": round(dt * 1e3, 4),
+                   "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": m * op.n * 4,
+                   "path": "htp_buf_upload -> message channel (1 request) -> "
+                           + ("NCCL all-gather -> " if world > 1 else "") + "download of the fp32 logits; "
+                           "weights stay resident, as the reference's mapped weight buffers do"}
+        finally:
+            chan.close()
+            lib.close_dsp_session()
+
+    line = None
+    if rank == 0:
+        clocks = clk.summary()
+        line = {
+            "metric": "decode_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16 x int8 -> f32", "data": "synthetic",
+            "config": {"workload": "cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1, rows sharded over "
+                                   f"{world} GPU(s)" + (" + NCCL all-gather of fp32 logits" if world > 1 else ""),
+                       "l2": f"rotating {copies} distinct weight copies per rank "
+                             f"({slab * copies / 1e6:.0f} MB > 126 MB L2): every pass reads HBM",
+                       "algorithmic_bytes_per_step": total_bytes,
+                       "ms_per_step_over_long_run": round(ms_step_long, 5)},
+            "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q8_0,f16,M=1>", "achieved": round(achieved, 1),
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         "peak_source": f"{peaks['source']} (copy bandwidth)", "ms_per_launch": round(k_ms, 5),
+                         "algorithmic_bytes_per_launch": k_bytes, "traffic": read_traffic("cfg4_m1_q8_0")},
+            "e2e": e2e, "gpu_launches": int(first_launches), "clocks": clocks,
+        }
+    # single-GPU extras and the CPU baseline: rank 0 at N = 1 only
+    if world == 1:
+        del ws, w0
+        torch.cuda.empty_cache()
+        if not args.no_extras:
+            line["configs"] = measure_single_gpu_configs(torch, pkg, lib, wl, peaks, sp, args.quick)
+        if not args.no_cpu:
+            b = cpu_baseline(wl, "cfg4", 1, seconds=12.0, sample_rows=16384)
+            line["cpu_baseline"] = {"value": round(b["gbps"], 3), "unit": "GB/s", "cores": b["cores"], "kind": "port",
+                                    "sample": f"first {b['rows']} of 128256 weight rows, {b['iters']} repeats over "
+                                              f"{b['seconds_per_sample'] * b['iters']:.1f} s, fp32, {b['build']}"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_case(args):
+    """One matmul shape, device-resident, rotating weight copies: the small case the ncu captures
+    use (`--case q8_0,f16,1,4096,32768`)."""
+    import torch
+
+    pkg = entry.load_package()
+    from htp_ops_lib_b200 import workloads as wl
+    lib = pkg.load()
+    wt_s, act_s, m, k, n = args.case.split(",")
+    m, k, n = int(m), int(k), int(n)
+    wtype = {"q4_0": wl.TYPE_Q4_0, "q8_0": wl.TYPE_Q8_0}[wt_s]
+    a16 = act_s == "f16"
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = wl.Config("case", 99, (m,), (wl.MatMul("case", wtype, a16, k, n),))
+    op = cfg.ops[0]
+    slab = wl.weight_bytes(wtype, k, n)
+    copies = max(2, -(-L2_BYTES // slab) + 1) if m <= 8 else 1
+    w0 = wl.make_weight_torch(cfg, dev)
+    ws = [w0] + [w0.clone() for _ in range(copies - 1)]
+    x = torch.randn((m, k), device=dev, dtype=torch.float32)
+    x = x.to(torch.float16) if a16 else x
+    y = torch.empty((m, n), device=dev, dtype=torch.float32)
+    stream = torch.cuda.current_stream()
+
+    def step(i):
+        assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, k, n, wtype,
+                                    pkg.ACT_F16 if a16 else pkg.ACT_F32, stream.cuda_stream) == 0
+    for i in range(args.warmup):
+        step(i)
+    ms = time_region(torch, step, args.steps, stream) / args.steps
+    assert lib.htp_b200_stream_status(stream.cuda_stream) == 0
+    peaks = read_peaks()
+    r = {"case": args.case, "ms": round(ms, 5), "weight_copies": copies,
+         "GBps": round(wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9, 1),
+         "TFLOPs": round(wl.flops(op, m) / (ms * 1e-3) / 1e12, 2)}
+    r["frac_hbm"] = round(r["GBps"] / peaks["hbm_gbs"], 4)
+    r["frac_tensor"] = round(r["TFLOPs"] / peaks["tflops"], 4)
+    print(json.dumps(r), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the brief single-GPU runs of the other configs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--quick", action="store_true", help="fewer repeats in the extra runs")
+    ap.add_argument("--case", default=None, help="wtype,act,m,k,n: time one shape only (profiling aid)")
+    args = ap.parse_args()
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

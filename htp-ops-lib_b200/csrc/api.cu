@@ -147,7 +147,7 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       a.N             = n;
       a.kblocks       = pn * 8;
       a.accumulate    = c > 0;
-      a.stages_per_tile = (a.kblocks + kGemvStageBlocks - 1) / kGemvStageBlocks;
+      a.stages_per_tile = (a.kblocks + gemv_stage_blocks(wt) - 1) / gemv_stage_blocks(wt);
       a.total_items     = (long long) (n / kGemvTileRows) * a.stages_per_tile;
       const size_t frag = gemv_frag_bytes(wt, a16, mpad, a.kblocks);
       // ring depth: never more stages than the busiest CTA has items

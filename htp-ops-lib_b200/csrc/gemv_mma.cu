@@ -8,10 +8,13 @@
 //     every SM streams the same number of bytes whatever N is.  A tile cut by a range boundary is
 //     finished through a small scratch area: each part is written in a fixed slot, the last CTA to
 //     arrive adds the parts in ascending order (bit-reproducible, no floating-point atomics).
-//   * A producer warp streams the raw 18-/34-byte blocks with one bulk async copy per weight row
-//     and stage into a shared-memory ring (mbarrier full/empty pairs, L2 evict-first).  Rows are
-//     padded to an odd multiple of 16 bytes so the fragment reads below are bank-conflict-free.
-//   * Eight consumer warps split a stage along K.  Quants stay INTEGERS: a lane turns one 32-bit
+//   * A producer thread streams the raw 18-/34-byte blocks with ONE tiled TMA copy per stage
+//     (32 rows x one stage of blocks, through a tensor map over the weight bytes) into a
+//     shared-memory ring (mbarrier full/empty pairs, L2 evict-first).  The box is 16 bytes wider
+//     than a stage, which makes the shared-memory row pitch an odd multiple of 16 bytes: the
+//     fragment reads below are bank-conflict-free, and the 16 extra bytes are simply the start of
+//     the next stage (zero fill past the end of the row).
+//   * Sixteen consumer warps split a stage along K.  Quants stay INTEGERS: a lane turns one 32-bit
 //     word of nibbles/bytes into fp16 pairs (unpack.cuh) that are the A fragment of a warp MMA
 //     (m16n8k16, fp32 accumulate) whose B fragment holds the activations.  The block scale is
 //     applied to the 32-weight partial sum in fp32, i.e. sum_k (q_k x_k) * d - the same value as
@@ -26,6 +29,7 @@
 // Every mbarrier wait is bounded; a wait that runs out stores an error code and the CTA leaves.
 #include "gemv_mma.h"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "ptx.cuh"
@@ -35,7 +39,8 @@ namespace htp {
 
 namespace {
 
-constexpr int kConsumerWarps   = 8;
+constexpr int kConsumerWarps   = 16;
+constexpr int kReduceThreads   = 256;  // one per element of a 32-row x 8-column tile result
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads         = kConsumerThreads + 32;
 
@@ -45,6 +50,8 @@ struct Cfg {
   static constexpr int  CH       = (!A16 && MPAD == 8) ? 2 : 1;           // chained MMAs per k-step
   static constexpr int  NC       = A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD);  // MMA columns in use
   static constexpr bool SPLITCOL = (!A16 && MPAD < 8);                    // column = 2 m + piece
+  static constexpr int  SB       = gemv_stage_blocks(WT);  // blocks per stage and row
+  static constexpr int  BPW      = SB / kConsumerWarps;    // blocks per consumer warp and stage (even count)
   static constexpr int  PSTRIDE  = gemv_row_pitch(WT);
   static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
   static constexpr int  FRAG_U2  = 2 * CH * NC * 4;  // uint2 entries per block
@@ -220,11 +227,12 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
   const float da = lds_scale(ra);
   const float db = lds_scale(rb);
 
-  float c[4] = { 0.f, 0.f, 0.f, 0.f };
-#pragma unroll
-  for (int ch = 0; ch < C::CH; ++ch) {
-    mma_16816(c, a0, bf[0][ch].x, bf[0][ch].y);
-    mma_16816(c, a1, bf[1][ch].x, bf[1][ch].y);
+  float c[4];
+  mma_16816_zero(c, a0, bf[0][0].x, bf[0][0].y);
+  mma_16816(c, a1, bf[1][0].x, bf[1][0].y);
+  if constexpr (C::CH == 2) {
+    mma_16816(c, a0, bf[0][1].x, bf[0][1].y);
+    mma_16816(c, a1, bf[1][1].x, bf[1][1].y);
   }
   acc[0] = fmaf(da, c[0], acc[0]);
   acc[1] = fmaf(da, c[1], acc[1]);
@@ -246,11 +254,16 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
   }
   named_bar_sync(1, kConsumerThreads);
   float v = 0.f;
+  if (tid < kReduceThreads) {
 #pragma unroll
-  for (int w = 0; w < kConsumerWarps; ++w) {
-    v += sm->red[w][tid];
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      v += sm->red[w][tid];
+    }
   }
   named_bar_sync(1, kConsumerThreads);  // red may be rewritten by the next flush
+  if (tid >= kReduceThreads) {
+    return;  // the first eight warps finish the tile
+  }
 
   const long long first = tile * S, last = first + S - 1;
   bool            write_out = true;
@@ -263,7 +276,7 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
     float          *mine    = p.partials + ((size_t) blockIdx.x * 2 + slot) * 256;
     __stcg(mine + tid, v);
     __threadfence();
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(2, kReduceThreads);
     if (tid == 0) {
       const unsigned old  = atomicAdd(p.counters + c_first, 1u);
       const int      done = (old == (unsigned) (c_last - c_first));
@@ -272,7 +285,7 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
       }
       sm->last_flag = done;
     }
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(2, kReduceThreads);
     write_out = sm->last_flag != 0;
     if (write_out) {
       __threadfence();
@@ -282,7 +295,7 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
         v += __ldcg(p.partials + ((size_t) c * 2 + s) * 256 + tid);
       }
     }
-    named_bar_sync(1, kConsumerThreads);  // last_flag may be rewritten by the next flush
+    named_bar_sync(2, kReduceThreads);  // last_flag may be rewritten by the next flush
   }
   if constexpr (C::SPLITCOL) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);  // hi-piece column + lo-piece column
@@ -314,7 +327,8 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
 // ------------------------------------------------------------------ the kernel
 
 template <int WT, bool A16, int MPAD>
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p) {
+__global__ void __launch_bounds__(kThreads, 1)
+  gemv_mma_kernel(const GemvArgs p, const __grid_constant__ CUtensorMap wmap) {
   using C = Cfg<WT, A16, MPAD>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem    *sm     = reinterpret_cast<Smem *>(smem_raw);
@@ -340,25 +354,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p)
 
   if (warp == kConsumerWarps) {
     // ---------------- producer: weights only, may run ahead of the previous kernel's completion
-    const uint64_t pol = l2_policy_evict_first();
-    int            li  = 0;
-    for (long long it = it0; it < it1; ++it, ++li) {
-      const int slot = li % NST, ph = (li / NST) & 1;
-      if (!mbar_wait(&sm->empty[slot], ph ^ 1)) {
-        record_error(p, kGemvErrProducerWait);
-        break;
+    if (lane == 0) {
+      tma_prefetch_descriptor(&wmap);
+      const uint64_t pol = l2_policy_evict_first();
+      long long      tile = it0 / S;
+      int            st   = (int) (it0 - tile * S);
+      int            slot = 0, ph = 0;
+      for (long long it = it0; it < it1; ++it) {
+        if (!mbar_wait(&sm->empty[slot], ph ^ 1)) {
+          record_error(p, kGemvErrProducerWait);
+          break;
+        }
+        mbar_arrive_expect_tx(&sm->full[slot], (uint32_t) C::STAGE);
+        // box = 32 rows x PSTRIDE bytes, in 8-byte elements
+        tma_load_2d(stages + (size_t) slot * C::STAGE, &wmap, st * (C::SB * C::BB / 8),
+                    (int) (tile * kGemvTileRows), &sm->full[slot], pol);
+        if (++slot == NST) {
+          slot = 0;
+          ph ^= 1;
+        }
+        if (++st == S) {
+          st = 0;
+          ++tile;
+        }
       }
-      const long long tile  = it / S;
-      const int       st    = (int) (it - tile * S);
-      const int       nblk  = min(kGemvStageBlocks, p.kblocks - st * kGemvStageBlocks);
-      const uint32_t  bytes = (uint32_t) nblk * C::BB;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&sm->full[slot], bytes * kGemvTileRows);
-      }
-      __syncwarp();
-      const uint8_t *src = p.w + (tile * kGemvTileRows + lane) * p.w_row_bytes + p.w_k_off_bytes +
-                           (long long) st * kGemvStageBlocks * C::BB;
-      bulk_g2s(stages + (size_t) slot * C::STAGE + lane * C::PSTRIDE, src, bytes, &sm->full[slot], pol);
     }
   } else {
     // ---------------- consumers
@@ -376,51 +395,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p)
         acc[rg][i] = 0.f;
       }
     }
-    long long cur_tile = it0 / S;
-    int       li       = 0;
-    bool      ok       = true;
-    for (long long it = it0; it < it1; ++it, ++li) {
-      const long long tile = it / S;
-      const int       st   = (int) (it - tile * S);
-      if (tile != cur_tile) {
-        flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid);
-        cur_tile = tile;
-#pragma unroll
-        for (int rg = 0; rg < 2; ++rg) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[rg][i] = 0.f;
-          }
-        }
-      }
-      const int slot = li % NST, ph = (li / NST) & 1;
+    // item -> (tile, stage) and ring position are tracked incrementally: no divisions in the loop
+    long long tile = it0 / S;
+    int       st   = (int) (it0 - tile * S);
+    int       slot = 0, ph = 0;
+    bool      ok   = true;
+    // lanes whose MMA column is beyond the columns in use read a valid fragment of another column:
+    // their output columns are never stored, so what they multiply is irrelevant
+    const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
+    const uint8_t *warp_base = stages + g * C::PSTRIDE + warp * C::BPW * C::BB;
+    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW * 2) * C::CH * C::NC * 4;
+    for (long long it = it0; it < it1; ++it) {
       if (!mbar_wait(&sm->full[slot], ph)) {
         record_error(p, kGemvErrConsumerWait);
         ok = false;
         break;
       }
-      const int nblk = min(kGemvStageBlocks, p.kblocks - st * kGemvStageBlocks);
-      const int bl0  = warp * 4;
-      if (bl0 < nblk) {
-        const uint8_t *sb = stages + (size_t) slot * C::STAGE + g * C::PSTRIDE;
+      const int nblk = min(C::SB, p.kblocks - st * C::SB);
+      if (warp * C::BPW < nblk) {
+        const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
+        const uint2   *fp = warp_frag + (size_t) (st * C::SB * 2) * C::CH * C::NC * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int    bl = bl0 + i;
-          const uint2 *fp = frags + (size_t) ((st * kGemvStageBlocks + bl) * 2) * C::CH * C::NC * 4;
-          uint2        bf[2][2];
+        for (int i = 0; i < C::BPW; ++i) {
+          uint2 bf[2][2];
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
 #pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
-              bf[j][ch] = make_uint2(0u, 0u);
-              if (ch < C::CH && g < C::NC) {
-                bf[j][ch] = fp[(j * C::CH + ch) * C::NC * 4 + g * 4 + t];
-              }
+              bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
             }
           }
 #pragma unroll
           for (int rg = 0; rg < 2; ++rg) {
-            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + bl * C::BB;
+            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
             if ((i & 1) == 0) {
               block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
             } else {
@@ -433,7 +440,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p)
       if (lane == 0) {
         mbar_arrive(&sm->empty[slot]);
       }
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1;
+      }
+      if (++st == S) {
+        st = 0;
+        if (it + 1 < it1) {
+          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid);
+#pragma unroll
+          for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[rg][i] = 0.f;
+            }
+          }
+          ++tile;
+        }
+      }
     }
+    const long long cur_tile = tile;
     if (ok && it1 > it0) {
       flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid);
     }
@@ -441,7 +467,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_kernel(const GemvArgs p)
 }
 
 template <int WT, bool A16, int MPAD>
-cudaError_t launch_one(const GemvArgs &args, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+cudaError_t launch_one(const GemvArgs &args, const CUtensorMap &wmap, int grid, size_t smem, cudaStream_t stream,
+                       bool pdl) {
   auto        kern = gemv_mma_kernel<WT, A16, MPAD>;
   cudaError_t e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
   if (e != cudaSuccess) {
@@ -457,17 +484,37 @@ cudaError_t launch_one(const GemvArgs &args, int grid, size_t smem, cudaStream_t
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs                                          = attr;
   cfg.numAttrs                                       = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, args);
+  return cudaLaunchKernelEx(&cfg, kern, args, wmap);
 }
 
 template <int WT, bool A16>
-cudaError_t launch_mpad(const GemvArgs &a, int mpad, int grid, size_t smem, cudaStream_t s, bool pdl) {
+cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int grid, size_t smem, cudaStream_t s,
+                        bool pdl) {
   switch (mpad) {
-    case 1: return launch_one<WT, A16, 1>(a, grid, smem, s, pdl);
-    case 2: return launch_one<WT, A16, 2>(a, grid, smem, s, pdl);
-    case 4: return launch_one<WT, A16, 4>(a, grid, smem, s, pdl);
-    default: return launch_one<WT, A16, 8>(a, grid, smem, s, pdl);
+    case 1: return launch_one<WT, A16, 1>(a, wm, grid, smem, s, pdl);
+    case 2: return launch_one<WT, A16, 2>(a, wm, grid, smem, s, pdl);
+    case 4: return launch_one<WT, A16, 4>(a, wm, grid, smem, s, pdl);
+    default: return launch_one<WT, A16, 8>(a, wm, grid, smem, s, pdl);
   }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup (no link against libcuda)
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void                           *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
 }
 
 }  // namespace
@@ -482,12 +529,30 @@ size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
 
 cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                             cudaStream_t stream, bool pdl) {
-  if (wt == kQ4) {
-    return a16 ? launch_mpad<kQ4, true>(args, mpad, grid, smem, stream, pdl)
-               : launch_mpad<kQ4, false>(args, mpad, grid, smem, stream, pdl);
+  // Tensor map over this launch's K range of the weight bytes, as 8-byte elements:
+  // inner dimension = bytes of the K range per row / 8, outer = N rows, row pitch = w_row_bytes.
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    return cudaErrorNotSupported;
   }
-  return a16 ? launch_mpad<kQ8, true>(args, mpad, grid, smem, stream, pdl)
-             : launch_mpad<kQ8, false>(args, mpad, grid, smem, stream, pdl);
+  const int         bb        = wt == kQ4 ? 18 : 34;
+  CUtensorMap       wmap;
+  const cuuint64_t  gdim[2]   = { (cuuint64_t) args.kblocks * bb / 8, (cuuint64_t) args.N };
+  const cuuint64_t  gstride[1] = { (cuuint64_t) args.w_row_bytes };
+  const cuuint32_t  box[2]    = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
+  const cuuint32_t  estr[2]   = { 1, 1 };
+  void             *base      = const_cast<uint8_t *>(args.w) + args.w_k_off_bytes;
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
+      CUDA_SUCCESS) {
+    return cudaErrorInvalidValue;
+  }
+  if (wt == kQ4) {
+    return a16 ? launch_mpad<kQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
+               : launch_mpad<kQ4, false>(args, wmap, mpad, grid, smem, stream, pdl);
+  }
+  return a16 ? launch_mpad<kQ8, true>(args, wmap, mpad, grid, smem, stream, pdl)
+             : launch_mpad<kQ8, false>(args, wmap, mpad, grid, smem, stream, pdl);
 }
 
 }  // namespace htp

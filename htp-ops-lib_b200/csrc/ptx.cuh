@@ -82,6 +82,22 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
     : "memory");
 }
 
+// 2-D tiled tensor copy global -> this CTA's shared memory through a tensor map (no multicast).
+// x is the coordinate along the innermost dimension in ELEMENTS of the map's data type; x times
+// the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *tmap, int x, int y, uint64_t *bar,
+                                            uint64_t policy) {
+  asm volatile(
+    "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+    "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst_smem)),
+    "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+    : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_descriptor(const void *tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 
 __device__ __forceinline__ void pdl_wait_prior_grids() {
@@ -99,6 +115,14 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
     "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
     : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
     : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// same, with a zero accumulator input: c = a * b
+__device__ __forceinline__ void mma_16816_zero(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+    "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+    : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+    : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
