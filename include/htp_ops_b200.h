@@ -37,6 +37,26 @@ int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int 
                      int act_type, void *stream);
 
 /*
+ * The decode mat-vec (m <= 8) for callers that must not allocate device memory once they are
+ * running - a server that has handed all of device memory to its own pools, or a decode loop that
+ * cannot take the device-wide synchronisation an allocation implies.  Same arguments, checks and
+ * results as htp_b200_mul_mat, but the kernel's scratch is a static device array inside the
+ * library (about 0.4 MB per GPU, held until the process exits) and the call makes no cudaMalloc,
+ * cudaFree or other allocating call.  No counterpart in the reference.
+ *   - Range: m <= 8, k % 256 == 0, and the activation fragments of the whole k must fit in one
+ *     launch's shared memory (always true for k <= 4096; for fp32 activations k = 14336 fits up to
+ *     m = 2, for fp16 activations up to m = 4).  Outside it the call prints the reason to stderr and returns -3.
+ *   - All calls on a device share the one array, which keeps the previous call's contents; what
+ *     must start at zero is cleared on `stream` at the start of each call.  Calls that overlap on
+ *     the GPU (two streams, two threads) race on it: keep them ordered, e.g. on one stream.
+ *   - The first call on each device resolves the array's device address; make that call during
+ *     set-up, before any stream capture.
+ *   - A bounded wait that runs out inside the kernel is not reported by this entry point.
+ */
+int htp_b200_mul_mat_static_scratch(void *dst, const void *activation, const void *weight, int m, int k, int n,
+                                    int weight_type, int act_type, void *stream);
+
+/*
  * Integer probe of the block unpack: for each of n_blocks consecutive blocks writes
  * s[b] = sum_i v_i and t[b] = sum_i (i + 1) * v_i (int32), v_i the block's 32 integer values in
  * element order.  No counterpart in the reference (it has no integer path); exists so the
