@@ -9,12 +9,15 @@
 
 #include "aux_kernels.h"
 #include "device_ctx.h"
+#include "gemm_tcgen05.h"
 #include "gemv_mma.h"
 
 namespace htp {
 
 int g_opt_pdl           = 1;
 int g_opt_force_generic = 0;
+int g_opt_gemm_min_m     = 64;
+int g_opt_gemm_tile_n    = 0;   // 0 = choose 224 or 256 weight rows per tile by wave count; else force  // fp16 activations with at least this many tokens go to the tensor-core GEMM
 
 namespace {
 std::mutex                                            g_mu;
@@ -209,6 +212,22 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     count_launch();
     return 0;
   }
+  if (a16 && m >= g_opt_gemm_min_m) {
+    // prefill: tensor-core GEMM
+    StreamScratch *sc = stream_scratch(ctx, st);
+    if (!sc) {
+      return -2;
+    }
+    GemmArgs a = {};
+    a.y = static_cast<float *>(dst), a.x = activation, a.w = static_cast<const uint8_t *>(weight);
+    a.M = m, a.N = n, a.K = k, a.err = sc->err;
+    if (gemm_tcgen05_launch(a, wt, ctx->sm_count, st) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    count_launch();
+    return 0;
+  }
   return run_gemv(ctx, static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n, wt, a16,
                   st, allow_pdl && g_opt_pdl != 0);
 }
@@ -283,6 +302,13 @@ int htp_b200_set_option(const char *name, int value) {
     slot = &g_opt_pdl;
   } else if (!strcmp(name, "force_generic")) {
     slot = &g_opt_force_generic;
+  } else if (!strcmp(name, "gemm_min_m")) {
+    slot = &g_opt_gemm_min_m;
+  } else if (!strcmp(name, "gemm_tile_n")) {
+    if (value != 0 && value != 224 && value != 256) {
+      return -1;
+    }
+    slot = &g_opt_gemm_tile_n;
   }
   if (!slot) {
     return -1;

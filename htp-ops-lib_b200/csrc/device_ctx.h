@@ -35,6 +35,8 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
 
 extern int      g_opt_pdl;
 extern int      g_opt_force_generic;
+extern int      g_opt_gemm_min_m;
+extern int      g_opt_gemm_tile_n;
 void            count_launch(int n = 1);
 
 }  // namespace htp

@@ -1,0 +1,24 @@
+// Launch interface of the prefill-side GEMM (gemm_tcgen05.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace htp {
+
+constexpr int kGemmErrProducer = 201;
+constexpr int kGemmErrMma      = 202;
+constexpr int kGemmErrEpilogue = 203;
+constexpr int kGemmErrDequant  = 204;
+
+struct GemmArgs {
+  float         *y;  // [M][N] fp32
+  const void    *x;  // [M][K] fp16
+  const uint8_t *w;  // N rows of K/32 blocks
+  int            M, N, K;  // K a multiple of 256, N a multiple of 32
+  int           *err;      // first error code, 0 when none
+};
+
+cudaError_t gemm_tcgen05_launch(const GemmArgs &args, int wt, int sm_count, cudaStream_t stream);
+
+}  // namespace htp

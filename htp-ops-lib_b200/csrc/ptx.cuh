@@ -44,7 +44,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 
 // Bounded wait.  try_wait itself blocks for a hardware-defined slice, so the cap below is
 // far beyond any legitimate latency (seconds) yet finite.
-constexpr uint32_t kWaitCap = 1u << 22;
+constexpr uint32_t kWaitCap = 1u << 20;
 
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   for (uint32_t i = 0; i < kWaitCap; ++i) {

@@ -1,0 +1,64 @@
+"""GPU parity of the prefill GEMM (tcgen05 / TMEM): fp16 activations, M >= 64, against the fp64
+oracle.  Gate: max|y - o| / max|o| <= 1e-3 (weights are rounded to fp16 once, as the reference's
+dequantisation does, accumulation is fp32)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def run(dev, oracle, wl, wtype, m, k, n, seed=0, tol=1e-3):
+    wq, x = wl.random_case(900 + seed, wtype, True, m, k, n)
+    before = dev.lib.htp_b200_launch_count()
+    y = dev.matmul(x, wq, n, wtype)
+    assert dev.lib.htp_b200_launch_count() == before + 1  # one GEMM launch, not token slices
+    ref, absdot = oracle.mul_mat_f64(x, wq, n, wtype, want_absdot=True)
+    e = oracle.error_metrics(y, ref, absdot)
+    assert np.isfinite(y).all()
+    assert e["max_rel_to_max"] <= tol and e["max_cond_rel"] <= tol, e
+    return y
+
+
+@pytest.mark.parametrize("wtype", [2, 8])
+@pytest.mark.parametrize("m,k,n", [(128, 256, 256), (64, 256, 32), (128, 512, 224), (200, 1024, 480),
+                                   (512, 2048, 1024), (65, 768, 96), (384, 4096, 2240)])
+def test_gemm_shapes(dev, oracle, wl, wtype, m, k, n):
+    """Full and ragged tiles in M and N, one and many K steps, more tiles than one wave has."""
+    run(dev, oracle, wl, wtype, m, k, n)
+
+
+@pytest.mark.parametrize("wtype", [2, 8])
+@pytest.mark.parametrize("tile_n", [224, 256])
+def test_gemm_many_tiles_per_cta(dev, oracle, wl, wtype, tile_n):
+    """More tiles than SMs, so every CTA walks several tiles back to back with its rings full -
+    the regime in which a raw-weight stage released too early was overwritten while still being
+    read.  Three runs must agree bit for bit and match the oracle."""
+    lib = dev.lib
+    assert lib.htp_b200_set_option(b"gemm_tile_n", tile_n) == 0
+    try:
+        ys = [run(dev, oracle, wl, wtype, 128, 1024, tile_n * 300, seed=9) for _ in range(3)]
+    finally:
+        lib.htp_b200_set_option(b"gemm_tile_n", 0)
+    assert (ys[0] == ys[1]).all() and (ys[0] == ys[2]).all()
+
+
+def test_gemm_is_deterministic(dev, oracle, wl):
+    a = run(dev, oracle, wl, 2, 256, 1024, 512, seed=3)
+    b = run(dev, oracle, wl, 2, 256, 1024, 512, seed=3)
+    assert (a == b).all()
+
+
+def test_gemm_matches_decode_kernel(dev, wl):
+    """The same product through the decode kernel (token slices, exact integer weights) and the
+    GEMM (fp16-rounded weights) agrees to the fp16 rounding of the weights."""
+    lib = dev.lib
+    wq, x = wl.random_case(77, 8, True, 128, 1024, 256)
+    y_gemm = dev.matmul(x, wq, 256, 8)
+    assert lib.htp_b200_set_option(b"gemm_min_m", 1 << 30) == 64
+    try:
+        y_gemv = dev.matmul(x, wq, 256, 8)
+    finally:
+        lib.htp_b200_set_option(b"gemm_min_m", 64)
+    assert np.abs(y_gemm - y_gemv).max() <= 1e-3 * np.abs(y_gemv).max()
