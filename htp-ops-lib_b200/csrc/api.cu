@@ -17,7 +17,7 @@ namespace htp {
 int g_opt_pdl           = 1;
 int g_opt_force_generic = 0;
 int g_opt_gemm_min_m     = 64;
-int g_opt_gemm_tile_n    = 0;   // 0 = choose 224 or 256 weight rows per tile by wave count; else force  // fp16 activations with at least this many tokens go to the tensor-core GEMM
+int g_opt_gemm_tile_n    = 0;   // tokens per GEMM tile: 0 = by M, else 128 or 256  // fp16 activations with at least this many tokens go to the tensor-core GEMM
 
 namespace {
 std::mutex                                            g_mu;
@@ -305,7 +305,7 @@ int htp_b200_set_option(const char *name, int value) {
   } else if (!strcmp(name, "gemm_min_m")) {
     slot = &g_opt_gemm_min_m;
   } else if (!strcmp(name, "gemm_tile_n")) {
-    if (value != 0 && value != 224 && value != 256) {
+    if (value != 0 && value != 128 && value != 256) {
       return -1;
     }
     slot = &g_opt_gemm_tile_n;

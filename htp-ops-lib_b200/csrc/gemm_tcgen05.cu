@@ -5,19 +5,28 @@
 // 928-1005).  Like the reference the weights are dequantised to fp16, value * scale rounded once
 // (mat_mul.c:290, 304); unlike it the accumulator and the output stay fp32.
 //
-// One persistent CTA per SM, tile = 128 tokens x BN weight rows, K in steps of 64:
-//   warp 0      TMA producer: the activation tile (128 x 64 fp16, 128-byte swizzle) per K step and
-//               the RAW weight bytes (BN rows x 256 weights = 144 / 272 bytes per row) per 4 K steps
-//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M = 128, N = BN,
-//               K = 16) four times per K step, operands through shared-memory descriptors
-//   warp 2      TMEM allocation (512 columns = two BN-column accumulators)
-//   warps 4-7   epilogue: tcgen05.ld of an accumulator, fp32 stores to y (row-major)
-//   warps 8-15  dequantisation: thread r owns weight row r of the tile; 9 / 17 conflict-free 16-byte
-//               loads bring its 256 raw weights into registers, then per K step it writes 64 fp16
-//               values as eight 16-byte chunks into the K-major SWIZZLE_128B operand tile
-// Two accumulators let the epilogue of one tile overlap the main loop of the next.  All waits are
-// bounded; a wait that runs out records an error code, raises the CTA's abort flag and every role
-// leaves its loop; TMEM is freed before the CTA exits.  No cluster launch, no multicast.
+// The product is computed transposed, D[weight row][token] = W . x^T, so that the dequantised
+// weights are the MMA's A operand and can live in TENSOR MEMORY: the dequantisation warps write
+// their fp16 values straight into TMEM with tcgen05.st and the MMA reads them from there
+// (tcgen05.mma with A in TMEM, B = the activation tile in shared memory).  Compared with putting
+// the dequantised tile in shared memory this removes the 128-byte-swizzled stores, the proxy
+// fences and two thirds of the shared-memory traffic per K step, which is what bounds a
+// one-CTA UMMA pipeline.
+//
+// One persistent CTA per SM, tile = 128 weight rows x BT tokens (BT = 256, or 128 for M <= 128),
+// K in steps of 64:
+//   warp 0      TMA producer: the activation tile (BT x 64 fp16, 128-byte swizzle) per K step and
+//               the RAW weight bytes (128 rows x 256 weights = 144 / 272 bytes per row) per 4 K steps
+//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M = 128 weight
+//               rows, N = BT tokens, K = 16) four times per K step
+//   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 an 8-stage ring of A tiles
+//   warps 4-7   epilogue: tcgen05.ld of the accumulator, fp32 stores to y[token][weight row]
+//   warps 8-15  dequantisation, two groups of four warps; group g takes the raw stages whose
+//               running index is g (mod 2).  Thread = one weight row: 9 / 17 conflict-free 16-byte
+//               loads bring its 256 raw weights into registers, then per K step it converts 64 of
+//               them to fp16 and stores them as 32 TMEM columns of its lane
+// All waits are bounded; a wait that runs out records an error code, raises the CTA's abort flag
+// and every role leaves its loop; TMEM is freed before the CTA exits.  No cluster, no multicast.
 #include "gemm_tcgen05.h"
 
 #include <cuda.h>
@@ -32,44 +41,41 @@ namespace htp {
 
 namespace {
 
-constexpr int kBM          = 128;  // tokens per tile (UMMA M)
-constexpr int kBK          = 64;   // K per pipeline step: one 128-byte swizzled row of fp16
-constexpr int kKPerRaw     = 256;  // weights per row in one raw stage (a 16-byte aligned period)
-constexpr int kNB          = 3;    // dequantised-weight stages
-constexpr int kMaxNA       = 8;    // activation stages: as many as fit (see GCfg)
-constexpr int kSmemLimit   = 232448;  // opt-in dynamic shared memory per CTA
-constexpr int kThreads     = 512;
-constexpr int kDeqWarp0    = 8;    // first dequantisation warp
-constexpr int kDeqWarps    = 8;
-constexpr int kEpiWarp0    = 4;
-constexpr int kTmemCols    = 512;
+constexpr int kBW        = 128;  // weight rows per tile (UMMA M, the TMEM lanes)
+constexpr int kBK        = 64;   // K per pipeline step: one 128-byte swizzled row of fp16
+constexpr int kKPerRaw   = 256;  // weights per row in one raw stage (a 16-byte aligned period)
+constexpr int kQ         = kKPerRaw / kBK;  // K steps per raw stage
+constexpr int kNAT       = 8;    // A tiles (32 TMEM columns each) in the tensor-memory ring
+constexpr int kThreads   = 512;
+constexpr int kEpiWarp0  = 4;
+constexpr int kDeqWarp0  = 8;    // warps 8-11: group 0, warps 12-15: group 1
+constexpr int kTmemCols  = 512;
+constexpr int kTmemA     = 256;  // first column of the A ring
+constexpr int kMaxNX     = 6;
+constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
 
-struct GSmemBar;
-
-template <int WT, int BN>
+template <int WT, int BT>
 struct GCfg {
-  static constexpr int BB  = BlockTraits<WT>::kBytes;
-  static constexpr int RB  = 8 * BB;  // raw bytes per row and raw stage: 144 / 272
-  static constexpr int NR  = 1;       // raw stages: the bytes move to registers at once, one is enough
-  static constexpr int RW  = RB / 16;  // 16-byte words per row: 9 / 17
-  static constexpr int A_BYTES   = 128 * 128;
-  static constexpr int B_BYTES   = BN * 128;
-  static constexpr int RAW_BYTES = BN * RB;
-  // everything but the activation ring, plus alignment slack and the barrier block
-  static constexpr int FIXED = kNB * B_BYTES + ((NR * RAW_BYTES + 127) & ~127) + 1024 + 512;
-  static constexpr int NA_FIT = (kSmemLimit - FIXED) / A_BYTES;
-  static constexpr int NA     = NA_FIT > kMaxNA ? kMaxNA : NA_FIT;  // 5 / 6 (Q4_0), 3 / 5 (Q8_0) for BN 256 / 224
-  static_assert(NA >= 3, "activation ring too shallow");
+  static constexpr int BB        = BlockTraits<WT>::kBytes;
+  static constexpr int RB        = 8 * BB;   // raw bytes per row and raw stage: 144 / 272
+  static constexpr int RW        = RB / 16;  // 16-byte words per row: 9 / 17
+  static constexpr int X_BYTES   = BT * 128;
+  static constexpr int RAW_BYTES = kBW * RB;
+  static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512;  // raw ring, slack, barriers
+  static constexpr int NX_FIT    = (kSmemLimit - FIXED) / X_BYTES;
+  static constexpr int NX        = NX_FIT > kMaxNX ? kMaxNX : NX_FIT;  // activation stages
+  static_assert(NX >= 3, "activation ring too shallow");
 };
 
 struct GSmemBar {
-  uint64_t a_full[kMaxNA], a_empty[kMaxNA];
-  uint64_t b_full[kNB], b_empty[kNB];
+  uint64_t x_full[kMaxNX], x_empty[kMaxNX];
   uint64_t raw_full[2], raw_empty[2];
-  uint64_t acc_full[2], acc_empty[2];
+  uint64_t at_full[kNAT], at_empty[kNAT];
+  uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
   int      abort_flag;
 };
+static_assert(sizeof(GSmemBar) <= 512, "barrier block");
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 
@@ -90,17 +96,14 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void fence_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                         uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem desc]; issued by ONE thread
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
   asm volatile(
     "{\n\t.reg .pred p;\n\t"
     "setp.ne.b32 p, %4, 0;\n\t"
-    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-    "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+    "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
     : "memory");
 }
 // the mbarrier gets one arrival when every MMA issued so far by this thread has completed
@@ -126,6 +129,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     v[i] = __uint_as_float(r[i]);
   }
 }
+// 32 columns of this thread's TMEM lane <- 32 registers; returns once the store has completed
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&o)[8]) {
+  asm volatile(
+    "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+    "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,"
+    "%30,%31,%32};" ::"r"(taddr),
+    "r"(o[0].x), "r"(o[0].y), "r"(o[0].z), "r"(o[0].w), "r"(o[1].x), "r"(o[1].y), "r"(o[1].z), "r"(o[1].w),
+    "r"(o[2].x), "r"(o[2].y), "r"(o[2].z), "r"(o[2].w), "r"(o[3].x), "r"(o[3].y), "r"(o[3].z), "r"(o[3].w),
+    "r"(o[4].x), "r"(o[4].y), "r"(o[4].z), "r"(o[4].w), "r"(o[5].x), "r"(o[5].y), "r"(o[5].z), "r"(o[5].w),
+    "r"(o[6].x), "r"(o[6].y), "r"(o[6].z), "r"(o[6].w), "r"(o[7].x), "r"(o[7].y), "r"(o[7].z), "r"(o[7].w)
+    : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
 // K-major, 128-byte swizzled operand tile: rows of 128 bytes, 8-row atoms of 1024 bytes.
 __device__ __forceinline__ uint64_t smem_desc_sw128(const void *tile) {
@@ -137,7 +153,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void *tile) {
 
 // c = fp32, a = b = fp16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
 __host__ __device__ constexpr uint32_t instr_desc_f16(int n) {
-  return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kBM >> 4) << 24);
+  return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kBW >> 4) << 24);
 }
 
 // Bounded wait that also gives up when another role has raised the abort flag.  The hand-offs
@@ -226,44 +242,42 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw /* words 
 
 // ---------------------------------------------------------------- the kernel
 
-template <int WT, int BN>
+template <int WT, int BT>
 __global__ void __launch_bounds__(kThreads, 1)
   gemm_tcgen05_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap,
                       const __grid_constant__ CUtensorMap wmap) {
-  using C = GCfg<WT, BN>;
-  static_assert(BN % 32 == 0 && BN <= 256 && 2 * BN <= kTmemCols, "tile width");
-  static_assert(sizeof(GSmemBar) <= 512, "barrier block");
-  constexpr int      kNA       = C::NA;
-  constexpr int      A_BYTES   = C::A_BYTES;
-  constexpr int      B_BYTES   = C::B_BYTES;
+  using C = GCfg<WT, BT>;
+  static_assert(BT == 128 || BT == 256, "token tile");
+  constexpr int      NX        = C::NX;
+  constexpr int      X_BYTES   = C::X_BYTES;
   constexpr int      RAW_BYTES = C::RAW_BYTES;
-  constexpr uint32_t IDESC     = instr_desc_f16(BN);
+  constexpr int      RAW_PITCH = (RAW_BYTES + 127) & ~127;
+  constexpr uint32_t IDESC     = instr_desc_f16(BT);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled operand tiles need 1024-byte alignment in the shared address space
-  uint8_t  *sA   = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint8_t  *sB   = sA + kNA * A_BYTES;
-  uint8_t  *sRaw = sB + kNB * B_BYTES;
-  GSmemBar *bar  = reinterpret_cast<GSmemBar *>(sRaw + ((C::NR * RAW_BYTES + 127) & ~127));
+  uint8_t  *sX   = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t  *sRaw = sX + NX * X_BYTES;
+  GSmemBar *bar  = reinterpret_cast<GSmemBar *>(sRaw + 2 * RAW_PITCH);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int     warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *abort_flag = &bar->abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNA; ++i) {
-      mbar_init(&bar->a_full[i], 1);
-      mbar_init(&bar->a_empty[i], 1);
-    }
-    for (int i = 0; i < kNB; ++i) {
-      mbar_init(&bar->b_full[i], kDeqWarps * 32);
-      mbar_init(&bar->b_empty[i], 1);
+    for (int i = 0; i < NX; ++i) {
+      mbar_init(&bar->x_full[i], 1);
+      mbar_init(&bar->x_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar->raw_full[i], 1);
-      mbar_init(&bar->raw_empty[i], kDeqWarps);
-      mbar_init(&bar->acc_full[i], 1);
-      mbar_init(&bar->acc_empty[i], 4);
+      mbar_init(&bar->raw_empty[i], 4);  // the four warps of the group that reads the stage
     }
+    for (int i = 0; i < kNAT; ++i) {
+      mbar_init(&bar->at_full[i], 128);  // every thread of the writing group
+      mbar_init(&bar->at_empty[i], 1);
+    }
+    mbar_init(&bar->acc_full, 1);
+    mbar_init(&bar->acc_empty, 4);
     bar->abort_flag = 0;
     mbar_fence_init();
   }
@@ -276,9 +290,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = bar->tmem_base;
 
-  const int m_tiles = (p.M + kBM - 1) / kBM;
-  const int n_tiles = (p.N + BN - 1) / BN;
-  const int tiles   = m_tiles * n_tiles;
+  const int t_tiles = (p.M + BT - 1) / BT;          // token tiles
+  const int w_tiles = (p.N + kBW - 1) / kBW;        // weight-row tiles
+  const int tiles   = t_tiles * w_tiles;
   const int k_raws  = p.K / kKPerRaw;
 
   if (warp == 0) {
@@ -286,29 +300,28 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       tma_prefetch_descriptor(&xmap);
       tma_prefetch_descriptor(&wmap);
-      const uint64_t pol_w = l2_policy_evict_last();   // a weight panel is re-read by the other token tiles
-      const uint64_t pol_x = l2_policy_evict_last();
-      Ring           ra(kNA), rr(C::NR);
+      const uint64_t pol = l2_policy_evict_last();  // both operands are re-read by other tiles
+      Ring           rx(NX);
+      unsigned       gs = 0;  // running raw-stage index of this CTA
       bool           ok = true;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int n0 = (t / m_tiles) * BN, m0 = (t % m_tiles) * kBM;
-        for (int rs = 0; rs < k_raws && ok; ++rs) {
-          ok = wait_or_abort(&bar->raw_empty[rr.slot], rr.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
+        const int n0 = (t / t_tiles) * kBW, m0 = (t % t_tiles) * BT;
+        for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
+          const int g = gs & 1;
+          ok = wait_or_abort(&bar->raw_empty[g], ((gs >> 1) & 1) ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
             break;
           }
-          mbar_arrive_expect_tx(&bar->raw_full[rr.slot], RAW_BYTES);
-          tma_load_2d(sRaw + rr.slot * RAW_BYTES, &wmap, rs * (C::RB / 8), n0, &bar->raw_full[rr.slot], pol_w);
-          rr.next();
-          for (int q = 0; q < kKPerRaw / kBK; ++q) {
-            ok = wait_or_abort(&bar->a_empty[ra.slot], ra.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
+          mbar_arrive_expect_tx(&bar->raw_full[g], RAW_BYTES);
+          tma_load_2d(sRaw + g * RAW_PITCH, &wmap, rs * (C::RB / 8), n0, &bar->raw_full[g], pol);
+          for (int q = 0; q < kQ; ++q) {
+            ok = wait_or_abort(&bar->x_empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
             if (!ok) {
               break;
             }
-            mbar_arrive_expect_tx(&bar->a_full[ra.slot], A_BYTES);
-            tma_load_2d(sA + ra.slot * A_BYTES, &xmap, (rs * (kKPerRaw / kBK) + q) * kBK, m0, &bar->a_full[ra.slot],
-                        pol_x);
-            ra.next();
+            mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
+            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, (rs * kQ + q) * kBK, m0, &bar->x_full[rx.slot], pol);
+            rx.next();
           }
         }
       }
@@ -316,141 +329,138 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ---------------- MMA issuer
     if (lane == 0) {
-      Ring ra(kNA), rb(kNB);
-      int  it = 0;
-      bool ok = true;
+      Ring     rx(NX);
+      unsigned gs = 0;
+      int      it = 0;
+      bool     ok = true;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-        const int buf = it & 1, use = it >> 1;
-        ok = wait_or_abort(&bar->acc_empty[buf], (use & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
+        // the single accumulator must have been read out by the epilogue of the previous tile
+        ok = wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
         if (!ok) {
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t) buf * BN;
-        const int      k_steps = p.K / kBK;
-        for (int kb = 0; kb < k_steps; ++kb) {
-          ok = wait_or_abort(&bar->a_full[ra.slot], ra.phase, abort_flag, p.err, kGemmErrMma) &&
-               wait_or_abort(&bar->b_full[rb.slot], rb.phase, abort_flag, p.err, kGemmErrMma);
-          if (!ok) {
-            break;
-          }
-          tc_fence_after();
-          const uint64_t adesc = smem_desc_sw128(sA + ra.slot * A_BYTES);
-          const uint64_t bdesc = smem_desc_sw128(sB + rb.slot * B_BYTES);
+        for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
+          const int g = gs & 1, gph = (gs >> 1) & 1;
+          for (int q = 0; q < kQ; ++q) {
+            const int slot = g * kQ + q;
+            ok = wait_or_abort(&bar->x_full[rx.slot], rx.phase, abort_flag, p.err, kGemmErrMma) &&
+                 wait_or_abort(&bar->at_full[slot], gph, abort_flag, p.err, kGemmErrMma);
+            if (!ok) {
+              break;
+            }
+            tc_fence_after();
+            const uint64_t bdesc  = smem_desc_sw128(sX + rx.slot * X_BYTES);
+            const uint32_t a_tmem = tmem_base + kTmemA + slot * 32;
 #pragma unroll
-          for (int s = 0; s < kBK / 16; ++s) {
-            // 16 fp16 = 32 bytes along K inside the swizzled row: +2 in the descriptor's 16-byte units
-            umma_f16(d_tmem, adesc + 2 * s, bdesc + 2 * s, IDESC, (kb | s) ? 1u : 0u);
+            for (int s = 0; s < kBK / 16; ++s) {
+              // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
+              umma_f16_ts(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
+            }
+            umma_commit(&bar->x_empty[rx.slot]);
+            umma_commit(&bar->at_empty[slot]);
+            rx.next();
           }
-          umma_commit(&bar->a_empty[ra.slot]);
-          umma_commit(&bar->b_empty[rb.slot]);
-          ra.next();
-          rb.next();
         }
         if (ok) {
-          umma_commit(&bar->acc_full[buf]);
+          umma_commit(&bar->acc_full);
         }
       }
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
-    // ---------------- epilogue: TMEM -> registers -> y
+    // ---------------- epilogue: TMEM -> registers -> y[token][weight row]
     const int q4 = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     int       it = 0;
     bool      ok = true;
     for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-      const int buf = it & 1, use = it >> 1;
-      const int n0 = (t / m_tiles) * BN, m0 = (t % m_tiles) * kBM;
-      ok = wait_or_abort(&bar->acc_full[buf], use & 1, abort_flag, p.err, kGemmErrEpilogue);
+      const int n0 = (t / t_tiles) * kBW, m0 = (t % t_tiles) * BT;
+      ok = wait_or_abort(&bar->acc_full, it & 1, abort_flag, p.err, kGemmErrEpilogue);
       if (!ok) {
         break;
       }
       tc_fence_after();
-      const int      row   = m0 + q4 * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t) (q4 * 32) << 16) + (uint32_t) buf * BN;
+      const int      col   = n0 + q4 * 32 + lane;  // this thread's output column (weight row)
+      const uint32_t taddr = tmem_base + ((uint32_t) (q4 * 32) << 16);
+      const bool     col_ok = n0 + q4 * 32 < p.N;  // N is a multiple of 32: a warp is in or out
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        if (m0 + c0 >= p.M) {
+          break;
+        }
         float v[32];
         tmem_ld32(taddr + c0, v);
-        if (row < p.M && n0 + c0 < p.N) {  // N is a multiple of 32: a 32-column group is in or out
-          float4 *dst = reinterpret_cast<float4 *>(p.y + (long long) row * p.N + n0 + c0);
+        if (col_ok) {
+          float *dst = p.y + (long long) (m0 + c0) * p.N + col;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          for (int i = 0; i < 32; ++i) {
+            if (m0 + c0 + i < p.M) {
+              dst[(long long) i * p.N] = v[i];  // one 128-byte row segment per warp and token
+            }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bar->acc_empty[buf]);
+        mbar_arrive(&bar->acc_empty);
       }
     }
   } else if (warp >= kDeqWarp0) {
-    // ---------------- dequantisation: thread r owns weight row r of the tile
-    const int r = (warp - kDeqWarp0) * 32 + lane;
-    Ring      rr(C::NR), rb(kNB);
-    bool      ok = true;
-    {
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        for (int rs = 0; rs < k_raws && ok; ++rs) {
-          ok = wait_or_abort(&bar->raw_full[rr.slot], rr.phase, abort_flag, p.err, kGemmErrDequant);
+    // ---------------- dequantisation: group g, thread = weight row r of the tile
+    const int      g     = (warp - kDeqWarp0) >> 2;
+    const int      r     = (warp & 3) * 32 + lane;
+    const uint32_t tlane = tmem_base + kTmemA + ((uint32_t) ((warp & 3) * 32) << 16);
+    unsigned       gs    = 0;
+    bool           ok    = true;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
+        if ((int) (gs & 1) != g) {
+          continue;
+        }
+        const int gph = (gs >> 1) & 1;
+        ok = wait_or_abort(&bar->raw_full[g], gph, abort_flag, p.err, kGemmErrDequant);
+        if (!ok) {
+          break;
+        }
+        // The row's 144 / 272 raw bytes go to registers with 16-byte loads, LAST chunk first.  The
+        // stage is handed back to the TMA producer as soon as possible, but only after the loads
+        // have RETURNED: an mbarrier arrive does not wait for the thread's outstanding shared-memory
+        // loads (releasing right behind them let the next TMA copy overwrite the chunk loaded
+        // last).  Chunk 0 is therefore loaded last and consumed first, loads of one thread return
+        // in order, and the release follows that first use.
+        uint32_t raw[C::RW * 4 + 1];
+        {
+          const uint32_t src = smem_u32(sRaw + g * RAW_PITCH + r * C::RB);
+#pragma unroll
+          for (int i = C::RW - 1; i >= 0; --i) {
+            asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
+                         : "r"(src + 16 * i)
+                         : "memory");
+          }
+        }
+        raw[C::RW * 4] = 0;  // the word past the end is only ever the unused half of a byte_perm
+        // the fp16 values of a K step are computed before waiting for their TMEM slot
+        uint4 out[8];
+        dequant_two_blocks<WT>(raw, 0, out);
+        asm volatile("fence.acq_rel.cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bar->raw_empty[g]);
+        }
+#pragma unroll
+        for (int q = 0; q < kQ; ++q) {
+          const int slot = g * kQ + q;
+          ok = wait_or_abort(&bar->at_empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
           if (!ok) {
             break;
           }
-          // The row's 144 / 272 raw bytes go to registers with 16-byte loads, LAST chunk first.  The
-          // stage is handed back to the TMA producer as soon as possible, but only after the loads
-          // have RETURNED: issuing the release right behind the loads was observed to let the next
-          // TMA copy overwrite the chunk loaded last before it was read (an mbarrier arrive does not
-          // wait for this thread's outstanding shared-memory loads).  Chunk 0 is therefore loaded
-          // last and consumed first (the first K step needs it), loads of one thread return in
-          // order, and the release follows that first use.
-          uint32_t raw[C::RW * 4 + 1];
-          if (r < BN) {
-            const uint32_t src = smem_u32(sRaw + rr.slot * RAW_BYTES + r * C::RB);
-#pragma unroll
-            for (int i = C::RW - 1; i >= 0; --i) {
-              asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
-                           : "r"(src + 16 * i)
-                           : "memory");
-            }
-          }
-          raw[C::RW * 4]     = 0;  // the word past the end is only ever the unused half of a byte_perm
-          const int raw_slot = rr.slot;
-          rr.next();
-          // The fp16 values of a K step are computed BEFORE waiting for its operand stage to be
-          // free, so the arithmetic overlaps the tensor core's work on the previous steps.
-          uint4 out[8];
-          if (r < BN) {
-            dequant_two_blocks<WT>(raw, 0, out);
-          }
-          // `out` was computed from chunk 0, the load issued last: every raw load has returned
-          asm volatile("fence.acq_rel.cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            mbar_arrive(&bar->raw_empty[raw_slot]);
-          }
-#pragma unroll
-          for (int q = 0; q < kKPerRaw / kBK; ++q) {
-            ok = wait_or_abort(&bar->b_empty[rb.slot], rb.phase ^ 1, abort_flag, p.err, kGemmErrDequant);
-            if (!ok) {
-              break;
-            }
-            if (r < BN) {
-              uint8_t *row = sB + rb.slot * B_BYTES + r * 128;
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                *reinterpret_cast<uint4 *>(row + ((c ^ (r & 7)) << 4)) = out[c];
-              }
-            }
-            // every thread orders its own generic-proxy stores before the tensor core's async-proxy
-            // reads, then arrives itself
-            fence_async_smem();
-            mbar_arrive(&bar->b_full[rb.slot]);
-            rb.next();
-            if (q + 1 < kKPerRaw / kBK && r < BN) {
-              dequant_two_blocks<WT>(raw, q + 1, out);
-            }
+          tc_fence_after();
+          tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
+          tc_fence_before();
+          mbar_arrive(&bar->at_full[slot]);
+          if (q + 1 < kQ) {
+            dequant_two_blocks<WT>(raw, q + 1, out);
           }
         }
       }
@@ -484,9 +494,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int WT, int BN>
+template <int WT, int BT>
 cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
-  using C = GCfg<WT, BN>;
+  using C = GCfg<WT, BT>;
   EncodeTiledFn enc = encode_fn();
   if (!enc) {
     return cudaErrorNotSupported;
@@ -495,7 +505,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   {
     const cuuint64_t gdim[2] = { (cuuint64_t) a.K, (cuuint64_t) a.M };
     const cuuint64_t gstr[1] = { (cuuint64_t) a.K * 2 };
-    const cuuint32_t box[2]  = { kBK, kBM };
+    const cuuint32_t box[2]  = { kBK, BT };
     const cuuint32_t es[2]   = { 1, 1 };
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstr, box, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -507,7 +517,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
     const cuuint64_t row_bytes = (cuuint64_t) (a.K / 32) * C::BB;
     const cuuint64_t gdim[2]   = { row_bytes / 8, (cuuint64_t) a.N };
     const cuuint64_t gstr[1]   = { row_bytes };
-    const cuuint32_t box[2]    = { C::RB / 8, BN };
+    const cuuint32_t box[2]    = { C::RB / 8, kBW };
     const cuuint32_t es[2]     = { 1, 1 };
     if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstr, box, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -515,14 +525,13 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
       return cudaErrorInvalidValue;
     }
   }
-  const size_t smem = (size_t) C::NA * C::A_BYTES + C::FIXED;
-  auto         kern = gemm_tcgen05_kernel<WT, BN>;
+  const size_t smem = (size_t) C::NX * C::X_BYTES + C::FIXED;
+  auto         kern = gemm_tcgen05_kernel<WT, BT>;
   cudaError_t  e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
   if (e != cudaSuccess) {
     return e;
   }
-  const int m_tiles = (a.M + kBM - 1) / kBM, n_tiles = (a.N + BN - 1) / BN;
-  int       grid    = m_tiles * n_tiles;
+  int grid = ((a.M + BT - 1) / BT) * ((a.N + kBW - 1) / kBW);
   if (grid > sm_count) {
     grid = sm_count;
   }
@@ -533,21 +542,12 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t gemm_tcgen05_launch(const GemmArgs &args, int wt, int sm_count, cudaStream_t stream) {
-  // 224-column tiles give 256 tiles for N = 14336, M = 512 (1.73 waves) where 256 columns give 224
-  // tiles (1.51 waves, the second half empty); otherwise the widest tile.
-  const int  m_tiles = (args.M + kBM - 1) / kBM;
-  const auto waves   = [&](int bn) {
-    const long tiles = (long) m_tiles * ((args.N + bn - 1) / bn);
-    const long full  = (tiles + sm_count - 1) / sm_count;
-    return (double) tiles * bn / ((double) full * sm_count * bn) * (bn / 256.0 * 0.1 + 0.9);
-  };
-  const bool use224 = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 224 : waves(224) > waves(256);
+  // token tile: 256 columns of the accumulator, or 128 when there are no more tokens than that
+  const bool bt128 = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
   if (wt == kQ4) {
-    return use224 ? launch<kQ4, 224>(args, sm_count, stream) : launch<kQ4, 256>(args, sm_count, stream);
+    return bt128 ? launch<kQ4, 128>(args, sm_count, stream) : launch<kQ4, 256>(args, sm_count, stream);
   }
-  // Q8_0: the 272-byte raw rows leave room for only three activation stages beside a 256-row tile
-  const bool q8_224 = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 224 : true;
-  return q8_224 ? launch<kQ8, 224>(args, sm_count, stream) : launch<kQ8, 256>(args, sm_count, stream);
+  return bt128 ? launch<kQ8, 128>(args, sm_count, stream) : launch<kQ8, 256>(args, sm_count, stream);
 }
 
 }  // namespace htp

@@ -75,7 +75,7 @@ int htp_b200_stream_status(void *stream);
 /* Tuning / debugging switches: "pdl" (programmatic dependent launch, default 1),
  * "force_generic" (route every matmul to the shape-agnostic kernel, default 0), "gemm_min_m"
  * (fp16-activation matmuls with at least this many tokens use the tensor-core GEMM, default 64),
- * "gemm_tile_n" (weight rows per GEMM tile: 0 = automatic, 224 or 256).  Returns the previous value,
+ * "gemm_tile_n" (tokens per GEMM tile: 0 = automatic, 128 or 256).  Returns the previous value,
  * or -1 for an unknown name. */
 int htp_b200_set_option(const char *name, int value);
 
