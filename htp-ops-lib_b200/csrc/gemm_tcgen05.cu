@@ -15,8 +15,9 @@
 //
 // One persistent CTA per SM, tile = 128 weight rows x BT tokens (BT = 256, or 128 for M <= 128),
 // K in steps of 64:
-//   warp 0      TMA producer: the activation tile (BT x 64 fp16, 128-byte swizzle) per K step and
-//               the RAW weight bytes (128 rows x 256 weights = 144 / 272 bytes per row) per 4 K steps
+//   warp 0      TMA producer of the activation tile (BT x 64 fp16, 128-byte swizzle), one per K step
+//   warp 3      TMA producer of the RAW weight bytes (128 rows x 256 weights = 144 / 272 bytes per
+//               row), one per 4 K steps
 //   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M = 128 weight
 //               rows, N = BT tokens, K = 16) four times per K step
 //   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 an 8-stage ring of A tiles
@@ -296,17 +297,36 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int k_raws  = p.K / kKPerRaw;
 
   if (warp == 0) {
-    // ---------------- TMA producer
+    // ---------------- TMA producer of the activation tiles
     if (lane == 0) {
       tma_prefetch_descriptor(&xmap);
-      tma_prefetch_descriptor(&wmap);
-      const uint64_t pol = l2_policy_evict_last();  // both operands are re-read by other tiles
+      const uint64_t pol = l2_policy_evict_last();  // re-read by the other weight-row tiles
       Ring           rx(NX);
-      unsigned       gs = 0;  // running raw-stage index of this CTA
       bool           ok = true;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int n0 = (t / t_tiles) * kBW, m0 = (t % t_tiles) * BT;
-        for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
+        const int m0 = (t % t_tiles) * BT;
+        for (int kb = 0; kb < k_raws * kQ; ++kb) {
+          ok = wait_or_abort(&bar->x_empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
+          if (!ok) {
+            break;
+          }
+          mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
+          tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+          rx.next();
+        }
+      }
+    }
+  } else if (warp == 3) {
+    // ---------------- TMA producer of the raw weight bytes: its own thread, so that a raw stage is
+    // requested the moment its buffer is released and never queues behind activation loads
+    if (lane == 0) {
+      tma_prefetch_descriptor(&wmap);
+      const uint64_t pol = l2_policy_evict_last();  // re-read by the other token tiles
+      unsigned       gs  = 0;                       // running raw-stage index of this CTA
+      bool           ok  = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int n0 = (t / t_tiles) * kBW;
+        for (int rs = 0; rs < k_raws; ++rs, ++gs) {
           const int g = gs & 1;
           ok = wait_or_abort(&bar->raw_empty[g], ((gs >> 1) & 1) ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
@@ -314,15 +334,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           mbar_arrive_expect_tx(&bar->raw_full[g], RAW_BYTES);
           tma_load_2d(sRaw + g * RAW_PITCH, &wmap, rs * (C::RB / 8), n0, &bar->raw_full[g], pol);
-          for (int q = 0; q < kQ; ++q) {
-            ok = wait_or_abort(&bar->x_empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
-            if (!ok) {
-              break;
-            }
-            mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
-            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, (rs * kQ + q) * kBK, m0, &bar->x_full[rx.slot], pol);
-            rx.next();
-          }
         }
       }
     }
