@@ -301,7 +301,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     peaks = read_peaks()
     steps, warm = args.steps, max(3, args.warmup)
 
@@ -340,17 +341,21 @@ def run_ours(args):
     barrier()
     l0 = lib.htp_b200_launch_count()
     with ClockSampler(local) as clk:
-        # repeat the timed region until it is long enough for nvidia-smi to see it (>= ~0.5 s)
-        reps, ms_total, k_total = 0, 0.0, 0
-        while True:
+        # The first region is the reported one (EXACTLY `steps` steps).  It is then repeated so that
+        # the whole lasts long enough (~0.5 s) for nvidia-smi to sample clocks under load; the number
+        # of repeats is agreed between the ranks (max over ranks of the first region's time).
+        barrier()
+        first_ms = time_region(torch, step, steps, stream)
+        first_launches = lib.htp_b200_launch_count() - l0
+        t = torch.tensor([first_ms], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        reps = int(min(400, max(1, 500.0 / max(float(t[0]), 1e-3))))
+        ms_total, k_total = first_ms, steps
+        for _ in range(reps - 1):
             barrier()
             ms_total += time_region(torch, step, steps, stream)
             k_total += steps
-            reps += 1
-            if reps == 1:
-                first_ms, first_launches = ms_total, lib.htp_b200_launch_count() - l0
-            if ms_total >= 500.0 or reps >= 400:
-                break
     barrier()
     assert lib.htp_b200_stream_status(sp) == 0
     t = torch.tensor([first_ms, ms_total / k_total * steps], device=dev, dtype=torch.float64)
