@@ -56,7 +56,8 @@ def read_traffic(key: str):
     """DRAM bytes per launch of the dominant kernel from the committed ncu summary, if any."""
     p = ROOT / "profiles" / "ncu_traffic.json"
     if p.exists():
-        return json.loads(p.read_text()).get(key)
+        e = json.loads(p.read_text()).get(key)
+        return e["bytes_per_launch"] if isinstance(e, dict) else e
     return None
 
 
