@@ -489,8 +489,14 @@ def run_case(args):
         step(i)
     ms = time_region(torch, step, args.steps, stream) / args.steps
     assert lib.htp_b200_stream_status(stream.cuda_stream) == 0
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(i)
+    enqueue_us = (time.perf_counter() - t0) / args.steps * 1e6  # host time to issue one op
+    torch.cuda.synchronize()
     peaks = read_peaks()
-    r = {"case": args.case, "ms": round(ms, 5), "weight_copies": copies,
+    r = {"case": args.case, "ms": round(ms, 5), "host_enqueue_us": round(enqueue_us, 2), "weight_copies": copies,
          "GBps": round(wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9, 1),
          "TFLOPs": round(wl.flops(op, m) / (ms * 1e-3) / 1e12, 2)}
     r["frac_hbm"] = round(r["GBps"] / peaks["hbm_gbs"], 4)

@@ -128,7 +128,7 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       if (nst > kGemvMaxStages) {
         nst = kGemvMaxStages;
       }
-      if (nst >= 4 || (nst >= 2 && chunk_periods == 1)) {
+      if (nst >= 3 || (nst >= 2 && chunk_periods == 1)) {
         break;
       }
       if (chunk_periods == 1) {

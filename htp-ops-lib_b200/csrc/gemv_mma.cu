@@ -32,6 +32,10 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <functional>
+#include <mutex>
+#include <unordered_map>
+
 #include "ptx.cuh"
 #include "unpack.cuh"
 
@@ -66,7 +70,7 @@ struct Smem {
   int      last_flag;
   int      abort_flag;
   int      pad[6];
-  float    red[kConsumerWarps][256];
+  float    red[2][kConsumerWarps][256];  // double-buffered: one barrier per tile completion
 };
 static_assert(sizeof(Smem) % 128 == 0, "keep the regions after the header 128-byte aligned");
 static_assert(sizeof(Smem) == kGemvSmemHeader, "host-side size computation must match");
@@ -244,25 +248,27 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
 
 template <int WT, bool A16, int MPAD>
 __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long long it0, long long it1, int S,
-                           float (&acc)[2][4], int tid) {
+                           float (&acc)[2][4], int tid, int &flush_parity) {
   using C = Cfg<WT, A16, MPAD>;
   const int warp = tid >> 5, lane = tid & 31;
+  // The reduction buffer alternates between two copies, so one barrier per completion suffices:
+  // a warp can only overwrite copy b again after passing the barrier of the completion in between,
+  // which the reducing warps reach only after they have finished reading copy b.
+  float(*red)[256] = sm->red[flush_parity];
+  flush_parity ^= 1;
 #pragma unroll
   for (int rg = 0; rg < 2; ++rg) {
-    *reinterpret_cast<float4 *>(&sm->red[warp][rg * 128 + lane * 4]) =
+    *reinterpret_cast<float4 *>(&red[warp][rg * 128 + lane * 4]) =
       make_float4(acc[rg][0], acc[rg][1], acc[rg][2], acc[rg][3]);
   }
   named_bar_sync(1, kConsumerThreads);
-  float v = 0.f;
-  if (tid < kReduceThreads) {
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; ++w) {
-      v += sm->red[w][tid];
-    }
-  }
-  named_bar_sync(1, kConsumerThreads);  // red may be rewritten by the next flush
   if (tid >= kReduceThreads) {
     return;  // the first eight warps finish the tile
+  }
+  float v = 0.f;
+#pragma unroll
+  for (int w = 0; w < kConsumerWarps; ++w) {
+    v += red[w][tid];
   }
 
   const long long first = tile * S, last = first + S - 1;
@@ -400,6 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     int       st   = (int) (it0 - tile * S);
     int       slot = 0, ph = 0;
     bool      ok   = true;
+    int       flush_parity = 0;
     // lanes whose MMA column is beyond the columns in use read a valid fragment of another column:
     // their output columns are never stored, so what they multiply is irrelevant
     const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
@@ -447,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (++st == S) {
         st = 0;
         if (it + 1 < it1) {
-          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid);
+          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
 #pragma unroll
           for (int rg = 0; rg < 2; ++rg) {
 #pragma unroll
@@ -461,7 +468,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     const long long cur_tile = tile;
     if (ok && it1 > it0) {
-      flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid);
+      flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid, flush_parity);
     }
   }
 }
@@ -469,10 +476,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 template <int WT, bool A16, int MPAD>
 cudaError_t launch_one(const GemvArgs &args, const CUtensorMap &wmap, int grid, size_t smem, cudaStream_t stream,
                        bool pdl) {
-  auto        kern = gemv_mma_kernel<WT, A16, MPAD>;
-  cudaError_t e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
-  if (e != cudaSuccess) {
-    return e;
+  auto kern = gemv_mma_kernel<WT, A16, MPAD>;
+  // the opt-in shared-memory size is set once per device and instantiation, not per launch
+  static bool attr_set[64] = {};
+  int         dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBudget);
+    if (e != cudaSuccess) {
+      return e;
+    }
+    if (dev >= 0 && dev < 64) {
+      attr_set[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3(grid);
@@ -531,21 +547,62 @@ cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, in
                             cudaStream_t stream, bool pdl) {
   // Tensor map over this launch's K range of the weight bytes, as 8-byte elements:
   // inner dimension = bytes of the K range per row / 8, outer = N rows, row pitch = w_row_bytes.
-  EncodeTiledFn enc = encode_tiled_fn();
-  if (!enc) {
-    return cudaErrorNotSupported;
+  // Encoding costs about a microsecond of host time, comparable to a small launch, and a decoder
+  // re-issues the same few hundred weight matrices every token: the maps are cached by what
+  // they describe.
+  struct Key {
+    const void *base;
+    long long   row_bytes;
+    int         kblocks, n, wt, dev;
+    bool operator==(const Key &o) const {
+      return base == o.base && row_bytes == o.row_bytes && kblocks == o.kblocks && n == o.n && wt == o.wt &&
+             dev == o.dev;
+    }
+  };
+  struct KeyHash {
+    size_t operator()(const Key &k) const {
+      size_t h = std::hash<const void *>()(k.base);
+      h ^= std::hash<long long>()(k.row_bytes * 131 + k.kblocks) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+      h ^= std::hash<long long>()(((long long) k.n << 8) ^ (k.wt << 4) ^ k.dev) + (h << 6) + (h >> 2);
+      return h;
+    }
+  };
+  static std::mutex                                    cache_mu;
+  static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+  int                                                  dev = 0;
+  cudaGetDevice(&dev);
+  void       *base = const_cast<uint8_t *>(args.w) + args.w_k_off_bytes;
+  const Key   key{ base, args.w_row_bytes, args.kblocks, args.N, wt, dev };
+  CUtensorMap wmap;
+  bool        hit = false;
+  {
+    std::lock_guard<std::mutex> lk(cache_mu);
+    auto                        it = cache.find(key);
+    if (it != cache.end()) {
+      wmap = it->second;
+      hit  = true;
+    }
   }
-  const int         bb        = wt == kQ4 ? 18 : 34;
-  CUtensorMap       wmap;
-  const cuuint64_t  gdim[2]   = { (cuuint64_t) args.kblocks * bb / 8, (cuuint64_t) args.N };
-  const cuuint64_t  gstride[1] = { (cuuint64_t) args.w_row_bytes };
-  const cuuint32_t  box[2]    = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
-  const cuuint32_t  estr[2]   = { 1, 1 };
-  void             *base      = const_cast<uint8_t *>(args.w) + args.w_k_off_bytes;
-  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
-      CUDA_SUCCESS) {
-    return cudaErrorInvalidValue;
+  if (!hit) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) {
+      return cudaErrorNotSupported;
+    }
+    const int        bb         = wt == kQ4 ? 18 : 34;
+    const cuuint64_t gdim[2]    = { (cuuint64_t) args.kblocks * bb / 8, (cuuint64_t) args.N };
+    const cuuint64_t gstride[1] = { (cuuint64_t) args.w_row_bytes };
+    const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
+    const cuuint32_t estr[2]    = { 1, 1 };
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
+        CUDA_SUCCESS) {
+      return cudaErrorInvalidValue;
+    }
+    std::lock_guard<std::mutex> lk(cache_mu);
+    if (cache.size() >= 8192) {
+      cache.clear();
+    }
+    cache.emplace(key, wmap);
   }
   if (wt == kQ4) {
     return a16 ? launch_mpad<kQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
