@@ -252,15 +252,20 @@ def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
         chan = pkg.MessageChannel(16384)
         try:
             for m in cfg.ms:
+                # independent N(0,1) activations per matrix kind, one output buffer per (layer, matrix):
+                # no request reads or overwrites what another one writes
                 xs = [torch.randn((m, op.k), device=dev, dtype=torch.float32) for op in cfg.ops]
-                ys = [torch.empty((m, op.n), device=dev, dtype=torch.float32) for op in cfg.ops]
+                ys = [[torch.empty((m, op.n), device=dev, dtype=torch.float32) for op in cfg.ops]
+                      for _ in range(layers)]
                 xfd = [lib.htp_buf_wrap(x.data_ptr(), x.numel() * 4) for x in xs]
-                yfd = [lib.htp_buf_wrap(y.data_ptr(), y.numel() * 4) for y in ys]
+                yfd = [lib.htp_buf_wrap(y.data_ptr(), y.numel() * 4) for ly in ys for y in ly]
                 reqs = []
                 for l in range(layers):
                     for i, op in enumerate(cfg.ops):
-                        reqs.append(pkg.pack_matmul_request(pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32, (yfd[i], 0),
-                                                            (xfd[i], 0), (wfd[l][i], 0), m, op.k, op.n))
+                        reqs.append(pkg.pack_matmul_request(pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32,
+                                                            (yfd[l * len(cfg.ops) + i], 0), (xfd[i], 0),
+                                                            (wfd[l][i], 0), m, op.k, op.n))
+                launches0 = lib.htp_b200_launch_count()
                 for _ in range(2):
                     st = chan.submit(reqs)
                     assert all(s == 0 for s in st), st
@@ -274,6 +279,7 @@ def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
                 out[f"cfg3_llama8b_stack_q4_0_m{m}"] = {
                     "ms_per_pass": round(ms, 4), "ops_per_pass": len(reqs), "GBps": round(gb, 1),
                     "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4),
+                    "kernel_launches_per_pass": (lib.htp_b200_launch_count() - launches0) // (n_pass + 2),
                     "timed": "host wall clock around message-channel round trips (224 requests per message)"}
                 for fd in xfd + yfd:
                     lib.htp_buf_free(fd)

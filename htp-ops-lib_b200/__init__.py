@@ -45,6 +45,7 @@ _vp, _i, _u, _sz, _i64, _u64 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ct
 EXPORTS = {
     # include/htp_ops_b200.h
     "htp_b200_mul_mat": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "htp_b200_mul_mat_batch": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "htp_b200_mul_mat_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "htp_b200_block_sums": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "htp_b200_weight_bytes": (_sz, [_i, _i64, _i64]),

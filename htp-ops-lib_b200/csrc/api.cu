@@ -3,9 +3,11 @@
 #include "htp_ops_b200.h"
 
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <vector>
 
 #include "aux_kernels.h"
 #include "device_ctx.h"
@@ -14,7 +16,7 @@
 
 namespace htp {
 
-int g_opt_pdl           = 1;
+int g_opt_pdl           = getenv("HTP_OPS_NO_PDL") ? 0 : 1;  // programmatic dependent launch
 int g_opt_force_generic = 0;
 int g_opt_gemm_min_m     = 64;
 int g_opt_gemm_tile_n    = 0;   // tokens per GEMM tile: 0 = by M, else 128 or 256  // fp16 activations with at least this many tokens go to the tensor-core GEMM
@@ -66,7 +68,9 @@ StreamScratch *stream_scratch(DeviceCtx *ctx, cudaStream_t stream) {
     cudaGetLastError();
     return nullptr;
   }
-  if (cudaMemset(base, 0, pbytes + cbytes + 256) != cudaSuccess) {
+  // (the memset runs on the default stream, which non-blocking streams do not wait for: finish it
+  // before any kernel can use the area)
+  if (cudaMemset(base, 0, pbytes + cbytes + 256) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
     cudaGetLastError();
     cudaFree(base);
     return nullptr;
@@ -232,6 +236,104 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
                   st, allow_pdl && g_opt_pdl != 0);
 }
 
+
+bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type) {
+  const int wt = wt_index(weight_type);
+  if (wt < 0 || m <= 0 || m > 8 || k <= 0 || n <= 0 || k % 256 != 0 || n % 32 != 0 || g_opt_force_generic) {
+    return false;
+  }
+  const bool a16 = act_type == HTP_B200_ACT_F16;
+  if (a16 && m >= g_opt_gemm_min_m) {
+    return false;
+  }
+  const int    mpad = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
+  const size_t frag = gemv_frag_bytes(wt, a16, mpad, k / 32);
+  const long   room = (long) kGemvSmemBudget - kGemvSmemHeader - (long) frag;
+  return room >= 3L * kGemvTileRows * gemv_row_pitch(wt);
+}
+
+int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type, int act_type, cudaStream_t st,
+                          bool allow_pdl) {
+  const int wt = wt_index(weight_type);
+  if (!d || n_ops <= 0 || wt < 0 || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
+    return -1;
+  }
+  for (int i = 0; i < n_ops; ++i) {
+    if (!d[i].y || !d[i].x || !d[i].w || !aligned128(d[i].y) || !aligned128(d[i].x) || !aligned128(d[i].w) ||
+        !mul_mat_batchable(m, d[i].k, d[i].n, weight_type, act_type)) {
+      return -1;
+    }
+  }
+  DeviceCtx *ctx = current_device_ctx();
+  if (!ctx) {
+    return -2;
+  }
+  StreamScratch *sc = stream_scratch(ctx, st);
+  if (!sc) {
+    return -2;
+  }
+  const bool a16   = act_type == HTP_B200_ACT_F16;
+  const int  mpad  = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
+  const int  bb    = wt == 0 ? 18 : 34;
+  const int  stage = kGemvTileRows * gemv_row_pitch(wt);
+  const int  sb    = gemv_stage_blocks(wt);
+  static thread_local GemvBatchArgs args;  // ~25 KB of kernel parameters, reused between launches
+  for (int o0 = 0; o0 < n_ops; o0 += kGemvBatchMaxOps) {
+    const int cnt = (n_ops - o0) < kGemvBatchMaxOps ? (n_ops - o0) : kGemvBatchMaxOps;
+    long long items = 0;
+    size_t    frag  = 0;
+    for (int i = 0; i < cnt; ++i) {
+      const MatMulDesc &q  = d[o0 + i];
+      GemvBatchOp      &op = args.ops[i];
+      const int         kb = q.k / 32;
+      if (gemv_weight_map(op.wmap, q.w, (long long) kb * bb, kb, q.n, wt) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
+      }
+      op.y               = q.y;
+      op.x               = q.x;
+      op.item_begin      = items;
+      op.N               = q.n;
+      op.kblocks         = kb;
+      op.x_stride        = q.k;
+      op.stages_per_tile = (kb + sb - 1) / sb;
+      items += (long long) (q.n / kGemvTileRows) * op.stages_per_tile;
+      const size_t f = gemv_frag_bytes(wt, a16, mpad, kb);
+      frag           = f > frag ? f : frag;
+    }
+    args.total_items = items;
+    args.partials    = sc->partials;
+    args.counters    = sc->counters;
+    args.err         = sc->err;
+    args.n_ops       = cnt;
+    args.M           = m;
+    args.frag_bytes  = (int) frag;
+    long long grid   = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
+    if (grid > items) {
+      grid = items;
+    }
+    const int budget = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
+    int       nst    = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
+    nst              = nst > kGemvMaxStages ? kGemvMaxStages : nst;
+    const long long per_cta = (items + grid - 1) / grid;
+    if (nst > per_cta) {
+      nst = (int) (per_cta < 2 ? 2 : per_cta);
+    }
+    if (nst < 2) {
+      return -2;
+    }
+    args.n_stages     = nst;
+    const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
+    if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    count_launch();
+  }
+  return 0;
+}
+
 }  // namespace htp
 
 extern "C" {
@@ -240,6 +342,22 @@ int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int 
                      int act_type, void *stream) {
   return mul_mat_checked(dst, activation, weight, m, k, n, weight_type, act_type, static_cast<cudaStream_t>(stream),
                          true);
+}
+
+int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activation, const void *const *weight,
+                           const int *k, const int *n, int m, int weight_type, int act_type, void *stream) {
+  if (n_ops <= 0 || !dst || !activation || !weight || !k || !n) {
+    return -1;
+  }
+  std::vector<MatMulDesc> d((size_t) n_ops);
+  for (int i = 0; i < n_ops; ++i) {
+    d[i] = MatMulDesc{ static_cast<float *>(dst[i]), activation[i], static_cast<const uint8_t *>(weight[i]), k[i],
+                       n[i] };
+    if (!mul_mat_batchable(m, k[i], n[i], weight_type, act_type)) {
+      return -1;
+    }
+  }
+  return mul_mat_batch_checked(d.data(), n_ops, m, weight_type, act_type, static_cast<cudaStream_t>(stream), true);
 }
 
 int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream) {
@@ -286,9 +404,10 @@ int htp_b200_stream_status(void *stream) {
     return -2;
   }
   if (code != 0) {
-    cudaMemset(sc->err, 0, sizeof(int));
+    cudaMemsetAsync(sc->err, 0, sizeof(int), st);
     // a kernel that gave up may have left arrival counters behind
-    cudaMemset(sc->counters, 0, (size_t) kGemvMaxGrid * sizeof(unsigned));
+    cudaMemsetAsync(sc->counters, 0, (size_t) kGemvMaxGrid * sizeof(unsigned), st);
+    cudaStreamSynchronize(st);
   }
   return code;
 }

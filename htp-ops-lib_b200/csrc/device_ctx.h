@@ -33,6 +33,19 @@ void release_all_scratch();
 int mul_mat_checked(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
                     int act_type, cudaStream_t stream, bool allow_pdl);
 
+// Several independent mat-vecs of one kind (same weight format, activation type and token count
+// m <= 8) in one persistent launch.  The caller guarantees that no operator reads what another one
+// of the batch writes.
+struct MatMulDesc {
+  float         *y;
+  const void    *x;
+  const uint8_t *w;
+  int            k, n;
+};
+bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type);
+int  mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type, int act_type, cudaStream_t stream,
+                           bool allow_pdl);
+
 extern int      g_opt_pdl;
 extern int      g_opt_force_generic;
 extern int      g_opt_gemm_min_m;

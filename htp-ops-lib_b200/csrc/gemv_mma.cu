@@ -32,6 +32,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <cstring>
 #include <functional>
 #include <mutex>
 #include <unordered_map>
@@ -271,7 +272,7 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
     v += red[w][tid];
   }
 
-  const long long first = tile * S, last = first + S - 1;
+  const long long first = p.item_base + tile * S, last = first + S - 1;
   bool            write_out = true;
   if (first < it0 || last >= it1) {
     // this CTA holds only part of the tile
@@ -443,6 +444,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
+      // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
+      // (the block scales) may be scheduled after it, so a fence makes sure every load of the
+      // stage has been performed before the slot can be overwritten.
+      asm volatile("fence.acq_rel.cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&sm->empty[slot]);
@@ -514,6 +520,243 @@ cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int 
   }
 }
 
+// ------------------------------------------------------------------ the batched kernel
+//
+// Same pipeline, but the item list is the concatenation of the items of up to 128 independent
+// operators of one kind.  CTA c still owns the contiguous range [T c / G, T (c+1) / G) of the WHOLE
+// list, so it touches only one or two operators; the activation fragments are rebuilt when its
+// range crosses into the next operator (all consumer warps have passed the tile-completion barrier
+// by then, i.e. nobody reads the old fragments any more).  Tiles cut by a range boundary are
+// finished exactly as in the single-operator kernel, with list-wide item indices.
+
+template <int WT, bool A16, int MPAD>
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __grid_constant__ GemvBatchArgs b) {
+  using C = Cfg<WT, A16, MPAD>;
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  Smem    *sm     = reinterpret_cast<Smem *>(smem_raw);
+  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + sizeof(Smem));
+  uint8_t *stages = smem_raw + sizeof(Smem) + b.frag_bytes;
+
+  const int       warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int       NST = b.n_stages;
+  const long long T = b.total_items, G = gridDim.x;
+  const long long it0 = T * blockIdx.x / G, it1 = T * (blockIdx.x + 1) / G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&sm->full[s], 1);
+      mbar_init(&sm->empty[s], kConsumerWarps);
+    }
+    sm->abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  // operator that holds item it0
+  int oi = 0;
+  while (oi + 1 < b.n_ops && b.ops[oi + 1].item_begin <= it0) {
+    ++oi;
+  }
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer
+    if (lane == 0) {
+      const uint64_t pol  = l2_policy_evict_first();
+      int            S    = b.ops[oi].stages_per_tile;
+      long long      li   = it0 - b.ops[oi].item_begin;
+      long long      tile = li / S;
+      int            st   = (int) (li - tile * S);
+      long long      tiles_in_op = b.ops[oi].N / kGemvTileRows;
+      int            slot = 0, ph = 0;
+      tma_prefetch_descriptor(b.ops[oi].wmap);
+      for (long long it = it0; it < it1; ++it) {
+        if (!mbar_wait(&sm->empty[slot], ph ^ 1)) {
+          atomicCAS(b.err, 0, kGemvErrProducerWait);
+          break;
+        }
+        mbar_arrive_expect_tx(&sm->full[slot], (uint32_t) C::STAGE);
+        tma_load_2d(stages + (size_t) slot * C::STAGE, b.ops[oi].wmap, st * (C::SB * C::BB / 8),
+                    (int) (tile * kGemvTileRows), &sm->full[slot], pol);
+        if (++slot == NST) {
+          slot = 0;
+          ph ^= 1;
+        }
+        if (++st == S) {
+          st = 0;
+          if (++tile == tiles_in_op && oi + 1 < b.n_ops) {
+            ++oi;
+            tile        = 0;
+            S           = b.ops[oi].stages_per_tile;
+            tiles_in_op = b.ops[oi].N / kGemvTileRows;
+            tma_prefetch_descriptor(b.ops[oi].wmap);
+          }
+        }
+      }
+    }
+  } else {
+    // ---------------- consumers
+    const int tid = threadIdx.x;
+    const int g = lane >> 2, t = lane & 3;
+    pdl_wait_prior_grids();
+
+    auto op_args = [&](int i) {
+      GemvArgs p        = {};
+      p.y               = b.ops[i].y;
+      p.x               = b.ops[i].x;
+      p.x_k_off         = 0;
+      p.x_stride        = b.ops[i].x_stride;
+      p.M               = b.M;
+      p.N               = b.ops[i].N;
+      p.kblocks         = b.ops[i].kblocks;
+      p.accumulate      = 0;
+      p.stages_per_tile = b.ops[i].stages_per_tile;
+      p.item_base       = b.ops[i].item_begin;
+      p.total_items     = b.total_items;
+      p.partials        = b.partials;
+      p.counters        = b.counters;
+      p.err             = b.err;
+      return p;
+    };
+    GemvArgs p = op_args(oi);
+    build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
+    named_bar_sync(1, kConsumerThreads);
+
+    float acc[2][4];
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[rg][i] = 0.f;
+      }
+    }
+    int       S    = p.stages_per_tile;
+    long long li   = it0 - p.item_base;
+    long long tile = li / S;
+    int       st   = (int) (li - tile * S);
+    long long tiles_in_op = p.N / kGemvTileRows;
+    int       slot = 0, ph = 0;
+    bool      ok   = true;
+    int       flush_parity = 0;
+    const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
+    const uint8_t *warp_base = stages + g * C::PSTRIDE + warp * C::BPW * C::BB;
+    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW * 2) * C::CH * C::NC * 4;
+    for (long long it = it0; it < it1; ++it) {
+      if (!mbar_wait(&sm->full[slot], ph)) {
+        atomicCAS(b.err, 0, kGemvErrConsumerWait);
+        ok = false;
+        break;
+      }
+      const int nblk = min(C::SB, p.kblocks - st * C::SB);
+      if (warp * C::BPW < nblk) {
+        const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
+        const uint2   *fp = warp_frag + (size_t) (st * C::SB * 2) * C::CH * C::NC * 4;
+#pragma unroll
+        for (int i = 0; i < C::BPW; ++i) {
+          uint2 bf[2][2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+              bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
+            }
+          }
+#pragma unroll
+          for (int rg = 0; rg < 2; ++rg) {
+            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
+            if ((i & 1) == 0) {
+              block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
+            } else {
+              block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
+            }
+          }
+        }
+      }
+      // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
+      // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
+      // (the block scales) may be scheduled after it, so a fence makes sure every load of the
+      // stage has been performed before the slot can be overwritten.
+      asm volatile("fence.acq_rel.cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&sm->empty[slot]);
+      }
+      if (++slot == NST) {
+        slot = 0;
+        ph ^= 1;
+      }
+      if (++st == S) {
+        st = 0;
+        if (it + 1 < it1) {
+          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
+#pragma unroll
+          for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc[rg][i] = 0.f;
+            }
+          }
+          if (++tile == tiles_in_op && oi + 1 < b.n_ops) {
+            // next operator: its activations replace the fragments (every consumer warp is past
+            // the completion barrier above, so the old ones are no longer read)
+            ++oi;
+            p           = op_args(oi);
+            tile        = 0;
+            S           = p.stages_per_tile;
+            tiles_in_op = p.N / kGemvTileRows;
+            if constexpr (A16) {
+              named_bar_sync(1, kConsumerThreads);  // the fp32 path starts with a barrier of its own
+            }
+            build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
+            named_bar_sync(1, kConsumerThreads);
+          }
+        }
+      }
+    }
+    if (ok && it1 > it0) {
+      flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
+    }
+  }
+}
+
+template <int WT, bool A16, int MPAD>
+cudaError_t batch_one(const GemvBatchArgs &args, int grid, size_t smem, cudaStream_t stream, bool pdl) {
+  auto kern = gemv_mma_batch_kernel<WT, A16, MPAD>;
+  static bool attr_set[64] = {};
+  int         dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvSmemBudget);
+    if (e != cudaSuccess) {
+      return e;
+    }
+    if (dev >= 0 && dev < 64) {
+      attr_set[dev] = true;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(grid);
+  cfg.blockDim           = dim3(kThreads);
+  cfg.dynamicSmemBytes   = smem;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs                                          = attr;
+  cfg.numAttrs                                       = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args);
+}
+
+template <int WT, bool A16>
+cudaError_t batch_mpad(const GemvBatchArgs &a, int mpad, int grid, size_t smem, cudaStream_t s, bool pdl) {
+  switch (mpad) {
+    case 1: return batch_one<WT, A16, 1>(a, grid, smem, s, pdl);
+    case 2: return batch_one<WT, A16, 2>(a, grid, smem, s, pdl);
+    case 4: return batch_one<WT, A16, 4>(a, grid, smem, s, pdl);
+    default: return batch_one<WT, A16, 8>(a, grid, smem, s, pdl);
+  }
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver-entry-point lookup (no link against libcuda)
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -543,13 +786,11 @@ size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
   return (b + 127) & ~(size_t) 127;
 }
 
-cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
-                            cudaStream_t stream, bool pdl) {
-  // Tensor map over this launch's K range of the weight bytes, as 8-byte elements:
-  // inner dimension = bytes of the K range per row / 8, outer = N rows, row pitch = w_row_bytes.
-  // Encoding costs about a microsecond of host time, comparable to a small launch, and a decoder
-  // re-issues the same few hundred weight matrices every token: the maps are cached by what
-  // they describe.
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt) {
+  // Tensor map over a K range of the weight bytes, as 8-byte elements: inner dimension = bytes of
+  // the K range per row / 8, outer = n rows, row pitch = w_row_bytes.  Encoding costs about a
+  // microsecond of host time, comparable to a small launch, and a decoder re-issues the same few
+  // hundred weight matrices every token: the maps are cached by what they describe.
   struct Key {
     const void *base;
     long long   row_bytes;
@@ -571,38 +812,47 @@ cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, in
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
   int                                                  dev = 0;
   cudaGetDevice(&dev);
-  void       *base = const_cast<uint8_t *>(args.w) + args.w_k_off_bytes;
-  const Key   key{ base, args.w_row_bytes, args.kblocks, args.N, wt, dev };
-  CUtensorMap wmap;
-  bool        hit = false;
+  const Key key{ w, w_row_bytes, kblocks, n, wt, dev };
   {
     std::lock_guard<std::mutex> lk(cache_mu);
     auto                        it = cache.find(key);
     if (it != cache.end()) {
-      wmap = it->second;
-      hit  = true;
+      memcpy(wmap_out, &it->second, sizeof(CUtensorMap));
+      return cudaSuccess;
     }
   }
-  if (!hit) {
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) {
-      return cudaErrorNotSupported;
-    }
-    const int        bb         = wt == kQ4 ? 18 : 34;
-    const cuuint64_t gdim[2]    = { (cuuint64_t) args.kblocks * bb / 8, (cuuint64_t) args.N };
-    const cuuint64_t gstride[1] = { (cuuint64_t) args.w_row_bytes };
-    const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
-    const cuuint32_t estr[2]    = { 1, 1 };
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) !=
-        CUDA_SUCCESS) {
-      return cudaErrorInvalidValue;
-    }
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) {
+    return cudaErrorNotSupported;
+  }
+  CUtensorMap      wmap;
+  const int        bb         = wt == kQ4 ? 18 : 34;
+  const cuuint64_t gdim[2]    = { (cuuint64_t) kblocks * bb / 8, (cuuint64_t) n };
+  const cuuint64_t gstride[1] = { (cuuint64_t) w_row_bytes };
+  const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
+  const cuuint32_t estr[2]    = { 1, 1 };
+  if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    return cudaErrorInvalidValue;
+  }
+  {
     std::lock_guard<std::mutex> lk(cache_mu);
     if (cache.size() >= 8192) {
       cache.clear();
     }
     cache.emplace(key, wmap);
+  }
+  memcpy(wmap_out, &wmap, sizeof(CUtensorMap));
+  return cudaSuccess;
+}
+
+cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
+                            cudaStream_t stream, bool pdl) {
+  CUtensorMap wmap;
+  cudaError_t e = gemv_weight_map(&wmap, args.w + args.w_k_off_bytes, args.w_row_bytes, args.kblocks, args.N, wt);
+  if (e != cudaSuccess) {
+    return e;
   }
   if (wt == kQ4) {
     return a16 ? launch_mpad<kQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
@@ -610,6 +860,16 @@ cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, in
   }
   return a16 ? launch_mpad<kQ8, true>(args, wmap, mpad, grid, smem, stream, pdl)
              : launch_mpad<kQ8, false>(args, wmap, mpad, grid, smem, stream, pdl);
+}
+
+cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
+                                  cudaStream_t stream, bool pdl) {
+  if (wt == kQ4) {
+    return a16 ? batch_mpad<kQ4, true>(args, mpad, grid, smem, stream, pdl)
+               : batch_mpad<kQ4, false>(args, mpad, grid, smem, stream, pdl);
+  }
+  return a16 ? batch_mpad<kQ8, true>(args, mpad, grid, smem, stream, pdl)
+             : batch_mpad<kQ8, false>(args, mpad, grid, smem, stream, pdl);
 }
 
 }  // namespace htp

@@ -41,11 +41,40 @@ struct GemvArgs {
   int            accumulate;  // add to y instead of overwriting it
   int            n_stages;    // ring depth
   int            stages_per_tile;
-  long long      total_items;  // (N / 32) * stages_per_tile
+  long long      item_base;    // index of this operator's first item in the launch's item list (0 when alone)
+  long long      total_items;  // items of the whole launch: (N / 32) * stages_per_tile when alone
   float         *partials;     // [grid][2][256] scratch for tiles cut by a CTA range boundary
   unsigned      *counters;     // [grid] arrival counters, zero between launches
   int           *err;          // first error code, 0 when none
 };
+
+// One operator of a batched launch: several independent mat-vecs of the same kind (weight format,
+// activation type, token count) streamed by ONE persistent kernel as a single item list, so that
+// small operators pay neither a launch nor a pipeline fill and drain each.
+constexpr int kGemvBatchMaxOps = 128;
+
+struct alignas(64) GemvBatchOp {
+  unsigned char  wmap[128];   // CUtensorMap over the operator's weight bytes
+  float         *y;
+  const void    *x;
+  long long      item_begin;  // first item of this operator in the launch's item list
+  int            N, kblocks, x_stride, stages_per_tile;
+};
+
+struct GemvBatchArgs {
+  GemvBatchOp ops[kGemvBatchMaxOps];
+  long long   total_items;
+  float      *partials;
+  unsigned   *counters;
+  int        *err;
+  int         n_ops, M, n_stages, frag_bytes;  // frag_bytes: fragment region, sized for the largest K
+};
+
+// Fills op.wmap for a weight matrix of n rows and kblocks blocks per row (cached by geometry).
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt);
+
+cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
+                                  cudaStream_t stream, bool pdl);
 
 // Bytes of shared memory the activation fragments of `kblocks` blocks occupy.
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks);

@@ -11,6 +11,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <iterator>
+#include <map>
 #include <mutex>
 #include <thread>
 #include <unordered_map>
@@ -36,8 +38,61 @@ struct Buffer {
   int      kind = kDeviceBuf;
 };
 
-struct Range {
-  uintptr_t lo, hi;
+// Set of disjoint address intervals (merged on insertion); used to detect operators that touch
+// memory an earlier, still pending operator writes or reads.
+class IntervalSet {
+ public:
+  bool overlaps(uintptr_t lo, uintptr_t hi) const {
+    if (lo >= hi || m_.empty()) {
+      return false;
+    }
+    auto it = m_.lower_bound(hi);  // first interval starting at or after hi
+    if (it == m_.begin()) {
+      return false;
+    }
+    --it;
+    return it->second > lo;  // intervals are disjoint: the last one starting below hi decides
+  }
+  void add(uintptr_t lo, uintptr_t hi) {
+    if (lo >= hi) {
+      return;
+    }
+    auto it = m_.lower_bound(lo);
+    if (it != m_.begin()) {
+      auto prev = std::prev(it);
+      if (prev->second >= lo) {
+        it = prev;
+      }
+    }
+    while (it != m_.end() && it->first <= hi) {
+      lo = it->first < lo ? it->first : lo;
+      hi = it->second > hi ? it->second : hi;
+      it = m_.erase(it);
+    }
+    m_[lo] = hi;
+  }
+  void clear() { m_.clear(); }
+  bool empty() const { return m_.empty(); }
+
+ private:
+  std::map<uintptr_t, uintptr_t> m_;
+};
+
+// Decode-sized operators of one kind that do not depend on each other, collected while a message
+// is being read and issued as ONE persistent launch.
+struct PendingBatch {
+  std::vector<htp::MatMulDesc> ops;
+  std::vector<RequestHeader *> owners;  // where to report a launch failure
+  int                          m = 0, weight_type = 0, act_type = 0;
+  IntervalSet                  writes, reads;
+  bool                         weights_hazard = false;  // a weight overlaps an earlier pending output
+  void clear() {
+    ops.clear();
+    owners.clear();
+    writes.clear();
+    reads.clear();
+    weights_hazard = false;
+  }
 };
 
 struct Session {
@@ -50,7 +105,8 @@ struct Session {
   int                             next_fd = 16;
   // regions written by operators enqueued since the stream was last waited for; a weight buffer
   // that overlaps one of them must not be prefetched ahead of stream order
-  std::vector<Range> pending_out;
+  IntervalSet  pending_out;
+  PendingBatch batch;
   // message channel
   std::thread       servicer;
   std::atomic<bool> stop{ false };
@@ -102,19 +158,35 @@ uint8_t *resolve(const RpcmemBufAddr &a, size_t bytes) {
   return b.ptr + off;
 }
 
-bool overlaps_pending(const uint8_t *p, size_t bytes) {
-  const uintptr_t lo = (uintptr_t) p, hi = lo + bytes;
-  for (const Range &r : g.pending_out) {
-    if (lo < r.hi && r.lo < hi) {
-      return true;
+// Issues the collected batch (if any).  Returns 0 or the launch error.
+int flush_batch() {
+  PendingBatch &b = g.batch;
+  if (b.ops.empty()) {
+    return 0;
+  }
+  int rc;
+  if (b.ops.size() == 1) {
+    const htp::MatMulDesc &d = b.ops[0];
+    rc = htp::mul_mat_checked(d.y, d.x, d.w, b.m, d.k, d.n, b.weight_type, b.act_type, g.stream, !b.weights_hazard);
+  } else {
+    rc = htp::mul_mat_batch_checked(b.ops.data(), (int) b.ops.size(), b.m, b.weight_type, b.act_type, g.stream,
+                                    !b.weights_hazard);
+  }
+  if (rc != 0) {
+    for (RequestHeader *rh : b.owners) {
+      if (rh) {
+        rh->state = rc;
+      }
     }
   }
-  return false;
+  b.clear();
+  return rc;
 }
 
 // Enqueue one operator on the session stream.  Returns the synchronous part of the result
-// (argument validation); kernel-side errors surface when the stream is waited for.
-int enqueue_op(const OpComputeRequest *req) {
+// (argument validation); launch and kernel-side errors surface later (flush / stream wait).
+// `owner` is the request to blame if the batch the operator joins fails to launch.
+int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   if (!g.open || !g.backend) {
     return -1;
   }
@@ -130,7 +202,7 @@ int enqueue_op(const OpComputeRequest *req) {
   }
   MatMulParams p;
   memcpy(&p, req->payload, sizeof(p));
-  if (p.m <= 0 || p.k <= 0 || p.n <= 0 || p.k % 32 != 0) {
+  if (p.m <= 0 || p.k <= 0 || p.n <= 0 || p.k % 32 != 0 || p.n % 32 != 0) {
     return -1;
   }
   // sizes as in op_executor.cc:124-126, in 64 bits
@@ -140,21 +212,46 @@ int enqueue_op(const OpComputeRequest *req) {
   uint8_t     *out = resolve(p.output, out_bytes);
   uint8_t     *act = resolve(p.activation, act_bytes);
   uint8_t     *w   = resolve(p.weight, w_bytes);
-  if (!out || !act || !w) {
+  if (!out || !act || !w || (((uintptr_t) out | (uintptr_t) act | (uintptr_t) w) & 127u)) {
     return -1;
   }
-  const bool pdl_ok = !overlaps_pending(w, w_bytes);
-  const int  rc     = htp::mul_mat_checked(out, act, w, p.m, p.k, p.n, weight_type, act_type, g.stream, pdl_ok);
-  if (rc == 0) {
-    g.pending_out.push_back({ (uintptr_t) out, (uintptr_t) out + out_bytes });
+  const uintptr_t o0 = (uintptr_t) out, a0 = (uintptr_t) act, w0 = (uintptr_t) w;
+  PendingBatch   &b  = g.batch;
+  const bool      batchable = htp::mul_mat_batchable(p.m, p.k, p.n, weight_type, act_type);
+  if (!b.ops.empty()) {
+    const bool same_kind = batchable && b.m == p.m && b.weight_type == weight_type && b.act_type == act_type;
+    const bool hazard    = b.writes.overlaps(a0, a0 + act_bytes) || b.writes.overlaps(w0, w0 + w_bytes) ||
+                        b.writes.overlaps(o0, o0 + out_bytes) || b.reads.overlaps(o0, o0 + out_bytes);
+    if (!same_kind || hazard) {
+      flush_batch();  // a failure is reported in the owners' request states
+    }
   }
-  return rc;
+  const bool weights_hazard = g.pending_out.overlaps(w0, w0 + w_bytes);
+  if (!batchable) {
+    const int rc = htp::mul_mat_checked(out, act, w, p.m, p.k, p.n, weight_type, act_type, g.stream, !weights_hazard);
+    if (rc == 0) {
+      g.pending_out.add(o0, o0 + out_bytes);
+    }
+    return rc;
+  }
+  if (b.ops.empty()) {
+    b.m = p.m, b.weight_type = weight_type, b.act_type = act_type;
+  }
+  b.ops.push_back(htp::MatMulDesc{ reinterpret_cast<float *>(out), act, w, p.k, p.n });
+  b.owners.push_back(owner);
+  b.writes.add(o0, o0 + out_bytes);
+  b.reads.add(a0, a0 + act_bytes);
+  b.reads.add(w0, w0 + w_bytes);
+  b.weights_hazard = b.weights_hazard || weights_hazard;
+  g.pending_out.add(o0, o0 + out_bytes);
+  return 0;
 }
 
 int wait_stream() {
-  const int rc = htp_b200_stream_status(g.stream);
+  const int frc = flush_batch();
+  const int rc  = htp_b200_stream_status(g.stream);
   g.pending_out.clear();
-  return rc;
+  return rc != 0 ? rc : frc;
 }
 
 // ---------------------------------------------------------------- message channel servicer
@@ -222,7 +319,7 @@ void servicer_loop() {
               rh->state = -1;
               break;
             }
-            rh->state = enqueue_op(reinterpret_cast<OpComputeRequest *>(rh->data));
+            rh->state = enqueue_op(reinterpret_cast<OpComputeRequest *>(rh->data), rh);
             if (rh->state == 0) {
               enqueued.push_back(i);
             }
@@ -324,6 +421,7 @@ void close_dsp_session(void) {
     g.bufs.clear();
   }
   g.pending_out.clear();
+  g.batch.clear();
   htp::release_all_scratch();
   if (g.stream) {
     cudaStreamDestroy(g.stream);
@@ -455,7 +553,7 @@ int execute_op_simple(struct OpComputeRequest *req) {
   if (!req || !set_session_device() || !g.backend) {
     return -1;
   }
-  const int rc = enqueue_op(req);
+  const int rc = enqueue_op(req, nullptr);
   if (rc != 0) {
     return rc;
   }
@@ -473,7 +571,10 @@ int htp_buf_alloc(size_t size) {
     cudaGetLastError();
     return -1;
   }
-  if (cudaMemset(b.ptr, 0, size) != cudaSuccess) {
+  // Zero-fill on the session stream and wait: a cudaMemset on the default stream is asynchronous
+  // and NOT ordered with the (non-blocking) session stream, so it could land after an operator
+  // had already written the buffer.
+  if (cudaMemsetAsync(b.ptr, 0, size, g.stream) != cudaSuccess || cudaStreamSynchronize(g.stream) != cudaSuccess) {
     cudaGetLastError();
     cudaFree(b.ptr);
     return -1;

@@ -37,6 +37,20 @@ int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int 
                      int act_type, void *stream);
 
 /*
+ * n_ops INDEPENDENT decode mat-vecs of one kind (same weight_type, act_type and token count
+ * m <= 8; k[i] % 256 == 0) as one persistent launch: dst[i][m][n[i]] = activation[i][m][k[i]] .
+ * weight[i][n[i]][k[i]]^T.  The operators are streamed as a single work list, so small matrices pay
+ * neither a launch nor a pipeline fill and drain each (a decoder layer's q/k/v or gate/up
+ * projections).  The caller guarantees that no operator reads a buffer another one of the batch
+ * writes.  Closest reference behaviour: a message carrying several requests, executed in order
+ * (src/dsp/commu.c:91-126); the message channel of this library forms such batches itself.
+ * Returns -1 when an operator cannot be batched (m > 8, k % 256, a fragment set that does not fit
+ * one launch, misaligned pointers): issue it with htp_b200_mul_mat instead.
+ */
+int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activation, const void *const *weight,
+                           const int *k, const int *n, int m, int weight_type, int act_type, void *stream);
+
+/*
  * The decode mat-vec (m <= 8) for callers that must not allocate device memory once they are
  * running - a server that has handed all of device memory to its own pools, or a decode loop that
  * cannot take the device-wide synchronisation an allocation implies.  Same arguments, checks and

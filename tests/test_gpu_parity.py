@@ -246,3 +246,68 @@ def test_generic_kernel_matches_streaming_kernel(dev, oracle, wl):
         lib.htp_b200_set_option(b"force_generic", 0)
     check(oracle, y_gen, x, wq, 128, 8)
     assert np.abs(y_gen - y_fast).max() <= 1e-3 * np.abs(y_fast).max()
+
+
+# ------------------------------------------------------------------ batched decode launches
+
+@pytest.mark.parametrize("wtype,act_f16,m", [(2, False, 1), (8, True, 1), (2, False, 3), (2, True, 8)])
+def test_batched_independent_ops(dev, oracle, wl, wtype, act_f16, m):
+    """Several independent mat-vecs of different shapes as ONE launch (htp_b200_mul_mat_batch):
+    every operator's result meets the oracle gate and agrees with its single-launch result to fp32
+    rounding (tiles are cut at different places, so the fp32 summation order differs).
+    Shapes chosen so that CTA ranges cross operator boundaries inside and between tiles."""
+    import ctypes
+    lib = dev.lib
+    shapes = [(1024, 256), (1024, 32), (4096, 1024), (256, 96), (2048, 4096), (4096, 128), (1024, 2016)]
+    cases = [wl.random_case(700 + i, wtype, act_f16, m, k, n) for i, (k, n) in enumerate(shapes)]
+    fw = [dev.put(wq) for wq, _ in cases]
+    fx = [dev.put(x) for _, x in cases]
+    fy = [dev.buf(m * n * 4) for _, n in shapes]
+    n_ops = len(shapes)
+    arr = lambda fds: (ctypes.c_void_p * n_ops)(*[lib.htp_buf_ptr(f) for f in fds])
+    ks = (ctypes.c_int * n_ops)(*[k for k, _ in shapes])
+    ns = (ctypes.c_int * n_ops)(*[n for _, n in shapes])
+    before = lib.htp_b200_launch_count()
+    rc = lib.htp_b200_mul_mat_batch(n_ops, arr(fy), arr(fx), arr(fw), ks, ns, m, wtype, 1 if act_f16 else 0,
+                                    lib.htp_session_stream())
+    assert rc == 0
+    assert lib.htp_session_synchronize() == 0
+    assert lib.htp_b200_launch_count() == before + 1
+    for i, ((k, n), (wq, x)) in enumerate(zip(shapes, cases)):
+        y = dev.get(fy[i], (m, n))
+        check(oracle, y, x, wq, n, wtype)
+        y1 = dev.matmul(x, wq, n, wtype)
+        assert np.abs(y - y1).max() <= 2e-6 * np.abs(y1).max()
+    # an operator that cannot join a batch is refused, nothing is launched
+    ks_bad = (ctypes.c_int * n_ops)(*([96] + [k for k, _ in shapes][1:]))
+    assert lib.htp_b200_mul_mat_batch(n_ops, arr(fy), arr(fx), arr(fw), ks_bad, ns, m, wtype, 1 if act_f16 else 0,
+                                      lib.htp_session_stream()) == -1
+    dev.free(*fw, *fx, *fy)
+
+
+def test_channel_batches_independent_requests(dev, oracle, wl):
+    """A message of twelve independent requests plus one that reads an earlier output: the servicer
+    issues the independent ones as one launch and the dependent one after it."""
+    lib, pkg = dev.lib, dev.pkg
+    op = pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32
+    shapes = [(1024, 512), (1024, 64), (2048, 256)] * 4
+    cases = [wl.random_case(800 + i, 2, False, 1, k, n) for i, (k, n) in enumerate(shapes)]
+    fw = [dev.put(wq) for wq, _ in cases]
+    fx = [dev.put(x) for _, x in cases]
+    fy = [dev.buf(n * 4) for _, n in shapes]
+    wdep, _ = wl.random_case(899, 2, False, 1, 512, 128)
+    fwd, fyd = dev.put(wdep), dev.buf(128 * 4)
+    reqs = [pkg.pack_matmul_request(op, (fy[i], 0), (fx[i], 0), (fw[i], 0), 1, k, n) for i, (k, n) in enumerate(shapes)]
+    reqs.append(pkg.pack_matmul_request(op, (fyd, 0), (fy[0], 0), (fwd, 0), 1, 512, 128))  # reads output 0
+    chan = pkg.MessageChannel(4096)
+    try:
+        before = lib.htp_b200_launch_count()
+        assert chan.submit(reqs) == [0] * 13
+        assert lib.htp_b200_launch_count() == before + 2
+    finally:
+        chan.close()
+    for i, ((k, n), (wq, x)) in enumerate(zip(shapes, cases)):
+        check(oracle, dev.get(fy[i], (1, n)), x, wq, n, 2)
+    h = dev.get(fy[0], (1, 512))
+    check(oracle, dev.get(fyd, (1, 128)), h, wdep, 128, 2)
+    dev.free(*fw, *fx, *fy, fwd, fyd)
