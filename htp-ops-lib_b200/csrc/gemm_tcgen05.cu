@@ -13,19 +13,25 @@
 // fences and two thirds of the shared-memory traffic per K step, which is what bounds a
 // one-CTA UMMA pipeline.
 //
-// One persistent CTA per SM, tile = 128 weight rows x BT tokens (BT = 256, or 128 for M <= 128),
-// K in steps of 64:
+// Two flavours.  M <= 128: one persistent CTA per SM, tile = 128 weight rows x 128 tokens,
+// tcgen05.mma.cta_group::1.  M > 128: persistent CTA PAIRS (a cluster of two SMs), pair tile = 256
+// weight rows x 256 tokens, tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16): each CTA dequantises
+// its own 128 weight rows into its own tensor memory and loads only ITS half (128 tokens) of the
+// activation tile - the tensor cores of both SMs read both halves - which halves the activation
+// re-reads through L2, the bound of the one-CTA version.  No multicast loads: every CTA fetches its
+// own operands; only tcgen05.commit multicasts its mbarrier arrival to the pair.
+//
+// Roles per CTA, K in steps of 64:
 //   warp 0      TMA producer of the activation tile (BT x 64 fp16, 128-byte swizzle), one per K step
-//   warp 3      TMA producer of the RAW weight bytes (128 rows x 256 weights = 144 / 272 bytes per
-//               row), one per 4 K steps
-//   warp 1      MMA issuer: one thread issues tcgen05.mma.cta_group::1.kind::f16 (M = 128 weight
-//               rows, N = BT tokens, K = 16) four times per K step
+//   warp 1      MMA issuer (in a pair: only in the leader CTA, whose barriers also collect the other
+//               CTA's TMA completions and tensor-memory stores)
 //   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 an 8-stage ring of A tiles
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator, fp32 stores to y[token][weight row]
-//   warps 8-15  dequantisation, two groups of four warps; group g takes the raw stages whose
-//               running index is g (mod 2).  Thread = one weight row: 9 / 17 conflict-free 16-byte
-//               loads bring its 256 raw weights into registers, then per K step it converts 64 of
-//               them to fp16 and stores them as 32 TMEM columns of its lane
+//   warps 8-15  dequantisation, two groups of four warps; group g takes the raw stages (256 weights
+//               per row) whose running index is g (mod 2).  Thread = one weight row: it fetches its
+//               144 / 272 raw bytes itself (cp.async, one stage ahead), moves them to registers
+//               with 9 / 17 conflict-free 16-byte loads, then per K step converts 64 weights to
+//               fp16 and stores them as 32 TMEM columns of its lane
 // All waits are bounded; a wait that runs out records an error code, raises the CTA's abort flag
 // and every role leaves its loop; TMEM is freed before the CTA exits.  No cluster, no multicast.
 #include "gemm_tcgen05.h"
@@ -52,15 +58,16 @@ constexpr int kEpiWarp0  = 4;
 constexpr int kDeqWarp0  = 8;    // warps 8-11: group 0, warps 12-15: group 1
 constexpr int kTmemCols  = 512;
 constexpr int kTmemA     = 256;  // first column of the A ring
-constexpr int kMaxNX     = 6;
+constexpr int kMaxNX     = 8;
 constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
 
-template <int WT, int BT>
+template <int WT, int BT, bool TWO>
 struct GCfg {
   static constexpr int BB        = BlockTraits<WT>::kBytes;
   static constexpr int RB        = 8 * BB;   // raw bytes per row and raw stage: 144 / 272
   static constexpr int RW        = RB / 16;  // 16-byte words per row: 9 / 17
-  static constexpr int X_BYTES   = BT * 128;
+  static constexpr int XROWS     = TWO ? BT / 2 : BT;  // activation rows this CTA loads per K step
+  static constexpr int X_BYTES   = XROWS * 128;
   static constexpr int RAW_BYTES = kBW * RB;
   static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512;  // raw ring, slack, barriers
   static constexpr int NX_FIT    = (kSmemLimit - FIXED) / X_BYTES;
@@ -70,7 +77,6 @@ struct GCfg {
 
 struct GSmemBar {
   uint64_t x_full[kMaxNX], x_empty[kMaxNX];
-  uint64_t raw_full[2], raw_empty[2];
   uint64_t at_full[kNAT], at_empty[kNAT];
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
@@ -80,16 +86,51 @@ static_assert(sizeof(GSmemBar) <= 512, "barrier block");
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 
+template <bool TWO>
 __device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
-               "r"(ncols)
-               : "memory");
+  if constexpr (TWO) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+  } else {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+                 "r"(ncols)
+                 : "memory");
+  }
 }
+template <bool TWO>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if constexpr (TWO) {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  } else {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
 }
+template <bool TWO>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  if constexpr (TWO) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  } else {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  }
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// all threads of both CTAs of the pair
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// one arrival on the mbarrier at the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ void mbar_arrive_remote(uint64_t *bar, uint32_t rank) {
+  asm volatile(
+    "{\n\t.reg .b32 ra;\n\t"
+    "mapa.shared::cluster.u32 ra, %0, %1;\n\t"
+    "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)),
+    "r"(rank)
+    : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -97,20 +138,53 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem desc]; issued by ONE thread
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                            uint32_t accumulate) {
+// Tiled TMA load whose completion is signalled on the LEADER CTA's mbarrier (the barrier at this
+// shared-memory offset in the even CTA of the pair); the data goes to this CTA's shared memory.
+// No multicast: each CTA fetches its own box.
+__device__ __forceinline__ void tma_load_2d_pair(void *dst_smem, const void *tmap, int x, int y, uint64_t *bar,
+                                                 uint64_t policy) {
+  const uint32_t leader_bar = smem_u32(bar) & 0xFEFFFFFFu;  // bit 24 of a shared::cluster address: CTA rank
   asm volatile(
-    "{\n\t.reg .pred p;\n\t"
-    "setp.ne.b32 p, %4, 0;\n\t"
-    "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-    "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+    "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+    "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(dst_smem)),
+    "l"(tmap), "r"(x), "r"(y), "r"(leader_bar), "l"(policy)
     : "memory");
 }
-// the mbarrier gets one arrival when every MMA issued so far by this thread has completed
+
+// D[tmem] (+)= A[tmem] * B[smem desc]; issued by ONE thread (of the leader CTA for a pair)
+template <bool TWO>
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  if constexpr (TWO) {
+    asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+  } else {
+    asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+  }
+}
+// The mbarrier gets one arrival when every MMA issued so far by this thread has completed; for a
+// pair the arrival is delivered to the barrier at this offset in BOTH CTAs.
+template <bool TWO>
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+  if constexpr (TWO) {
+    asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+        smem_u32(bar)),
+      "h"((uint16_t) 3)
+      : "memory");
+  } else {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+  }
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
@@ -153,8 +227,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void *tile) {
 }
 
 // c = fp32, a = b = fp16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-__host__ __device__ constexpr uint32_t instr_desc_f16(int n) {
-  return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (kBW >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t) (n >> 3) << 17) | ((uint32_t) (m >> 4) << 24);
 }
 
 // Bounded wait that also gives up when another role has raised the abort flag.  The hand-offs
@@ -243,17 +317,18 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw /* words 
 
 // ---------------------------------------------------------------- the kernel
 
-template <int WT, int BT>
+template <int WT, int BT, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
   gemm_tcgen05_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap,
                       const __grid_constant__ CUtensorMap wmap) {
-  using C = GCfg<WT, BT>;
-  static_assert(BT == 128 || BT == 256, "token tile");
+  using C = GCfg<WT, BT, TWO>;
+  static_assert((!TWO && BT == 128) || (TWO && BT == 256), "token tile");
   constexpr int      NX        = C::NX;
   constexpr int      X_BYTES   = C::X_BYTES;
   constexpr int      RAW_BYTES = C::RAW_BYTES;
   constexpr int      RAW_PITCH = (RAW_BYTES + 127) & ~127;
-  constexpr uint32_t IDESC     = instr_desc_f16(BT);
+  constexpr int      ROWS_TILE = TWO ? 2 * kBW : kBW;  // weight rows per (pair) tile
+  constexpr uint32_t IDESC     = instr_desc_f16(ROWS_TILE, BT);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // swizzled operand tiles need 1024-byte alignment in the shared address space
@@ -261,91 +336,83 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t  *sRaw = sX + NX * X_BYTES;
   GSmemBar *bar  = reinterpret_cast<GSmemBar *>(sRaw + 2 * RAW_PITCH);
 
-  const int     warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  volatile int *abort_flag = &bar->abort_flag;
+  const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = TWO ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+  volatile int  *abort_flag = &bar->abort_flag;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NX; ++i) {
       mbar_init(&bar->x_full[i], 1);
       mbar_init(&bar->x_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar->raw_full[i], 1);
-      mbar_init(&bar->raw_empty[i], 4);  // the four warps of the group that reads the stage
-    }
     for (int i = 0; i < kNAT; ++i) {
-      mbar_init(&bar->at_full[i], 128);  // every thread of the writing group
+      // every thread of the writing group, plus (leader of a pair) the four warps of the other CTA's
+      mbar_init(&bar->at_full[i], TWO ? 128 + 4 : 128);
       mbar_init(&bar->at_empty[i], 1);
     }
     mbar_init(&bar->acc_full, 1);
-    mbar_init(&bar->acc_empty, 4);
+    mbar_init(&bar->acc_empty, TWO ? 8 : 4);  // the epilogue warps of every CTA of the tile
     bar->abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 2) {
-    tmem_alloc(&bar->tmem_base, kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<TWO>(&bar->tmem_base, kTmemCols);
+    tmem_relinquish<TWO>();
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (TWO) {
+    cluster_sync_all();  // both CTAs' barriers and tensor memory exist before anyone signals across
+  }
   tc_fence_after();
   const uint32_t tmem_base = bar->tmem_base;
 
-  const int t_tiles = (p.M + BT - 1) / BT;          // token tiles
-  const int w_tiles = (p.N + kBW - 1) / kBW;        // weight-row tiles
+  const int t_tiles = (p.M + BT - 1) / BT;                // token tiles
+  const int w_tiles = (p.N + ROWS_TILE - 1) / ROWS_TILE;  // weight-row tiles
   const int tiles   = t_tiles * w_tiles;
   const int k_raws  = p.K / kKPerRaw;
+  const int worker  = TWO ? (int) (blockIdx.x >> 1) : (int) blockIdx.x;  // CTA, or CTA pair
+  const int workers = TWO ? (int) (gridDim.x >> 1) : (int) gridDim.x;
+  const int row_off = (int) rank * kBW;        // this CTA's weight rows inside the tile
+  const int tok_off = (int) rank * C::XROWS;   // this CTA's tokens inside the activation tile
 
   if (warp == 0) {
-    // ---------------- TMA producer of the activation tiles
+    // ---------------- TMA producer of the activation tiles (this CTA's share of the tokens)
     if (lane == 0) {
       tma_prefetch_descriptor(&xmap);
       const uint64_t pol = l2_policy_evict_last();  // re-read by the other weight-row tiles
       Ring           rx(NX);
       bool           ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int m0 = (t % t_tiles) * BT;
+      for (int t = worker; t < tiles && ok; t += workers) {
+        const int m0 = (t % t_tiles) * BT + tok_off;
         for (int kb = 0; kb < k_raws * kQ; ++kb) {
           ok = wait_or_abort(&bar->x_empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
             break;
           }
-          mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
-          tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+          if constexpr (TWO) {
+            // both halves of the activation tile complete on the leader's barrier
+            if (rank == 0) {
+              mbar_arrive_expect_tx(&bar->x_full[rx.slot], 2 * X_BYTES);
+            }
+            tma_load_2d_pair(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+          } else {
+            mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
+            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+          }
           rx.next();
         }
       }
     }
-  } else if (warp == 3) {
-    // ---------------- TMA producer of the raw weight bytes: its own thread, so that a raw stage is
-    // requested the moment its buffer is released and never queues behind activation loads
-    if (lane == 0) {
-      tma_prefetch_descriptor(&wmap);
-      const uint64_t pol = l2_policy_evict_last();  // re-read by the other token tiles
-      unsigned       gs  = 0;                       // running raw-stage index of this CTA
-      bool           ok  = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int n0 = (t / t_tiles) * kBW;
-        for (int rs = 0; rs < k_raws; ++rs, ++gs) {
-          const int g = gs & 1;
-          ok = wait_or_abort(&bar->raw_empty[g], ((gs >> 1) & 1) ^ 1, abort_flag, p.err, kGemmErrProducer);
-          if (!ok) {
-            break;
-          }
-          mbar_arrive_expect_tx(&bar->raw_full[g], RAW_BYTES);
-          tma_load_2d(sRaw + g * RAW_PITCH, &wmap, rs * (C::RB / 8), n0, &bar->raw_full[g], pol);
-        }
-      }
-    }
   } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
+      // ---------------- MMA issuer (leader CTA)
       Ring     rx(NX);
       unsigned gs = 0;
       int      it = 0;
       bool     ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-        // the single accumulator must have been read out by the epilogue of the previous tile
+      for (int t = worker; t < tiles && ok; t += workers, ++it) {
+        // the accumulator must have been read out by the epilogue(s) of the previous tile
         ok = wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
         if (!ok) {
           break;
@@ -366,15 +433,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int s = 0; s < kBK / 16; ++s) {
               // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
-              umma_f16_ts(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
+              umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
             }
-            umma_commit(&bar->x_empty[rx.slot]);
-            umma_commit(&bar->at_empty[slot]);
+            umma_commit<TWO>(&bar->x_empty[rx.slot]);
+            umma_commit<TWO>(&bar->at_empty[slot]);
             rx.next();
           }
         }
         if (ok) {
-          umma_commit(&bar->acc_full);
+          umma_commit<TWO>(&bar->acc_full);
         }
       }
     }
@@ -383,8 +450,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int q4 = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     int       it = 0;
     bool      ok = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
-      const int n0 = (t / t_tiles) * kBW, m0 = (t % t_tiles) * BT;
+    for (int t = worker; t < tiles && ok; t += workers, ++it) {
+      const int n0 = (t / t_tiles) * ROWS_TILE + row_off, m0 = (t % t_tiles) * BT;
       ok = wait_or_abort(&bar->acc_full, it & 1, abort_flag, p.err, kGemmErrEpilogue);
       if (!ok) {
         break;
@@ -413,77 +480,113 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bar->acc_empty);
+        if (TWO && rank != 0) {
+          mbar_arrive_remote(&bar->acc_empty, 0);  // the leader issues the next tile's first MMA
+        } else {
+          mbar_arrive(&bar->acc_empty);
+        }
       }
     }
   } else if (warp >= kDeqWarp0) {
-    // ---------------- dequantisation: group g, thread = weight row r of the tile
+    // ---------------- dequantisation: group g, thread = weight row r of this CTA's 128 rows.
+    // The thread also FETCHES its row: 9 / 17 asynchronous 16-byte copies (cp.async) per raw stage
+    // into a private 144 / 272-byte slot of shared memory, issued one stage of the group ahead.
+    // (A tiled TMA copy of 128 such short rows was the bottleneck of an earlier version: the copy
+    // engine's cost is per row, about the same for 144 bytes as for a kilobyte.)  Only this thread
+    // reads or writes the slot, so its own wait_group is all the synchronisation the stage needs.
     const int      g     = (warp - kDeqWarp0) >> 2;
     const int      r     = (warp & 3) * 32 + lane;
     const uint32_t tlane = tmem_base + kTmemA + ((uint32_t) ((warp & 3) * 32) << 16);
-    unsigned       gs    = 0;
-    bool           ok    = true;
-    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-      for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
-        if ((int) (gs & 1) != g) {
-          continue;
-        }
-        const int gph = (gs >> 1) & 1;
-        ok = wait_or_abort(&bar->raw_full[g], gph, abort_flag, p.err, kGemmErrDequant);
+    const uint32_t slot_smem = smem_u32(sRaw + g * RAW_PITCH + r * C::RB);
+    const long long row_bytes = (long long) (p.K / 32) * C::BB;
+
+    // this group's stages, in order: running index gs = g, g + 2, ... over (tile, raw stage)
+    int  ft = worker, frs = g;  // (tile, raw stage) of the next stage to FETCH
+    auto normalise = [&](int &t, int &rs) {
+      while (t < tiles && rs >= k_raws) {
+        rs -= k_raws;
+        t += workers;
+      }
+    };
+    auto fetch = [&](int t, int rs) {
+      const long long row = (long long) (t / t_tiles) * ROWS_TILE + row_off + r;
+      const uint32_t  sz  = row < p.N ? 16u : 0u;  // rows past the matrix read as zeros
+      const uint8_t  *src = p.w + (row < p.N ? row : 0) * row_bytes + (long long) rs * C::RB;
+#pragma unroll
+      for (int i = 0; i < C::RW; ++i) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(slot_smem + 16 * i), "l"(src + 16 * i),
+                     "r"(sz)
+                     : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    normalise(ft, frs);
+    if (ft < tiles) {
+      fetch(ft, frs);
+    }
+    int  ct = ft, crs = frs;  // the stage being consumed
+    bool ok = true;
+    while (ct < tiles && ok) {
+      const unsigned gs  = (unsigned) (((ct - worker) / workers) * k_raws + crs);  // running stage index
+      const int      gph = (gs >> 1) & 1;
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      uint32_t raw[C::RW * 4 + 1];
+#pragma unroll
+      for (int i = 0; i < C::RW; ++i) {
+        asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
+                     : "r"(slot_smem + 16 * i)
+                     : "memory");
+      }
+      raw[C::RW * 4] = 0;  // the word past the end is only ever the unused half of a byte_perm
+      // the fp16 values of a K step are computed before waiting for their TMEM slot
+      uint4 out[8];
+      dequant_two_blocks<WT>(raw, 0, out);
+      // Next stage of this group into the same slot.  The copies are issued by the thread that did
+      // the loads above, behind them in the same load/store pipe, and write shared memory only
+      // after a global-memory round trip; the fence keeps the order explicit.
+      ft = ct, frs = crs + 2;
+      normalise(ft, frs);
+      if (ft < tiles) {
+        asm volatile("fence.acq_rel.cta;" ::: "memory");
+        fetch(ft, frs);
+      }
+#pragma unroll
+      for (int q = 0; q < kQ; ++q) {
+        const int slot = g * kQ + q;
+        ok = wait_or_abort(&bar->at_empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
         if (!ok) {
           break;
         }
-        // The row's 144 / 272 raw bytes go to registers with 16-byte loads, LAST chunk first.  The
-        // stage is handed back to the TMA producer as soon as possible, but only after the loads
-        // have RETURNED: an mbarrier arrive does not wait for the thread's outstanding shared-memory
-        // loads (releasing right behind them let the next TMA copy overwrite the chunk loaded
-        // last).  Chunk 0 is therefore loaded last and consumed first, loads of one thread return
-        // in order, and the release follows that first use.
-        uint32_t raw[C::RW * 4 + 1];
-        {
-          const uint32_t src = smem_u32(sRaw + g * RAW_PITCH + r * C::RB);
-#pragma unroll
-          for (int i = C::RW - 1; i >= 0; --i) {
-            asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
-                         : "r"(src + 16 * i)
-                         : "memory");
+        tc_fence_after();
+        tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
+        tc_fence_before();
+        if (TWO && rank != 0) {
+          __syncwarp();  // every lane's store has completed (wait::st above)
+          if (lane == 0) {
+            mbar_arrive_remote(&bar->at_full[slot], 0);  // the MMA is issued by the leader CTA
           }
-        }
-        raw[C::RW * 4] = 0;  // the word past the end is only ever the unused half of a byte_perm
-        // the fp16 values of a K step are computed before waiting for their TMEM slot
-        uint4 out[8];
-        dequant_two_blocks<WT>(raw, 0, out);
-        asm volatile("fence.acq_rel.cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&bar->raw_empty[g]);
-        }
-#pragma unroll
-        for (int q = 0; q < kQ; ++q) {
-          const int slot = g * kQ + q;
-          ok = wait_or_abort(&bar->at_empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
-          if (!ok) {
-            break;
-          }
-          tc_fence_after();
-          tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
-          tc_fence_before();
+        } else {
           mbar_arrive(&bar->at_full[slot]);
-          if (q + 1 < kQ) {
-            dequant_two_blocks<WT>(raw, q + 1, out);
-          }
+        }
+        if (q + 1 < kQ) {
+          dequant_two_blocks<WT>(raw, q + 1, out);
         }
       }
+      ct = ft, crs = frs;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
   }
 
   // ---------------- teardown
   tc_fence_before();
   __syncthreads();
+  if constexpr (TWO) {
+    cluster_sync_all();  // nobody leaves while the other CTA may still signal or read this one
+  }
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc<TWO>(tmem_base, kTmemCols);
   }
 }
 
@@ -505,9 +608,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-template <int WT, int BT>
+template <int WT, int BT, bool TWO>
 cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
-  using C = GCfg<WT, BT>;
+  using C = GCfg<WT, BT, TWO>;
   EncodeTiledFn enc = encode_fn();
   if (!enc) {
     return cudaErrorNotSupported;
@@ -516,7 +619,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   {
     const cuuint64_t gdim[2] = { (cuuint64_t) a.K, (cuuint64_t) a.M };
     const cuuint64_t gstr[1] = { (cuuint64_t) a.K * 2 };
-    const cuuint32_t box[2]  = { kBK, BT };
+    const cuuint32_t box[2]  = { kBK, (cuuint32_t) C::XROWS };
     const cuuint32_t es[2]   = { 1, 1 };
     if (enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a.x), gdim, gstr, box, es,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -537,28 +640,41 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
     }
   }
   const size_t smem = (size_t) C::NX * C::X_BYTES + C::FIXED;
-  auto         kern = gemm_tcgen05_kernel<WT, BT>;
+  auto         kern = gemm_tcgen05_kernel<WT, BT, TWO>;
   cudaError_t  e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
   if (e != cudaSuccess) {
     return e;
   }
-  int grid = ((a.M + BT - 1) / BT) * ((a.N + kBW - 1) / kBW);
-  if (grid > sm_count) {
-    grid = sm_count;
+  const int rows_tile = TWO ? 2 * kBW : kBW;
+  int       workers   = ((a.M + BT - 1) / BT) * ((a.N + rows_tile - 1) / rows_tile);
+  const int max_w     = TWO ? sm_count / 2 : sm_count;
+  if (workers > max_w) {
+    workers = max_w;
   }
-  kern<<<grid, kThreads, smem, stream>>>(a, xmap, wmap);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(TWO ? 2 * workers : workers);
+  cfg.blockDim           = dim3(kThreads);
+  cfg.dynamicSmemBytes   = smem;
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs                = attr;
+  cfg.numAttrs             = TWO ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, a, xmap, wmap);
 }
 
 }  // namespace
 
 cudaError_t gemm_tcgen05_launch(const GemmArgs &args, int wt, int sm_count, cudaStream_t stream) {
-  // token tile: 256 columns of the accumulator, or 128 when there are no more tokens than that
-  const bool bt128 = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
+  // up to 128 tokens: single-CTA tiles of 128 tokens; more: CTA pairs on 256 x 256 tiles
+  const bool one = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
   if (wt == kQ4) {
-    return bt128 ? launch<kQ4, 128>(args, sm_count, stream) : launch<kQ4, 256>(args, sm_count, stream);
+    return one ? launch<kQ4, 128, false>(args, sm_count, stream) : launch<kQ4, 256, true>(args, sm_count, stream);
   }
-  return bt128 ? launch<kQ8, 128>(args, sm_count, stream) : launch<kQ8, 256>(args, sm_count, stream);
+  return one ? launch<kQ8, 128, false>(args, sm_count, stream) : launch<kQ8, 256, true>(args, sm_count, stream);
 }
 
 }  // namespace htp

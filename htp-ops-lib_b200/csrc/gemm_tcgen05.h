@@ -10,6 +10,7 @@ constexpr int kGemmErrProducer = 201;
 constexpr int kGemmErrMma      = 202;
 constexpr int kGemmErrEpilogue = 203;
 constexpr int kGemmErrDequant  = 204;
+constexpr int kGemmErrRelay    = 205;
 
 struct GemmArgs {
   float         *y;  // [M][N] fp32
