@@ -50,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         o = objdir / (s.stem + ".o")
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(s), "-o", str(o)]
+            cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("HTP_OPS_NVCC_FLAGS", "").split(), "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -39,6 +39,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "device_ctx.h"
 #include "ptx.cuh"
@@ -58,7 +59,6 @@ constexpr int kEpiWarp0  = 4;
 constexpr int kDeqWarp0  = 8;    // warps 8-11: group 0, warps 12-15: group 1
 constexpr int kTmemCols  = 512;
 constexpr int kTmemA     = 256;  // first column of the A ring
-constexpr int kMaxNX     = 8;
 constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
 
 template <int WT, int BT, bool TWO>
@@ -70,14 +70,15 @@ struct GCfg {
   static constexpr int X_BYTES   = XROWS * 128;
   static constexpr int RAW_BYTES = kBW * RB;
   static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512;  // raw ring, slack, barriers
-  static constexpr int NX_FIT    = (kSmemLimit - FIXED) / X_BYTES;
-  static constexpr int NX        = NX_FIT > kMaxNX ? kMaxNX : NX_FIT;  // activation stages
-  static_assert(NX >= 3, "activation ring too shallow");
+  static constexpr int NX        = kNAT;  // activation stages: the same ring as the A tiles
+  static_assert(NX * X_BYTES + FIXED <= kSmemLimit, "shared memory");
 };
 
+// One ring of kNAT K steps.  Slot i holds the activation tile (shared memory) and the dequantised
+// weight tile (tensor memory) of one K step; both are filled behind ONE barrier and released by
+// ONE tcgen05.commit, so the MMA issuer waits once and commits once per K step.
 struct GSmemBar {
-  uint64_t x_full[kMaxNX], x_empty[kMaxNX];
-  uint64_t at_full[kNAT], at_empty[kNAT];
+  uint64_t full[kNAT], empty[kNAT];
   uint64_t acc_full, acc_empty;
   uint32_t tmem_base;
   int      abort_flag;
@@ -131,6 +132,16 @@ __device__ __forceinline__ void mbar_arrive_remote(uint64_t *bar, uint32_t rank)
     "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)),
     "r"(rank)
     : "memory");
+}
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+    "{\n\t.reg .pred p;\n\t"
+    "elect.sync _|p, 0xffffffff;\n\t"
+    "selp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -186,23 +197,21 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                  : "memory");
   }
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
-  asm volatile(
-    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-    "%29,%30,%31}, [%32];"
-    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-      "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-      "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-    : "r"(taddr)
-    : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    v[i] = __uint_as_float(r[i]);
-  }
+// 32 columns of this thread's TMEM lane -> 32 registers, asynchronously: the registers hold the
+// values only after tmem_ld_wait on the same array
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
+}
+// Waits for every tcgen05.ld of this thread.  The registers pass through the statement so that
+// the compiler cannot read or move them before the wait.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
 }
 // 32 columns of this thread's TMEM lane <- 32 registers; returns once the store has completed
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&o)[8]) {
@@ -252,6 +261,17 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
   *abort_flag = 1;
   return false;
 }
+
+#ifdef HTP_GEMM_PROF
+__device__ long long g_gemm_prof[32];
+#define PROF_T0() long long _t0 = clock64()
+#define PROF_ADD(i) do { long long _t1 = clock64(); if (blockIdx.x == 0) prof[i] += _t1 - _t0; _t0 = _t1; } while (0)
+#define DBG_SKIP(bit) (p.dbg & (bit))
+#else
+#define PROF_T0()
+#define PROF_ADD(i)
+#define DBG_SKIP(bit) false
+#endif
 
 struct Ring {
   int slot = 0, phase = 0, n;
@@ -341,14 +361,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int  *abort_flag = &bar->abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NX; ++i) {
-      mbar_init(&bar->x_full[i], 1);
-      mbar_init(&bar->x_empty[i], 1);
-    }
     for (int i = 0; i < kNAT; ++i) {
-      // every thread of the writing group, plus (leader of a pair) the four warps of the other CTA's
-      mbar_init(&bar->at_full[i], TWO ? 128 + 4 : 128);
-      mbar_init(&bar->at_empty[i], 1);
+      // the TMA producer's expect_tx arrival and the four warps of the writing group, of both CTAs
+      // for a pair
+      mbar_init(&bar->full[i], TWO ? 1 + 4 + 4 : 1 + 4);
+      mbar_init(&bar->empty[i], 1);  // one tcgen05.commit
     }
     mbar_init(&bar->acc_full, 1);
     mbar_init(&bar->acc_empty, TWO ? 8 : 4);  // the epilogue warps of every CTA of the tile
@@ -386,73 +403,95 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int t = worker; t < tiles && ok; t += workers) {
         const int m0 = (t % t_tiles) * BT + tok_off;
         for (int kb = 0; kb < k_raws * kQ; ++kb) {
-          ok = wait_or_abort(&bar->x_empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
+          ok = wait_or_abort(&bar->empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
             break;
           }
           if constexpr (TWO) {
             // both halves of the activation tile complete on the leader's barrier
             if (rank == 0) {
-              mbar_arrive_expect_tx(&bar->x_full[rx.slot], 2 * X_BYTES);
+              mbar_arrive_expect_tx(&bar->full[rx.slot], 2 * X_BYTES);
             }
-            tma_load_2d_pair(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+            tma_load_2d_pair(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[rx.slot], pol);
           } else {
-            mbar_arrive_expect_tx(&bar->x_full[rx.slot], X_BYTES);
-            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->x_full[rx.slot], pol);
+            mbar_arrive_expect_tx(&bar->full[rx.slot], X_BYTES);
+            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[rx.slot], pol);
           }
           rx.next();
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
-      // ---------------- MMA issuer (leader CTA)
-      Ring     rx(NX);
+    if (rank == 0) {
+      // ---------------- MMA issuer (leader CTA).  The whole warp runs the loop so that control
+      // flow and operands stay warp-uniform; one elected lane issues the tensor-core instructions.
       unsigned gs = 0;
       int      it = 0;
       bool     ok = true;
+#ifdef HTP_GEMM_PROF
+      long long prof[4] = {0, 0, 0, 0};
+#endif
+      PROF_T0();
       for (int t = worker; t < tiles && ok; t += workers, ++it) {
         // the accumulator must have been read out by the epilogue(s) of the previous tile
-        ok = wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
+        ok = DBG_SKIP(8) || wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
+        ok = __all_sync(0xffffffffu, ok);
+        PROF_ADD(0);
         if (!ok) {
           break;
         }
         tc_fence_after();
         for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
           const int g = gs & 1, gph = (gs >> 1) & 1;
+#pragma unroll
           for (int q = 0; q < kQ; ++q) {
             const int slot = g * kQ + q;
-            ok = wait_or_abort(&bar->x_full[rx.slot], rx.phase, abort_flag, p.err, kGemmErrMma) &&
-                 wait_or_abort(&bar->at_full[slot], gph, abort_flag, p.err, kGemmErrMma);
+            ok = wait_or_abort(&bar->full[slot], gph, abort_flag, p.err, kGemmErrMma);
+            ok = __all_sync(0xffffffffu, ok);
+            PROF_ADD(2);
             if (!ok) {
               break;
             }
             tc_fence_after();
-            const uint64_t bdesc  = smem_desc_sw128(sX + rx.slot * X_BYTES);
-            const uint32_t a_tmem = tmem_base + kTmemA + slot * 32;
+            if (elect_one()) {
+              const uint64_t bdesc  = smem_desc_sw128(sX + slot * X_BYTES);
+              const uint32_t a_tmem = tmem_base + kTmemA + slot * 32;
 #pragma unroll
-            for (int s = 0; s < kBK / 16; ++s) {
-              // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
-              umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
+              for (int s = 0; s < kBK / 16; ++s) {
+                // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
+                umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
+              }
+              umma_commit<TWO>(&bar->empty[slot]);
             }
-            umma_commit<TWO>(&bar->x_empty[rx.slot]);
-            umma_commit<TWO>(&bar->at_empty[slot]);
-            rx.next();
+            __syncwarp();
+            PROF_ADD(3);
           }
         }
-        if (ok) {
+        if (ok && elect_one()) {
           umma_commit<TWO>(&bar->acc_full);
         }
+        __syncwarp();
       }
+#ifdef HTP_GEMM_PROF
+      if (blockIdx.x == 0 && lane == 0) {
+        for (int i = 0; i < 4; ++i) g_gemm_prof[i] = prof[i];
+      }
+#endif
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
     // ---------------- epilogue: TMEM -> registers -> y[token][weight row]
     const int q4 = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     int       it = 0;
     bool      ok = true;
+#ifdef HTP_GEMM_PROF
+    long long prof[4] = {0, 0, 0, 0};
+#endif
+    PROF_T0();
     for (int t = worker; t < tiles && ok; t += workers, ++it) {
       const int n0 = (t / t_tiles) * ROWS_TILE + row_off, m0 = (t % t_tiles) * BT;
       ok = wait_or_abort(&bar->acc_full, it & 1, abort_flag, p.err, kGemmErrEpilogue);
+      ok = __all_sync(0xffffffffu, ok);  // tensor-memory loads are warp-wide
+      PROF_ADD(0);
       if (!ok) {
         break;
       }
@@ -460,21 +499,38 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int      col   = n0 + q4 * 32 + lane;  // this thread's output column (weight row)
       const uint32_t taddr = tmem_base + ((uint32_t) (q4 * 32) << 16);
       const bool     col_ok = n0 + q4 * 32 < p.N;  // N is a multiple of 32: a warp is in or out
-#pragma unroll 1
-      for (int c0 = 0; c0 < BT; c0 += 32) {
-        if (m0 + c0 >= p.M) {
-          break;
-        }
-        float v[32];
-        tmem_ld32(taddr + c0, v);
+      // two register buffers: the load of the next 32 tokens is in flight while these are stored
+      uint32_t   va[32], vb[32];
+      const int  m_end = p.M - m0 < BT ? p.M - m0 : BT;  // tokens of this tile inside the matrix
+      auto store32 = [&](int c0, const uint32_t (&v)[32]) {
         if (col_ok) {
           float *dst = p.y + (long long) (m0 + c0) * p.N + col;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            if (m0 + c0 + i < p.M) {
-              dst[(long long) i * p.N] = v[i];  // one 128-byte row segment per warp and token
+            if (c0 + i < m_end) {
+              dst[(long long) i * p.N] = __uint_as_float(v[i]);  // one 128-byte row segment per warp and token
             }
           }
+        }
+      };
+      tmem_ld32_issue(taddr, va);
+#pragma unroll 1
+      for (int c0 = 0; c0 < m_end; c0 += 64) {
+        tmem_ld_wait(va);
+        if (c0 + 32 < m_end) {
+          tmem_ld32_issue(taddr + c0 + 32, vb);
+        }
+        PROF_ADD(1);
+        store32(c0, va);
+        PROF_ADD(2);
+        if (c0 + 32 < m_end) {
+          tmem_ld_wait(vb);
+          if (c0 + 64 < m_end) {
+            tmem_ld32_issue(taddr + c0 + 64, va);
+          }
+          PROF_ADD(1);
+          store32(c0 + 32, vb);
+          PROF_ADD(2);
         }
       }
       tc_fence_before();
@@ -486,18 +542,27 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_arrive(&bar->acc_empty);
         }
       }
+      PROF_ADD(3);
     }
+#ifdef HTP_GEMM_PROF
+    if (blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
+      g_gemm_prof[4] = prof[0], g_gemm_prof[5] = prof[1], g_gemm_prof[6] = prof[2], g_gemm_prof[7] = prof[3];
+    }
+#endif
   } else if (warp >= kDeqWarp0) {
     // ---------------- dequantisation: group g, thread = weight row r of this CTA's 128 rows.
-    // The thread also FETCHES its row: 9 / 17 asynchronous 16-byte copies (cp.async) per raw stage
-    // into a private 144 / 272-byte slot of shared memory, issued one stage of the group ahead.
+    // Each WARP also fetches the raw stages of its own 32 rows (32 x 144 / 272 bytes) with 16-byte
+    // asynchronous copies (cp.async), one stage of the group ahead, into its slice of the group's
+    // buffer; the pieces are taken in linear order (lane after lane along a row, 2-4 rows per warp
+    // instruction) so that one instruction touches a handful of cache lines rather than 32.  Only
+    // the warp itself reads or writes the slice: __syncwarp is all the ordering the stage needs.
     // (A tiled TMA copy of 128 such short rows was the bottleneck of an earlier version: the copy
-    // engine's cost is per row, about the same for 144 bytes as for a kilobyte.)  Only this thread
-    // reads or writes the slot, so its own wait_group is all the synchronisation the stage needs.
+    // engine's cost is per row, about the same for 144 bytes as for a kilobyte.)
     const int      g     = (warp - kDeqWarp0) >> 2;
     const int      r     = (warp & 3) * 32 + lane;
     const uint32_t tlane = tmem_base + kTmemA + ((uint32_t) ((warp & 3) * 32) << 16);
-    const uint32_t slot_smem = smem_u32(sRaw + g * RAW_PITCH + r * C::RB);
+    const uint32_t warp_smem = smem_u32(sRaw + g * RAW_PITCH + (warp & 3) * 32 * C::RB);
+    const uint32_t slot_smem = warp_smem + lane * C::RB;  // this thread's row
     const long long row_bytes = (long long) (p.K / 32) * C::BB;
 
     // this group's stages, in order: running index gs = g, g + 2, ... over (tile, raw stage)
@@ -508,15 +573,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         t += workers;
       }
     };
+    // piece j = 32 i + lane of the warp's stage (i = 0 .. RW - 1) is piece j % RW of row j / RW and
+    // lands at byte 16 j of the slice; row and piece advance incrementally (32 = kA * RW + kB)
+    constexpr int kA = 32 / C::RW, kB = 32 % C::RW;
+    const int     row_first = lane / C::RW, pc_first = lane % C::RW;
     auto fetch = [&](int t, int rs) {
-      const long long row = (long long) (t / t_tiles) * ROWS_TILE + row_off + r;
-      const uint32_t  sz  = row < p.N ? 16u : 0u;  // rows past the matrix read as zeros
-      const uint8_t  *src = p.w + (row < p.N ? row : 0) * row_bytes + (long long) rs * C::RB;
+      const long long row0 = (long long) (t / t_tiles) * ROWS_TILE + row_off + (warp & 3) * 32;
+      if (row0 >= p.N) {
+        return;  // N is a multiple of 32: the warp's rows are all inside or all outside the matrix;
+                 // rows outside are computed on whatever the slice holds and never stored
+      }
+      const uint8_t *src = p.w + (row0 + row_first) * row_bytes + (long long) rs * C::RB + 16 * pc_first;
+      int            pc  = pc_first;
+      uint32_t       dst = warp_smem + 16 * lane;
 #pragma unroll
       for (int i = 0; i < C::RW; ++i) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(slot_smem + 16 * i), "l"(src + 16 * i),
-                     "r"(sz)
-                     : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        const bool wrap = pc + kB >= C::RW;
+        pc += wrap ? kB - C::RW : kB;
+        src += wrap ? (kA + 1) * row_bytes + 16 * (kB - C::RW) : kA * row_bytes + 16 * kB;
+        dst += 512;
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -526,10 +602,20 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     int  ct = ft, crs = frs;  // the stage being consumed
     bool ok = true;
-    while (ct < tiles && ok) {
+#ifdef HTP_GEMM_PROF
+    long long prof[5] = {0, 0, 0, 0, 0};
+#endif
+    PROF_T0();
+    while (ct < tiles) {
       const unsigned gs  = (unsigned) (((ct - worker) / workers) * k_raws + crs);  // running stage index
       const int      gph = (gs >> 1) & 1;
       asm volatile("cp.async.wait_group 0;" ::: "memory");
+      // every lane's pieces of the stage have landed; the warp also leaves TOGETHER here once a
+      // lane has given up a wait
+      if (!__all_sync(0xffffffffu, ok)) {
+        break;
+      }
+      PROF_ADD(0);
       uint32_t raw[C::RW * 4 + 1];
 #pragma unroll
       for (int i = 0; i < C::RW; ++i) {
@@ -547,35 +633,45 @@ __global__ void __launch_bounds__(kThreads, 1)
       // after a global-memory round trip; the fence keeps the order explicit.
       ft = ct, frs = crs + 2;
       normalise(ft, frs);
+      asm volatile("fence.acq_rel.cta;" ::: "memory");
+      __syncwarp();  // every lane has taken its row out of the slice
       if (ft < tiles) {
-        asm volatile("fence.acq_rel.cta;" ::: "memory");
         fetch(ft, frs);
       }
+      PROF_ADD(1);
 #pragma unroll
       for (int q = 0; q < kQ; ++q) {
         const int slot = g * kQ + q;
-        ok = wait_or_abort(&bar->at_empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
-        if (!ok) {
-          break;
-        }
-        tc_fence_after();
-        tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
-        tc_fence_before();
-        if (TWO && rank != 0) {
+        ok = ok && wait_or_abort(&bar->empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
+        PROF_ADD(2);
+        ok = __all_sync(0xffffffffu, ok);  // a warp stores to tensor memory as a whole or not at all
+        if (ok) {
+          tc_fence_after();
+          tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
+          tc_fence_before();
+          PROF_ADD(3);
           __syncwarp();  // every lane's store has completed (wait::st above)
           if (lane == 0) {
-            mbar_arrive_remote(&bar->at_full[slot], 0);  // the MMA is issued by the leader CTA
+            if (TWO && rank != 0) {
+              mbar_arrive_remote(&bar->full[slot], 0);  // the MMA is issued by the leader CTA
+            } else {
+              mbar_arrive(&bar->full[slot]);
+            }
           }
-        } else {
-          mbar_arrive(&bar->at_full[slot]);
         }
         if (q + 1 < kQ) {
           dequant_two_blocks<WT>(raw, q + 1, out);
         }
+        PROF_ADD(4);
       }
       ct = ft, crs = frs;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
+#ifdef HTP_GEMM_PROF
+    if (blockIdx.x == 0 && lane == 0 && (warp == kDeqWarp0 || warp == kDeqWarp0 + 4)) {
+      for (int i = 0; i < 5; ++i) g_gemm_prof[8 + 8 * g + i] = prof[i];
+    }
+#endif
   }
 
   // ---------------- teardown
@@ -668,7 +764,20 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
 
 }  // namespace
 
-cudaError_t gemm_tcgen05_launch(const GemmArgs &args, int wt, int sm_count, cudaStream_t stream) {
+#ifdef HTP_GEMM_PROF
+extern "C" int htp_b200_gemm_prof(long long *out) {
+  return (int) cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 32);
+}
+#endif
+
+cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, cudaStream_t stream) {
+  GemmArgs args = args_in;
+#ifdef HTP_GEMM_PROF
+  {
+    const char *d = getenv("HTP_GEMM_DBG");
+    args.dbg      = d ? atoi(d) : 0;
+  }
+#endif
   // up to 128 tokens: single-CTA tiles of 128 tokens; more: CTA pairs on 256 x 256 tiles
   const bool one = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
   if (wt == kQ4) {

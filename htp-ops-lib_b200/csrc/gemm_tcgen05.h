@@ -18,6 +18,9 @@ struct GemmArgs {
   const uint8_t *w;  // N rows of K/32 blocks
   int            M, N, K;  // K a multiple of 256, N a multiple of 32
   int           *err;      // first error code, 0 when none
+#ifdef HTP_GEMM_PROF
+  int            dbg;      // instrumented builds only: bit mask of waits to skip (timing experiments)
+#endif
 };
 
 cudaError_t gemm_tcgen05_launch(const GemmArgs &args, int wt, int sm_count, cudaStream_t stream);

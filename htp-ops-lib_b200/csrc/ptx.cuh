@@ -129,4 +129,19 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Barrier over `threads` threads that also ANDs a flag: every participant gets true only if every
+// participant passed true.  Lets a group leave a loop together when one member has given up a wait.
+__device__ __forceinline__ bool named_bar_and(int id, int threads, bool flag) {
+  uint32_t out;
+  asm volatile(
+    "{\n\t.reg .pred p, q;\n\t"
+    "setp.ne.u32 q, %3, 0;\n\t"
+    "bar.red.and.pred p, %1, %2, q;\n\t"
+    "selp.u32 %0, 1, 0, p;\n\t}"
+    : "=r"(out)
+    : "r"(id), "r"(threads), "r"((uint32_t) flag)
+    : "memory");
+  return out != 0;
+}
+
 }  // namespace htp
