@@ -59,6 +59,7 @@ constexpr int kEpiWarp0  = 4;
 constexpr int kDeqWarp0  = 8;    // warps 8-11: group 0, warps 12-15: group 1
 constexpr int kTmemCols  = 512;
 constexpr int kTmemA     = 256;  // first column of the A ring
+constexpr int kOutTok    = 16;      // tokens per output store (one TMA box of 32 weight rows x 16 tokens)
 constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
 
 template <int WT, int BT, bool TWO>
@@ -69,7 +70,8 @@ struct GCfg {
   static constexpr int XROWS     = TWO ? BT / 2 : BT;  // activation rows this CTA loads per K step
   static constexpr int X_BYTES   = XROWS * 128;
   static constexpr int RAW_BYTES = kBW * RB;
-  static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512;  // raw ring, slack, barriers
+  static constexpr int STAGE_OUT = 4 * 2 * kOutTok * 32 * 4;  // 4 epilogue warps x 2 buffers x 16 tokens x 32 rows
+  static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512 + STAGE_OUT;  // raw ring, slack, barriers, output staging
   static constexpr int NX        = kNAT;  // activation stages: the same ring as the A tiles
   static_assert(NX * X_BYTES + FIXED <= kSmemLimit, "shared memory");
 };
@@ -197,23 +199,43 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
                  : "memory");
   }
 }
-// 32 columns of this thread's TMEM lane -> 32 registers, asynchronously: the registers hold the
+// 16 columns of this thread's TMEM lane -> 16 registers, asynchronously: the registers hold the
 // values only after tmem_ld_wait on the same array
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                : "r"(taddr)
                : "memory");
 }
 // Waits for every tcgen05.ld of this thread.  The registers pass through the statement so that
 // the compiler cannot read or move them before the wait.
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                :
                : "memory");
 }
-// 32 columns of this thread's TMEM lane <- 32 registers; returns once the store has completed
+// 2-D tiled tensor store shared memory -> global through a tensor map (elements outside the
+// tensor are not written); completion is tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, int x, int y, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(x), "r"(y),
+               "r"(src_smem)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// at most N of this thread's bulk groups still have to READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+// generic-proxy writes to shared memory before this fence are visible to the copy engine after it
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// 32 columns of this thread's TMEM lane <- 32 registers, asynchronously: complete after tmem_st_wait
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&o)[8]) {
   asm volatile(
     "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -224,6 +246,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&o)[8]) {
     "r"(o[4].x), "r"(o[4].y), "r"(o[4].z), "r"(o[4].w), "r"(o[5].x), "r"(o[5].y), "r"(o[5].z), "r"(o[5].w),
     "r"(o[6].x), "r"(o[6].y), "r"(o[6].z), "r"(o[6].w), "r"(o[7].x), "r"(o[7].y), "r"(o[7].z), "r"(o[7].w)
     : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
@@ -286,29 +310,30 @@ struct Ring {
 
 // ---------------------------------------------------------------- dequantisation of one K step
 
-// 64 weights (two blocks) of one row -> eight 16-byte chunks of fp16 (value * scale, rounded once)
+// 64 weights (two blocks) of one row -> eight 16-byte chunks of fp16 (value * scale, rounded once).
+// `raw` holds the words of the row's raw stage; for Q8_0 every word has been XORed with 0x80808080
+// (quant bytes biased to 0..255; the scale halfwords are un-biased again where they are used).
 template <int WT>
-__device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw /* words of the row's raw stage */, int q,
-                                                   uint4 (&out)[8]) {
+__device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw, int q, uint4 (&out)[8]) {
   // block b of the raw stage starts at byte b * BB; its scale is the first halfword
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int      b    = 2 * q + h;
-    const int      off  = b * BlockTraits<WT>::kBytes;  // even, multiple of 4 when b is even
-    const uint32_t sw   = raw[off >> 2];
+    const int      off  = b * BlockTraits<WT>::kBytes;  // even; a multiple of 4 when b is even
+    const uint32_t sw   = raw[off >> 2] ^ (WT == kQ8 ? 0x80808080u : 0u);
     const uint16_t sbit = (off & 2) ? (uint16_t) (sw >> 16) : (uint16_t) (sw & 0xffff);
     const __half2  d2   = __half2half2(__ushort_as_half(sbit));
-    auto           word = [&](int i) -> uint32_t {  // i-th 32-bit word of the block's quants
-      const int o = off + 2 + 4 * i;
-      return (o & 2) ? __byte_perm(raw[o >> 2], raw[(o >> 2) + 1], 0x5432) : raw[o >> 2];
-    };
     if constexpr (WT == kQ4) {
       uint32_t lo[8], hi[8];  // fp16 pairs in element order: lo = elements 0..15, hi = 16..31
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        // bytes (B0, B1, B2, B3) -> (B0, B2, B1, B3): the unpack then yields {B0,B1} and {B2,B3}
-        uint32_t u[4];
-        q4_0_unpack_word(__byte_perm(word(i), 0u, 0x3120), u);
+        // quant bytes (B0, B1, B2, B3) of word i -> (B0, B2, B1, B3), taken straight from the one or
+        // two raw words that hold them; the unpack then yields {B0,B1} and {B2,B3}
+        const int      o = off + 2 + 4 * i;
+        const uint32_t w = (o & 2) ? __byte_perm(raw[o >> 2], raw[(o >> 2) + 1], 0x5342)
+                                   : __byte_perm(raw[o >> 2], 0u, 0x3120);
+        uint32_t       u[4];
+        q4_0_unpack_word(w, u);
         lo[2 * i]     = h2_as_u32(__hmul2(u32_as_h2(u[0]), d2));
         lo[2 * i + 1] = h2_as_u32(__hmul2(u32_as_h2(u[1]), d2));
         hi[2 * i]     = h2_as_u32(__hmul2(u32_as_h2(u[2]), d2));
@@ -319,13 +344,15 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw /* words 
       out[4 * h + 2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
       out[4 * h + 3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
     } else {
-      uint32_t v[16];
+      // elements 2p, 2p + 1 are two adjacent bytes of ONE raw word (the quants start on an even
+      // byte): 0x6400 | (byte + 128) = 1024 + 128 + value, exact in fp16
+      const __half2 k1152 = u32_as_h2(0x64806480u);
+      uint32_t      v[16];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        uint32_t u[2];
-        q8_0_unpack_word(word(i), u);
-        v[2 * i]     = h2_as_u32(__hmul2(u32_as_h2(u[0]), d2));
-        v[2 * i + 1] = h2_as_u32(__hmul2(u32_as_h2(u[1]), d2));
+      for (int pr = 0; pr < 16; ++pr) {
+        const int      o  = off + 2 + 2 * pr;
+        const uint32_t hh = __byte_perm(raw[o >> 2], 0x64646464u, (o & 2) ? 0x4342 : 0x4140);
+        v[pr]             = h2_as_u32(__hmul2(__hsub2(u32_as_h2(hh), k1152), d2));
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -340,7 +367,7 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw /* words 
 template <int WT, int BT, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
   gemm_tcgen05_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap,
-                      const __grid_constant__ CUtensorMap wmap) {
+                      const __grid_constant__ CUtensorMap ymap) {
   using C = GCfg<WT, BT, TWO>;
   static_assert((!TWO && BT == 128) || (TWO && BT == 256), "token tile");
   constexpr int      NX        = C::NX;
@@ -355,6 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t  *sX   = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t  *sRaw = sX + NX * X_BYTES;
   GSmemBar *bar  = reinterpret_cast<GSmemBar *>(sRaw + 2 * RAW_PITCH);
+  uint8_t  *sOut = sRaw + 2 * RAW_PITCH + 512;  // output staging, 128-byte aligned
 
   const int      warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = TWO ? cluster_ctarank() : 0u;  // 0 = leader of the pair
@@ -479,10 +507,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
-    // ---------------- epilogue: TMEM -> registers -> y[token][weight row]
+    // ---------------- epilogue: TMEM -> registers -> shared memory -> y[token][weight row].
+    // Each warp drains its 32 TMEM lanes (weight rows) 16 tokens at a time into a private
+    // [16 tokens][32 rows] staging buffer (two of them, alternating) and hands the buffer to the
+    // copy engine as one tiled store; the accumulator is released as soon as the last load has
+    // completed, the stores drain while the next tile is being computed.
     const int q4 = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. + 31
     int       it = 0;
     bool      ok = true;
+    unsigned  nbuf = 0;  // running count of staged chunks: buffer = nbuf & 1
+    const uint32_t stage0 = smem_u32(sOut + q4 * (2 * kOutTok * 128));
+    if (lane == 0) {
+      tma_prefetch_descriptor(&ymap);
+    }
 #ifdef HTP_GEMM_PROF
     long long prof[4] = {0, 0, 0, 0};
 #endif
@@ -496,53 +533,68 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tc_fence_after();
-      const int      col   = n0 + q4 * 32 + lane;  // this thread's output column (weight row)
-      const uint32_t taddr = tmem_base + ((uint32_t) (q4 * 32) << 16);
-      const bool     col_ok = n0 + q4 * 32 < p.N;  // N is a multiple of 32: a warp is in or out
-      // two register buffers: the load of the next 32 tokens is in flight while these are stored
-      uint32_t   va[32], vb[32];
-      const int  m_end = p.M - m0 < BT ? p.M - m0 : BT;  // tokens of this tile inside the matrix
-      auto store32 = [&](int c0, const uint32_t (&v)[32]) {
-        if (col_ok) {
-          float *dst = p.y + (long long) (m0 + c0) * p.N + col;
+      const int      col0   = n0 + q4 * 32;  // first output column (weight row) of this warp
+      const uint32_t taddr  = tmem_base + ((uint32_t) (q4 * 32) << 16);
+      const bool     col_ok = col0 < p.N;  // N is a multiple of 32: a warp is in or out
+      const int      m_end  = p.M - m0 < BT ? p.M - m0 : BT;  // tokens of this tile inside the matrix
+      uint32_t       va[16], vb[16];
+      // v = tokens c0 .. c0 + 15 of this thread's row; tokens past M are cut off by the tensor map
+      auto store16 = [&](int c0, const uint32_t (&v)[16]) {
+        const uint32_t buf = stage0 + (nbuf & 1) * (kOutTok * 128);
+        ++nbuf;
+        if (lane == 0) {
+          bulk_wait_read<1>();  // the store that last used this buffer has read it
+        }
+        __syncwarp();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (c0 + i < m_end) {
-              dst[(long long) i * p.N] = __uint_as_float(v[i]);  // one 128-byte row segment per warp and token
-            }
+        for (int i = 0; i < 16; ++i) {
+          asm volatile("st.shared.b32 [%0], %1;" ::"r"(buf + i * 128 + lane * 4), "r"(v[i]) : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && col_ok && !DBG_SKIP(4)) {
+          tma_store_2d(&ymap, col0, m0 + c0, buf);
+        }
+      };
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (TWO && rank != 0) {
+            mbar_arrive_remote(&bar->acc_empty, 0);  // the leader issues the next tile's first MMA
+          } else {
+            mbar_arrive(&bar->acc_empty);
           }
         }
       };
-      tmem_ld32_issue(taddr, va);
+      tmem_ld16_issue(taddr, va);
 #pragma unroll 1
-      for (int c0 = 0; c0 < m_end; c0 += 64) {
+      for (int c0 = 0; c0 < m_end; c0 += 32) {
         tmem_ld_wait(va);
-        if (c0 + 32 < m_end) {
-          tmem_ld32_issue(taddr + c0 + 32, vb);
+        if (c0 + 16 < m_end) {
+          tmem_ld16_issue(taddr + c0 + 16, vb);
+        } else {
+          release_acc();
         }
         PROF_ADD(1);
-        store32(c0, va);
+        store16(c0, va);
         PROF_ADD(2);
-        if (c0 + 32 < m_end) {
+        if (c0 + 16 < m_end) {
           tmem_ld_wait(vb);
-          if (c0 + 64 < m_end) {
-            tmem_ld32_issue(taddr + c0 + 64, va);
+          if (c0 + 32 < m_end) {
+            tmem_ld16_issue(taddr + c0 + 32, va);
+          } else {
+            release_acc();
           }
           PROF_ADD(1);
-          store32(c0 + 32, vb);
+          store16(c0 + 16, vb);
           PROF_ADD(2);
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (TWO && rank != 0) {
-          mbar_arrive_remote(&bar->acc_empty, 0);  // the leader issues the next tile's first MMA
-        } else {
-          mbar_arrive(&bar->acc_empty);
-        }
-      }
       PROF_ADD(3);
+    }
+    if (lane == 0) {
+      bulk_wait_all();  // the staging buffers stay valid until the copy engine is done with them
     }
 #ifdef HTP_GEMM_PROF
     if (blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
@@ -624,16 +676,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                      : "r"(slot_smem + 16 * i)
                      : "memory");
       }
+      if constexpr (WT == kQ8) {
+#pragma unroll
+        for (int i = 0; i < C::RW * 4; ++i) {
+          raw[i] ^= 0x80808080u;  // quant bytes biased to 0..255, once per word
+        }
+      }
       raw[C::RW * 4] = 0;  // the word past the end is only ever the unused half of a byte_perm
       // the fp16 values of a K step are computed before waiting for their TMEM slot
       uint4 out[8];
       dequant_two_blocks<WT>(raw, 0, out);
-      // Next stage of this group into the same slot.  The copies are issued by the thread that did
-      // the loads above, behind them in the same load/store pipe, and write shared memory only
-      // after a global-memory round trip; the fence keeps the order explicit.
+      // Next stage of this group into the same slice.
       ft = ct, frs = crs + 2;
       normalise(ft, frs);
-      asm volatile("fence.acq_rel.cta;" ::: "memory");
+      // The loads above are volatile (they stay where they are written) and the copies below go
+      // down the same in-order load/store pipe behind them, writing shared memory only after a
+      // global-memory round trip.
       __syncwarp();  // every lane has taken its row out of the slice
       if (ft < tiles) {
         fetch(ft, frs);
@@ -648,6 +706,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (ok) {
           tc_fence_after();
           tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
+#ifdef HTP_GEMM_DEFER_ST
+          if (q + 1 < kQ) {
+            dequant_two_blocks<WT>(raw, q + 1, out);  // overlaps the store
+          }
+#endif
+          tmem_st_wait();
           tc_fence_before();
           PROF_ADD(3);
           __syncwarp();  // every lane's store has completed (wait::st above)
@@ -659,9 +723,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
+#ifndef HTP_GEMM_DEFER_ST
         if (q + 1 < kQ) {
           dequant_two_blocks<WT>(raw, q + 1, out);
         }
+#endif
         PROF_ADD(4);
       }
       ct = ft, crs = frs;
@@ -711,7 +777,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   if (!enc) {
     return cudaErrorNotSupported;
   }
-  CUtensorMap xmap, wmap;
+  CUtensorMap xmap, ymap;
   {
     const cuuint64_t gdim[2] = { (cuuint64_t) a.K, (cuuint64_t) a.M };
     const cuuint64_t gstr[1] = { (cuuint64_t) a.K * 2 };
@@ -724,14 +790,13 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
     }
   }
   {
-    const cuuint64_t row_bytes = (cuuint64_t) (a.K / 32) * C::BB;
-    const cuuint64_t gdim[2]   = { row_bytes / 8, (cuuint64_t) a.N };
-    const cuuint64_t gstr[1]   = { row_bytes };
-    const cuuint32_t box[2]    = { C::RB / 8, kBW };
-    const cuuint32_t es[2]     = { 1, 1 };
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstr, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    // output y[M][N] fp32, stored in boxes of 32 weight rows (128 bytes) x 16 tokens
+    const cuuint64_t gdim[2] = { (cuuint64_t) a.N, (cuuint64_t) a.M };
+    const cuuint64_t gstr[1] = { (cuuint64_t) a.N * 4 };
+    const cuuint32_t box[2]  = { 32, kOutTok };
+    const cuuint32_t es[2]   = { 1, 1 };
+    if (enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a.y, gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
       return cudaErrorInvalidValue;
     }
   }
@@ -759,7 +824,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs                = attr;
   cfg.numAttrs             = TWO ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, a, xmap, wmap);
+  return cudaLaunchKernelEx(&cfg, kern, a, xmap, ymap);
 }
 
 }  // namespace
