@@ -11,6 +11,7 @@ struct StreamScratch {
   float    *partials = nullptr;  // [kGemvMaxGrid][2][256]
   unsigned *counters = nullptr;  // [kGemvMaxGrid], zero between launches
   int      *err      = nullptr;  // first kernel error code
+  float    *gemm_part = nullptr;  // split-tile scratch of the prefill GEMM, allocated on its first use
 };
 
 struct DeviceCtx {
@@ -50,6 +51,7 @@ extern int      g_opt_pdl;
 extern int      g_opt_force_generic;
 extern int      g_opt_gemm_min_m;
 extern int      g_opt_gemm_tile_n;
+extern int      g_opt_gemm_split;
 void            count_launch(int n = 1);
 
 }  // namespace htp

@@ -17,23 +17,31 @@
 // tcgen05.mma.cta_group::1.  M > 128: persistent CTA PAIRS (a cluster of two SMs), pair tile = 256
 // weight rows x 256 tokens, tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 16): each CTA dequantises
 // its own 128 weight rows into its own tensor memory and loads only ITS half (128 tokens) of the
-// activation tile - the tensor cores of both SMs read both halves - which halves the activation
-// re-reads through L2, the bound of the one-CTA version.  No multicast loads: every CTA fetches its
-// own operands; only tcgen05.commit multicasts its mbarrier arrival to the pair.
+// activation tile - the tensor cores of both SMs read both halves.  No multicast loads: every CTA
+// fetches its own operands; the other CTA's copy engine and dequantisation warps signal the
+// leader's barriers directly, and tcgen05.commit multicasts its arrival to the pair.
 //
-// Roles per CTA, K in steps of 64:
-//   warp 0      TMA producer of the activation tile (BT x 64 fp16, 128-byte swizzle), one per K step
-//   warp 1      MMA issuer (in a pair: only in the leader CTA, whose barriers also collect the other
-//               CTA's TMA completions and tensor-memory stores)
-//   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 an 8-stage ring of A tiles
-//   warps 4-7   epilogue: tcgen05.ld of the accumulator, fp32 stores to y[token][weight row]
+// K advances in steps of 64 through ONE ring of 8 slots; slot i holds the activation tile
+// (shared memory) and the dequantised weight tile (32 TMEM columns) of one K step, filled behind
+// one `full` barrier and released by one tcgen05.commit on one `empty` barrier.
+//
+// Roles per CTA:
+//   warp 0      TMA producer of the activation tile (128 tokens x 64 fp16, 128-byte swizzle)
+//   warp 1      MMA issuer (leader CTA of a pair only): the whole warp runs the loop, one elected
+//               lane issues; one wait, four MMAs and one commit per K step
+//   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 the ring of A tiles
+//   warps 4-7   epilogue: tcgen05.ld of the accumulator 16 tokens at a time -> shared-memory
+//               staging -> TMA store to y[token][weight row]; the accumulator is released after
+//               the last load, the stores drain under the next tile
 //   warps 8-15  dequantisation, two groups of four warps; group g takes the raw stages (256 weights
-//               per row) whose running index is g (mod 2).  Thread = one weight row: it fetches its
-//               144 / 272 raw bytes itself (cp.async, one stage ahead), moves them to registers
-//               with 9 / 17 conflict-free 16-byte loads, then per K step converts 64 weights to
-//               fp16 and stores them as 32 TMEM columns of its lane
+//               per row) whose running index is g (mod 2).  A warp fetches the 144 / 272 raw bytes
+//               of its 32 rows itself (coalesced cp.async, one stage ahead); thread = one weight
+//               row: 9 / 17 conflict-free 16-byte loads to registers, then per K step 64 weights to
+//               fp16 (value * scale, rounded once) stored as 32 TMEM columns of its lane
+// Optionally (off by default) tiles that do not divide among the SMs are cut into equal K ranges
+// and finished through a global scratch tile.
 // All waits are bounded; a wait that runs out records an error code, raises the CTA's abort flag
-// and every role leaves its loop; TMEM is freed before the CTA exits.  No cluster, no multicast.
+// and every role leaves its loop; TMEM is freed before the CTA exits.
 #include "gemm_tcgen05.h"
 
 #include <cuda.h>
@@ -61,6 +69,7 @@ constexpr int kTmemCols  = 512;
 constexpr int kTmemA     = 256;  // first column of the A ring
 constexpr int kOutTok    = 16;      // tokens per output store (one TMA box of 32 weight rows x 16 tokens)
 constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
+constexpr uint32_t kFlagWaitCap = 1u << 22;  // polls of the other contributor's flag (about a second)
 
 template <int WT, int BT, bool TWO>
 struct GCfg {
@@ -367,7 +376,7 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw, int q, u
 template <int WT, int BT, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
   gemm_tcgen05_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap,
-                      const __grid_constant__ CUtensorMap ymap) {
+                      const __grid_constant__ CUtensorMap ymap, const __grid_constant__ CUtensorMap pmap) {
   using C = GCfg<WT, BT, TWO>;
   static_assert((!TWO && BT == 128) || (TWO && BT == 256), "token tile");
   constexpr int      NX        = C::NX;
@@ -420,6 +429,44 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int workers = TWO ? (int) (gridDim.x >> 1) : (int) gridDim.x;
   const int row_off = (int) rank * kBW;        // this CTA's weight rows inside the tile
   const int tok_off = (int) rank * C::XROWS;   // this CTA's tokens inside the activation tile
+  // Work is counted in STAGES of one raw stage (256 of K) of one tile.  A worker first takes whole
+  // tiles, interleaved with the other workers' (tile = i * workers + worker: neighbours work on
+  // neighbouring tiles at the same time, which share weight rows or activations in L2).  When
+  // the tiles do not divide evenly among the workers (p.split) only all but the last FULL wave is
+  // handed out that way; the remaining tiles (between one and two per worker) are laid end to end
+  // and cut into `workers` contiguous ranges of equal length, anywhere inside a tile.  A tile cut
+  // in two has two contributors - the worker whose range ENDS in it (it has the head of the tile's
+  // K range and reaches it last) and the next worker, whose range STARTS in it (the tail of K,
+  // done first) - and the second hands its partial sums to the first through global scratch.  A
+  // range is at least one tile long, so no tile has more than two contributors.
+  const int dp_tiles  = p.split ? tiles / workers - 1 : (tiles - worker + workers - 1) / workers;  // whole tiles first
+  const int dp_stages = dp_tiles * k_raws;
+  const int sk_tile0  = dp_tiles * workers;  // first tile of the part that is cut into ranges
+  int       sk_begin = 0, sk_end = 0;        // this worker's range of that part, in stages
+  if (p.split) {
+    const long long sk_stages = (long long) (tiles - sk_tile0) * k_raws;
+    sk_begin = (int) (sk_stages * worker / workers);
+    sk_end   = (int) (sk_stages * (worker + 1) / workers);
+  }
+  const int n_stages = dp_stages + (sk_end - sk_begin);  // stages this worker goes through, in order
+  // stage li of this worker -> (tile, raw stage of the tile)
+  auto stage_at = [&](int li, int &t, int &rs) {
+    if (li < dp_stages) {
+      const int i = li / k_raws;
+      rs = li - i * k_raws;
+      t  = i * workers + worker;
+    } else {
+      const int u = sk_begin + (li - dp_stages), tt = u / k_raws;
+      rs = u - tt * k_raws;
+      t  = sk_tile0 + tt;
+    }
+  };
+  // segment = the stages of ONE tile that follow each other in this worker's order: stages
+  // rs0 .. rs1 - 1 of tile t, starting at the worker's stage li
+  auto segment = [&](int li, int &t, int &rs0, int &rs1) {
+    stage_at(li, t, rs0);
+    rs1 = rs0 + (n_stages - li) < k_raws ? rs0 + (n_stages - li) : k_raws;
+  };
 
   if (warp == 0) {
     // ---------------- TMA producer of the activation tiles (this CTA's share of the tokens)
@@ -428,9 +475,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint64_t pol = l2_policy_evict_last();  // re-read by the other weight-row tiles
       Ring           rx(NX);
       bool           ok = true;
-      for (int t = worker; t < tiles && ok; t += workers) {
+      for (int li = 0; li < n_stages && ok;) {
+        int t, rs0, rs1;
+        segment(li, t, rs0, rs1);
+        li += rs1 - rs0;
         const int m0 = (t % t_tiles) * BT + tok_off;
-        for (int kb = 0; kb < k_raws * kQ; ++kb) {
+        for (int kb = rs0 * kQ; kb < rs1 * kQ; ++kb) {
           ok = wait_or_abort(&bar->empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
             break;
@@ -460,8 +510,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       long long prof[4] = {0, 0, 0, 0};
 #endif
       PROF_T0();
-      for (int t = worker; t < tiles && ok; t += workers, ++it) {
-        // the accumulator must have been read out by the epilogue(s) of the previous tile
+      for (int li = 0; li < n_stages && ok; ++it) {
+        int t, rs0, rs1;
+        segment(li, t, rs0, rs1);
+        li += rs1 - rs0;
+        // the accumulator must have been read out by the epilogue(s) of the previous segment
         ok = DBG_SKIP(8) || wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
         ok = __all_sync(0xffffffffu, ok);
         PROF_ADD(0);
@@ -469,7 +522,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           break;
         }
         tc_fence_after();
-        for (int rs = 0; rs < k_raws && ok; ++rs, ++gs) {
+        for (int rs = rs0; rs < rs1 && ok; ++rs, ++gs) {
           const int g = gs & 1, gph = (gs >> 1) & 1;
 #pragma unroll
           for (int q = 0; q < kQ; ++q) {
@@ -487,7 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int s = 0; s < kBK / 16; ++s) {
                 // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
-                umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, (rs | q | s) ? 1u : 0u);
+                umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, ((rs - rs0) | q | s) ? 1u : 0u);
               }
               umma_commit<TWO>(&bar->empty[slot]);
             }
@@ -524,7 +577,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     long long prof[4] = {0, 0, 0, 0};
 #endif
     PROF_T0();
-    for (int t = worker; t < tiles && ok; t += workers, ++it) {
+    for (int li = 0; li < n_stages && ok; ++it) {
+      int t, rs0, rs1;
+      segment(li, t, rs0, rs1);
+      li += rs1 - rs0;
+      // whole tile: store y.  Tail of the K range (the other contributor finishes the tile): store
+      // the partial sums to this worker's scratch tile and raise this warp's flag.  Head of the K
+      // range: wait for the flag of the next worker's same warp, add its partial sums, store y.
+      const bool is_tail = rs0 > 0, is_head = rs0 == 0 && rs1 < k_raws;
       const int n0 = (t / t_tiles) * ROWS_TILE + row_off, m0 = (t % t_tiles) * BT;
       ok = wait_or_abort(&bar->acc_full, it & 1, abort_flag, p.err, kGemmErrEpilogue);
       ok = __all_sync(0xffffffffu, ok);  // tensor-memory loads are warp-wide
@@ -537,9 +597,52 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t taddr  = tmem_base + ((uint32_t) (q4 * 32) << 16);
       const bool     col_ok = col0 < p.N;  // N is a multiple of 32: a warp is in or out
       const int      m_end  = p.M - m0 < BT ? p.M - m0 : BT;  // tokens of this tile inside the matrix
-      uint32_t       va[16], vb[16];
+      const float   *other  = nullptr;  // the other contributor's partial sums of this thread's row
+      int           *flag   = nullptr;
+      if (is_head) {
+        flag  = p.flags + ((worker + 1) * 2 + (int) rank) * 4 + q4;
+        other = p.part + (size_t) (worker + 1) * BT * ROWS_TILE + row_off + q4 * 32 + lane;
+        bool seen = false;
+        for (uint32_t i = 0; i < kFlagWaitCap && !seen; ++i) {
+          int f;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
+          seen = f != 0;
+          if (!seen) {
+            if (*abort_flag) {
+              break;
+            }
+            __nanosleep(256);
+          }
+        }
+        if (!seen) {
+          atomicCAS(p.err, 0, kGemmErrFixup);
+          *abort_flag = 1;
+        }
+        ok = __all_sync(0xffffffffu, seen);
+        if (!ok) {
+          break;  // (the accumulator is not released: every other role runs into the abort flag)
+        }
+      }
+      uint32_t va[16], vb[16];
       // v = tokens c0 .. c0 + 15 of this thread's row; tokens past M are cut off by the tensor map
-      auto store16 = [&](int c0, const uint32_t (&v)[16]) {
+      // (the other contributor's sums of a chunk are requested one chunk ahead, with the chunk's
+      // tensor-memory load)
+      float adda[16], addb[16];
+      auto  load_other = [&](int c0, float (&add)[16]) {
+        if (is_head) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            add[i] = __ldcg(other + (size_t) (c0 + i) * ROWS_TILE);
+          }
+        }
+      };
+      auto store16 = [&](int c0, uint32_t (&v)[16], const float (&add)[16]) {
+        if (is_head) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            v[i] = __float_as_uint(__uint_as_float(v[i]) + add[i]);
+          }
+        }
         const uint32_t buf = stage0 + (nbuf & 1) * (kOutTok * 128);
         ++nbuf;
         if (lane == 0) {
@@ -552,8 +655,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && col_ok && !DBG_SKIP(4)) {
-          tma_store_2d(&ymap, col0, m0 + c0, buf);
+        if (lane == 0 && !DBG_SKIP(4)) {
+          if (is_tail) {
+            tma_store_2d(&pmap, row_off + q4 * 32, worker * BT + c0, buf);
+          } else if (col_ok) {
+            tma_store_2d(&ymap, col0, m0 + c0, buf);
+          }
         }
       };
       auto release_acc = [&]() {
@@ -561,34 +668,53 @@ __global__ void __launch_bounds__(kThreads, 1)
         __syncwarp();
         if (lane == 0) {
           if (TWO && rank != 0) {
-            mbar_arrive_remote(&bar->acc_empty, 0);  // the leader issues the next tile's first MMA
+            mbar_arrive_remote(&bar->acc_empty, 0);  // the leader issues the next segment's first MMA
           } else {
             mbar_arrive(&bar->acc_empty);
           }
         }
       };
       tmem_ld16_issue(taddr, va);
+      load_other(0, adda);
 #pragma unroll 1
       for (int c0 = 0; c0 < m_end; c0 += 32) {
         tmem_ld_wait(va);
         if (c0 + 16 < m_end) {
           tmem_ld16_issue(taddr + c0 + 16, vb);
+          load_other(c0 + 16, addb);
         } else {
           release_acc();
         }
         PROF_ADD(1);
-        store16(c0, va);
+        store16(c0, va, adda);
         PROF_ADD(2);
         if (c0 + 16 < m_end) {
           tmem_ld_wait(vb);
           if (c0 + 32 < m_end) {
             tmem_ld16_issue(taddr + c0 + 32, va);
+            load_other(c0 + 32, adda);
           } else {
             release_acc();
           }
           PROF_ADD(1);
-          store16(c0 + 16, vb);
+          store16(c0 + 16, vb, addb);
           PROF_ADD(2);
+        }
+      }
+      if (is_tail) {
+        // the partial sums are in global memory before the flag is: the stores have completed
+        // (wait_group), the copy engine's writes are ordered before this thread's release
+        if (lane == 0) {
+          bulk_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + (worker * 2 + (int) rank) * 4 + q4), "r"(1)
+                       : "memory");
+        }
+      } else if (is_head) {
+        __syncwarp();
+        if (lane == 0) {
+          *flag = 0;  // ready for the next launch on this stream
         }
       }
       PROF_ADD(3);
@@ -617,19 +743,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t slot_smem = warp_smem + lane * C::RB;  // this thread's row
     const long long row_bytes = (long long) (p.K / 32) * C::BB;
 
-    // this group's stages, in order: running index gs = g, g + 2, ... over (tile, raw stage)
-    int  ft = worker, frs = g;  // (tile, raw stage) of the next stage to FETCH
-    auto normalise = [&](int &t, int &rs) {
-      while (t < tiles && rs >= k_raws) {
-        rs -= k_raws;
-        t += workers;
-      }
-    };
+    // this group's stages: g, g + 2, ... of the worker's order
     // piece j = 32 i + lane of the warp's stage (i = 0 .. RW - 1) is piece j % RW of row j / RW and
     // lands at byte 16 j of the slice; row and piece advance incrementally (32 = kA * RW + kB)
     constexpr int kA = 32 / C::RW, kB = 32 % C::RW;
     const int     row_first = lane / C::RW, pc_first = lane % C::RW;
-    auto fetch = [&](int t, int rs) {
+    auto fetch = [&](int li) {
+      int t, rs;
+      stage_at(li, t, rs);
       const long long row0 = (long long) (t / t_tiles) * ROWS_TILE + row_off + (warp & 3) * 32;
       if (row0 >= p.N) {
         return;  // N is a multiple of 32: the warp's rows are all inside or all outside the matrix;
@@ -648,18 +769,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    normalise(ft, frs);
-    if (ft < tiles) {
-      fetch(ft, frs);
+    if (g < n_stages) {
+      fetch(g);
     }
-    int  ct = ft, crs = frs;  // the stage being consumed
     bool ok = true;
 #ifdef HTP_GEMM_PROF
     long long prof[5] = {0, 0, 0, 0, 0};
 #endif
     PROF_T0();
-    while (ct < tiles) {
-      const unsigned gs  = (unsigned) (((ct - worker) / workers) * k_raws + crs);  // running stage index
+    for (int li = g; li < n_stages; li += 2) {
+      const unsigned gs  = (unsigned) li;  // running stage index
       const int      gph = (gs >> 1) & 1;
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       // every lane's pieces of the stage have landed; the warp also leaves TOGETHER here once a
@@ -687,14 +806,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint4 out[8];
       dequant_two_blocks<WT>(raw, 0, out);
       // Next stage of this group into the same slice.
-      ft = ct, frs = crs + 2;
-      normalise(ft, frs);
       // The loads above are volatile (they stay where they are written) and the copies below go
       // down the same in-order load/store pipe behind them, writing shared memory only after a
       // global-memory round trip.
       __syncwarp();  // every lane has taken its row out of the slice
-      if (ft < tiles) {
-        fetch(ft, frs);
+      if (li + 2 < n_stages) {
+        fetch(li + 2);
       }
       PROF_ADD(1);
 #pragma unroll
@@ -730,7 +847,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
         PROF_ADD(4);
       }
-      ct = ft, crs = frs;
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #ifdef HTP_GEMM_PROF
@@ -750,6 +866,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     tmem_dealloc<TWO>(tmem_base, kTmemCols);
   }
+}
+
+// one partial tile per worker: 74 pairs x 256 x 256 or 148 CTAs x 128 x 128 floats
+size_t gemm_part_bytes(int sm_count) {
+  const size_t pair = (size_t) (sm_count / 2) * 256 * 256 * 4, one = (size_t) sm_count * 128 * 128 * 4;
+  return pair > one ? pair : one;
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -800,17 +922,31 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
       return cudaErrorInvalidValue;
     }
   }
+  const int rows_tile = TWO ? 2 * kBW : kBW;
+  const int tiles     = ((a.M + BT - 1) / BT) * ((a.N + rows_tile - 1) / rows_tile);
+  const int max_w     = TWO ? sm_count / 2 : sm_count;
+  const int workers   = tiles < max_w ? tiles : max_w;
+  GemmArgs  args      = a;
+  // uneven tile counts: cut the work into equal ranges (needs the scratch)
+  args.split = (a.part != nullptr && tiles > workers && tiles % workers != 0) ? 1 : 0;
+  args.flags = a.part ? reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(a.part) + gemm_part_bytes(sm_count)) : nullptr;
+  CUtensorMap pmap = ymap;
+  if (args.split) {
+    // partial tiles: [worker][token][weight row of the tile] fp32, stored in the same boxes as y
+    const cuuint64_t gdim[2] = { (cuuint64_t) rows_tile, (cuuint64_t) BT * workers };
+    const cuuint64_t gstr[1] = { (cuuint64_t) rows_tile * 4 };
+    const cuuint32_t box[2]  = { 32, kOutTok };
+    const cuuint32_t es[2]   = { 1, 1 };
+    if (enc(&pmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a.part, gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      return cudaErrorInvalidValue;
+    }
+  }
   const size_t smem = (size_t) C::NX * C::X_BYTES + C::FIXED;
   auto         kern = gemm_tcgen05_kernel<WT, BT, TWO>;
   cudaError_t  e    = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);
   if (e != cudaSuccess) {
     return e;
-  }
-  const int rows_tile = TWO ? 2 * kBW : kBW;
-  int       workers   = ((a.M + BT - 1) / BT) * ((a.N + rows_tile - 1) / rows_tile);
-  const int max_w     = TWO ? sm_count / 2 : sm_count;
-  if (workers > max_w) {
-    workers = max_w;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim            = dim3(TWO ? 2 * workers : workers);
@@ -824,7 +960,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs                = attr;
   cfg.numAttrs             = TWO ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, a, xmap, ymap);
+  return cudaLaunchKernelEx(&cfg, kern, args, xmap, ymap, pmap);
 }
 
 }  // namespace
@@ -834,6 +970,10 @@ extern "C" int htp_b200_gemm_prof(long long *out) {
   return (int) cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 32);
 }
 #endif
+
+size_t gemm_scratch_bytes(int sm_count) {
+  return gemm_part_bytes(sm_count) + (size_t) sm_count * 8 * sizeof(int);
+}
 
 cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, cudaStream_t stream) {
   GemmArgs args = args_in;

@@ -89,8 +89,9 @@ int htp_b200_stream_status(void *stream);
 /* Tuning / debugging switches: "pdl" (programmatic dependent launch, default 1),
  * "force_generic" (route every matmul to the shape-agnostic kernel, default 0), "gemm_min_m"
  * (fp16-activation matmuls with at least this many tokens use the tensor-core GEMM, default 64),
- * "gemm_tile_n" (tokens per GEMM tile: 0 = automatic, 128 or 256).  Returns the previous value,
- * or -1 for an unknown name. */
+ * "gemm_tile_n" (tokens per GEMM tile: 0 = automatic, 128 or 256), "gemm_split" (when the GEMM's
+ * tiles do not divide evenly among the SMs, cut the work into equal K ranges and finish the split
+ * tiles through a scratch area, default 0).  Returns the previous value, or -1 for an unknown name. */
 int htp_b200_set_option(const char *name, int value);
 
 /* Number of kernel launches this process has issued through the library (all devices). */

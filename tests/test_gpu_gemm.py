@@ -44,6 +44,24 @@ def test_gemm_many_tiles_per_cta(dev, oracle, wl, wtype, tile_n):
     assert (ys[0] == ys[1]).all() and (ys[0] == ys[2]).all()
 
 
+@pytest.mark.parametrize("wtype", [2, 8])
+@pytest.mark.parametrize("m,k,n", [(300, 1024, 19360), (100, 2048, 128 * 190 + 96)])
+def test_gemm_split_tiles(dev, oracle, wl, wtype, m, k, n):
+    """Tile counts that do not divide among the SMs: the work is cut into equal K ranges and the
+    tiles cut in two are finished through scratch.  Ragged in M and N; repeatable bit for bit;
+    equal to the unsplit schedule up to fp32 summation order."""
+    lib = dev.lib
+    c = run(dev, oracle, wl, wtype, m, k, n, seed=5)  # whole tiles only (the default)
+    old = lib.htp_b200_set_option(b"gemm_split", 1)
+    try:
+        a = run(dev, oracle, wl, wtype, m, k, n, seed=5)
+        b = run(dev, oracle, wl, wtype, m, k, n, seed=5)
+    finally:
+        lib.htp_b200_set_option(b"gemm_split", old)
+    assert (a == b).all()
+    assert np.abs(a - c).max() <= 1e-5 * np.abs(c).max()
+
+
 def test_gemm_is_deterministic(dev, oracle, wl):
     a = run(dev, oracle, wl, 2, 256, 1024, 512, seed=3)
     b = run(dev, oracle, wl, 2, 256, 1024, 512, seed=3)
