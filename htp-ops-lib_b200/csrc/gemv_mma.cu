@@ -52,14 +52,22 @@ constexpr int kThreads         = kConsumerThreads + 32;
 template <int WT, bool A16, int MPAD>
 struct Cfg {
   static constexpr int  BB       = BlockTraits<WT>::kBytes;
-  static constexpr int  CH       = (!A16 && MPAD == 8) ? 2 : 1;           // chained MMAs per k-step
-  static constexpr int  NC       = A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD);  // MMA columns in use
-  static constexpr bool SPLITCOL = (!A16 && MPAD < 8);                    // column = 2 m + piece
+  // Q4_0 with one or two tokens runs on the INTEGER tensor-core path: nibbles are masked into
+  // unsigned bytes (3 instructions per 8 weights instead of 9 for exact fp16), the activations are
+  // four signed base-128 digits of a 28-bit fixed-point value (column = 4 m + digit), one
+  // m16n8k32 MMA covers a whole block, and the -8 offset of the format comes in through the MMA's
+  // accumulator input.
+  static constexpr bool I8       = (WT == kQ4 && MPAD <= 2);
+  static constexpr int  CH       = I8 ? 1 : ((!A16 && MPAD == 8) ? 2 : 1);  // chained MMAs per k-step
+  static constexpr int  NC       = I8 ? 4 * MPAD : (A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD));  // MMA columns in use
+  static constexpr bool SPLITCOL = !I8 && (!A16 && MPAD < 8);             // column = 2 m + piece
   static constexpr int  SB       = gemv_stage_blocks(WT);  // blocks per stage and row
   static constexpr int  BPW      = SB / kConsumerWarps;    // blocks per consumer warp and stage (even count)
   static constexpr int  PSTRIDE  = gemv_row_pitch(WT);
   static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
-  static constexpr int  FRAG_U2  = 2 * CH * NC * 4;  // uint2 entries per block
+  // uint2 entries per block: two k-steps of fp16 fragments, or one int8 fragment per column and lane
+  // position followed by the columns' accumulator inputs (one int each)
+  static constexpr int  FRAG_U2  = I8 ? NC * 4 + NC / 2 : 2 * CH * NC * 4;
 };
 
 struct Smem {
@@ -94,9 +102,100 @@ __device__ __forceinline__ long long item_owner(long long i, long long T, long l
 
 // ------------------------------------------------------------------ activation fragments
 
+// float 12582912 = 2^23 + 2^22: added to an integer |v| < 2^22 in the integer domain, the bit
+// pattern is the float 12582912 + v exactly
+constexpr int   kMagicBits = 0x4B400000;
+constexpr float kMagic     = 12582912.0f;
+
+// Integer path: token m, scaled by a power of two so that |x| < 1, becomes the fixed-point integer
+// X = round(x * 2^27) = D3 * 2^21 + D2 * 2^14 + D1 * 2^7 + D0 with signed digits in [-64, 64];
+// digit d of token m is MMA column 4 m + d.  Per block and column the accumulator input
+// kMagicBits - 8 * sum_k D turns the MMA result into the float 12582912 + sum_k (q_k - 8) D_k.
+template <int WT, bool A16, int MPAD>
+__device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
+  using C = Cfg<WT, A16, MPAD>;
+  if (tid < 8) {
+    sm->tok_amax_bits[tid] = 0;
+  }
+  named_bar_sync(1, kConsumerThreads);
+  const int klen = p.kblocks * 32;
+  auto      xval = [&](int m, int k) -> float {
+    const long long i = (long long) m * p.x_stride + p.x_k_off + k;
+    if constexpr (A16) {
+      return __half2float(static_cast<const __half *>(p.x)[i]);
+    } else {
+      return static_cast<const float *>(p.x)[i];
+    }
+  };
+  for (int m = 0; m < p.M; ++m) {
+    float a = 0.0f;
+    for (int k = tid; k < klen; k += kConsumerThreads) {
+      a = fmaxf(a, fabsf(xval(m, k)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    }
+    if ((tid & 31) == 0) {
+      atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+  if (tid < 8) {
+    const int bits = sm->tok_amax_bits[tid];
+    int       sh   = ((bits >> 23) & 0xff) - 127 + 1;  // amax < 2^sh
+    sh             = sh < -100 ? -100 : (sh > 100 ? 100 : sh);
+    sm->tok_scale[tid] = __int_as_float((127 + 27 - sh) << 23);  // x -> fixed point
+    sm->tok_inv[tid]   = __int_as_float((127 + sh) << 23);
+  }
+  named_bar_sync(1, kConsumerThreads);
+
+  const int n_units = p.kblocks * 4;  // (block, t): a multiple of 32, so warps stay whole
+  for (int u = tid; u < n_units; u += kConsumerThreads) {
+    const int b = u >> 2, t = u & 3;
+    uint2    *dst = frags + (size_t) b * C::FRAG_U2;
+    for (int m = 0; m < MPAD; ++m) {
+      // this lane position multiplies block elements 4t .. 4t+3 (register 0) and 16+4t .. (register 1)
+      uint32_t dig[4][2] = {};
+      int      sum[4]    = { 0, 0, 0, 0 };
+      if (m < p.M) {
+        const float sc = sm->tok_scale[m];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            int r = __float2int_rn(xval(m, b * 32 + 16 * h + 4 * t + i) * sc);
+#pragma unroll
+            for (int d = 0; d < 4; ++d) {
+              const int dv = d < 3 ? ((r + 64) & 127) - 64 : r;
+              r            = (r - dv) >> 7;
+              sum[d] += dv;
+              dig[d][h] |= (uint32_t) (dv & 0xff) << (8 * i);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        dst[(4 * m + d) * 4 + t] = make_uint2(dig[d][0], dig[d][1]);
+        int sd                   = sum[d];
+        sd += __shfl_xor_sync(0xffffffffu, sd, 1);
+        sd += __shfl_xor_sync(0xffffffffu, sd, 2);
+        if (t == 0) {
+          reinterpret_cast<int *>(dst + C::NC * 4)[4 * m + d] = kMagicBits - 8 * sd;
+        }
+      }
+    }
+  }
+}
+
 template <int WT, bool A16, int MPAD>
 __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
   using C = Cfg<WT, A16, MPAD>;
+  if constexpr (C::I8) {
+    build_x_frags_i8<WT, A16, MPAD>(p, sm, frags, tid);
+    return;
+  }
   if constexpr (!A16) {
     // per-token power-of-two normalisation: the largest |x| of a token lands in [2^14, 2^15), so
     // fp16(x) neither overflows nor drops into the subnormal range for small-magnitude tokens
@@ -245,6 +344,79 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
   acc[3] = fmaf(db, c[3], acc[3]);
 }
 
+// Integer path: one Q4_0 block x 16 rows = ONE m16n8k32 MMA (unsigned nibbles x signed digits,
+// int32 accumulate starting from the column's accumulator input).
+template <int WT, bool A16, int MPAD, bool EVEN>
+__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint2 cin, int t, float (&acc)[4]) {
+  using C = Cfg<WT, A16, MPAD>;
+  const uint8_t *rb = ra + 8 * C::PSTRIDE;
+  uint32_t       qa, qb;
+  if constexpr (EVEN) {  // quants start 2 bytes past a word boundary
+    qa = __byte_perm(lds32(ra + 4 * t), lds32(ra + 4 * t + 4), 0x5432);
+    qb = __byte_perm(lds32(rb + 4 * t), lds32(rb + 4 * t + 4), 0x5432);
+  } else {
+    qa = lds32(ra + 2 + 4 * t);
+    qb = lds32(rb + 2 + 4 * t);
+  }
+  // byte i of the word: low nibble = element 4t + i, high nibble = element 16 + 4t + i
+  const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
+  const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+  int            d0, d1, d2, d3;
+  asm volatile(
+    "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+    : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+  const float da = lds_scale(ra);
+  const float db = lds_scale(rb);
+  acc[0] = fmaf(da, __int_as_float(d0) - kMagic, acc[0]);
+  acc[1] = fmaf(da, __int_as_float(d1) - kMagic, acc[1]);
+  acc[2] = fmaf(db, __int_as_float(d2) - kMagic, acc[2]);
+  acc[3] = fmaf(db, __int_as_float(d3) - kMagic, acc[3]);
+}
+
+// This warp's blocks of one stage, both 16-row groups.  sb: the lane's row g at the warp's first
+// block of the stage; fp: the lane's fragment entry (column g, lane position t) of that block;
+// cp (integer path): the lane's pair of accumulator inputs (columns 2t, 2t + 1) of that block.
+template <int WT, bool A16, int MPAD>
+__device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp, const uint2 *cp, int t,
+                                             float (&acc)[2][4]) {
+  using C = Cfg<WT, A16, MPAD>;
+#pragma unroll
+  for (int i = 0; i < C::BPW; ++i) {
+    if constexpr (C::I8) {
+      const uint2 bf  = fp[i * C::FRAG_U2];
+      const uint2 cin = cp[i * C::FRAG_U2];
+#pragma unroll
+      for (int rg = 0; rg < 2; ++rg) {
+        const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
+        if ((i & 1) == 0) {
+          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, acc[rg]);
+        } else {
+          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, acc[rg]);
+        }
+      }
+    } else {
+      uint2 bf[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int rg = 0; rg < 2; ++rg) {
+        const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
+        if ((i & 1) == 0) {
+          block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
+        } else {
+          block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
+        }
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------ tile completion
 
 template <int WT, bool A16, int MPAD>
@@ -304,16 +476,28 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
     }
     named_bar_sync(2, kReduceThreads);  // last_flag may be rewritten by the next flush
   }
+  const int i = tid & 3, t = (tid >> 2) & 3, g = (tid >> 4) & 7, rg = tid >> 7;
   if constexpr (C::SPLITCOL) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);  // hi-piece column + lo-piece column
+  }
+  if constexpr (C::I8) {
+    // column 2t + (i & 1) = 4 m + digit: weigh the digit (2^(7 digit - 27)), add the four columns
+    const int digit = ((t & 1) << 1) | (i & 1);
+    v *= __int_as_float((127 + 7 * digit - 27) << 23);
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
   }
   if (!write_out) {
     return;
   }
-  const int i = tid & 3, t = (tid >> 2) & 3, g = (tid >> 4) & 7, rg = tid >> 7;
   const int row = rg * 16 + g + 8 * (i >> 1);
   int       m;
-  if constexpr (C::SPLITCOL) {
+  if constexpr (C::I8) {
+    if ((i & 1) || (t & 1)) {
+      return;
+    }
+    m = t >> 1;
+  } else if constexpr (C::SPLITCOL) {
     if (i & 1) {
       return;
     }
@@ -324,7 +508,7 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
   if (m >= p.M) {
     return;
   }
-  if constexpr (!A16) {
+  if constexpr (!A16 || C::I8) {
     v *= sm->tok_inv[m];
   }
   float *dst = p.y + (long long) m * p.N + tile * kGemvTileRows + row;
@@ -412,7 +596,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // their output columns are never stored, so what they multiply is irrelevant
     const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
     const uint8_t *warp_base = stages + g * C::PSTRIDE + warp * C::BPW * C::BB;
-    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW * 2) * C::CH * C::NC * 4;
+    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW) * C::FRAG_U2;
+    // (integer path) accumulator inputs of columns 2t, 2t + 1; positions past the columns in use
+    // read another pair, their outputs are never stored
+    const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
       if (!mbar_wait(&sm->full[slot], ph)) {
         record_error(p, kGemvErrConsumerWait);
@@ -422,27 +609,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int nblk = min(C::SB, p.kblocks - st * C::SB);
       if (warp * C::BPW < nblk) {
         const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
-        const uint2   *fp = warp_frag + (size_t) (st * C::SB * 2) * C::CH * C::NC * 4;
-#pragma unroll
-        for (int i = 0; i < C::BPW; ++i) {
-          uint2 bf[2][2];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-              bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
-            }
-          }
-#pragma unroll
-          for (int rg = 0; rg < 2; ++rg) {
-            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
-            if ((i & 1) == 0) {
-              block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
-            } else {
-              block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
-            }
-          }
-        }
+        const uint2   *fp = warp_frag + (size_t) (st * C::SB) * C::FRAG_U2;
+        const uint2   *cp = warp_cin + (size_t) (st * C::SB) * C::FRAG_U2;
+        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, acc);
       }
       // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
       // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
@@ -640,7 +809,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     int       flush_parity = 0;
     const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
     const uint8_t *warp_base = stages + g * C::PSTRIDE + warp * C::BPW * C::BB;
-    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW * 2) * C::CH * C::NC * 4;
+    const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW) * C::FRAG_U2;
+    // (integer path) accumulator inputs of columns 2t, 2t + 1; positions past the columns in use
+    // read another pair, their outputs are never stored
+    const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
       if (!mbar_wait(&sm->full[slot], ph)) {
         atomicCAS(b.err, 0, kGemvErrConsumerWait);
@@ -650,27 +822,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
       const int nblk = min(C::SB, p.kblocks - st * C::SB);
       if (warp * C::BPW < nblk) {
         const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
-        const uint2   *fp = warp_frag + (size_t) (st * C::SB * 2) * C::CH * C::NC * 4;
-#pragma unroll
-        for (int i = 0; i < C::BPW; ++i) {
-          uint2 bf[2][2];
-#pragma unroll
-          for (int j = 0; j < 2; ++j) {
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-              bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
-            }
-          }
-#pragma unroll
-          for (int rg = 0; rg < 2; ++rg) {
-            const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
-            if ((i & 1) == 0) {
-              block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
-            } else {
-              block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
-            }
-          }
-        }
+        const uint2   *fp = warp_frag + (size_t) (st * C::SB) * C::FRAG_U2;
+        const uint2   *cp = warp_cin + (size_t) (st * C::SB) * C::FRAG_U2;
+        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, acc);
       }
       // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
       // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
@@ -779,10 +933,15 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
-  (void) wt;
-  const int ch = (!a16 && mpad == 8) ? 2 : 1;
-  const int nc = a16 ? mpad : (mpad == 8 ? 8 : 2 * mpad);
-  size_t    b  = (size_t) kblocks * 2 * ch * nc * 4 * 8;
+  size_t b;
+  if (wt == kQ4 && mpad <= 2) {  // integer path: 4 digit columns per token + their accumulator inputs
+    const int nc = 4 * mpad;
+    b            = (size_t) kblocks * (nc * 4 + nc / 2) * 8;
+  } else {
+    const int ch = (!a16 && mpad == 8) ? 2 : 1;
+    const int nc = a16 ? mpad : (mpad == 8 ? 8 : 2 * mpad);
+    b            = (size_t) kblocks * 2 * ch * nc * 4 * 8;
+  }
   return (b + 127) & ~(size_t) 127;
 }
 
