@@ -45,9 +45,10 @@ namespace htp {
 namespace {
 
 constexpr int kConsumerWarps   = 16;
-constexpr int kReduceThreads   = 256;  // one per element of a 32-row x 8-column tile result
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads         = kConsumerThreads + 32;
+constexpr int kReduceWarp0     = kConsumerWarps + 1;  // two warps finish the tiles, one per 16-row group
+constexpr int kReduceThreads   = 64;
+constexpr int kThreads         = kConsumerThreads + 32 + kReduceThreads;
 
 template <int WT, bool A16, int MPAD>
 struct Cfg {
@@ -79,7 +80,14 @@ struct Smem {
   int      last_flag;
   int      abort_flag;
   int      pad[6];
-  float    red[2][kConsumerWarps][256];  // double-buffered: one barrier per tile completion
+  // Tile completion runs on two warps of its own: the consumer warps drop their partial sums of a
+  // tile into red[n & 1] and carry on; red_full counts the 16 warps in, red_empty tells them the
+  // copy has been read.
+  uint64_t red_full[2];
+  uint64_t red_empty[2];
+  uint64_t op_bar;  // batched launch: the consumer warps meet here before an operator's activations replace the last one's
+  uint8_t  pad2[88];
+  float    red[2][kConsumerWarps][256];
 };
 static_assert(sizeof(Smem) % 128 == 0, "keep the regions after the header 128-byte aligned");
 static_assert(sizeof(Smem) == kGemvSmemHeader, "host-side size computation must match");
@@ -347,7 +355,8 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
 // Integer path: one Q4_0 block x 16 rows = ONE m16n8k32 MMA (unsigned nibbles x signed digits,
 // int32 accumulate starting from the column's accumulator input).
 template <int WT, bool A16, int MPAD, bool EVEN>
-__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint2 cin, int t, float (&acc)[4]) {
+__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint2 cin, int t, uint64_t neg_magic2,
+                                                float (&acc)[4]) {
   using C = Cfg<WT, A16, MPAD>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
   uint32_t       qa, qb;
@@ -368,10 +377,21 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
   const float da = lds_scale(ra);
   const float db = lds_scale(rb);
-  acc[0] = fmaf(da, __int_as_float(d0) - kMagic, acc[0]);
-  acc[1] = fmaf(da, __int_as_float(d1) - kMagic, acc[1]);
-  acc[2] = fmaf(db, __int_as_float(d2) - kMagic, acc[2]);
-  acc[3] = fmaf(db, __int_as_float(d3) - kMagic, acc[3]);
+  // int bits -> float: subtract the bias, two results per instruction (packed fp32 add)
+  float f0, f1, f2, f3;
+  asm("{\n\t.reg .b64 p, q;\n\t"
+      "mov.b64 p, {%4, %5};\n\t"
+      "mov.b64 q, {%6, %7};\n\t"
+      "add.rn.f32x2 p, p, %8;\n\t"
+      "add.rn.f32x2 q, q, %8;\n\t"
+      "mov.b64 {%0, %1}, p;\n\t"
+      "mov.b64 {%2, %3}, q;\n\t}"
+      : "=f"(f0), "=f"(f1), "=f"(f2), "=f"(f3)
+      : "r"(d0), "r"(d1), "r"(d2), "r"(d3), "l"(neg_magic2));
+  acc[0] = fmaf(da, f0, acc[0]);
+  acc[1] = fmaf(da, f1, acc[1]);
+  acc[2] = fmaf(db, f2, acc[2]);
+  acc[3] = fmaf(db, f3, acc[3]);
 }
 
 // This warp's blocks of one stage, both 16-row groups.  sb: the lane's row g at the warp's first
@@ -381,6 +401,8 @@ template <int WT, bool A16, int MPAD>
 __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp, const uint2 *cp, int t,
                                              float (&acc)[2][4]) {
   using C = Cfg<WT, A16, MPAD>;
+  uint64_t neg_magic2;  // the pair (-kMagic, -kMagic)
+  asm("mov.b64 %0, {%1, %1};" : "=l"(neg_magic2) : "f"(-kMagic));
 #pragma unroll
   for (int i = 0; i < C::BPW; ++i) {
     if constexpr (C::I8) {
@@ -390,9 +412,9 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if ((i & 1) == 0) {
-          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, acc[rg]);
+          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, neg_magic2, acc[rg]);
         } else {
-          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, acc[rg]);
+          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, neg_magic2, acc[rg]);
         }
       }
     } else {
@@ -419,29 +441,84 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
 
 // ------------------------------------------------------------------ tile completion
 
-template <int WT, bool A16, int MPAD>
-__device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long long it0, long long it1, int S,
-                           float (&acc)[2][4], int tid, int &flush_parity) {
-  using C = Cfg<WT, A16, MPAD>;
-  const int warp = tid >> 5, lane = tid & 31;
-  // The reduction buffer alternates between two copies, so one barrier per completion suffices:
-  // a warp can only overwrite copy b again after passing the barrier of the completion in between,
-  // which the reducing warps reach only after they have finished reading copy b.
-  float(*red)[256] = sm->red[flush_parity];
-  flush_parity ^= 1;
+// Bounded wait that also gives up when another role of the CTA has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+  for (uint32_t i = 0; i < kWaitCap; ++i) {
+    if (mbar_try_wait(bar, parity)) {
+      return true;
+    }
+    if (i > 64) {
+      if (*abort_flag) {
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  return false;
+}
+
+// Consumer side of a tile completion, n = how many tiles this CTA has completed before: the warp
+// drops its partial sums into copy n & 1 of the reduction buffer and carries on.  Copy n & 1 was
+// last used by completion n - 2, which the completion warps have read once red_empty says so.
+__device__ __forceinline__ bool publish_tile(Smem *sm, const float (&acc)[2][4], int warp, int lane, unsigned n) {
+  const int buf = n & 1;
+  if (n >= 2 && !mbar_wait_abort(&sm->red_empty[buf], ((n >> 1) - 1) & 1, &sm->abort_flag)) {
+    return false;
+  }
 #pragma unroll
   for (int rg = 0; rg < 2; ++rg) {
-    *reinterpret_cast<float4 *>(&red[warp][rg * 128 + lane * 4]) =
+    *reinterpret_cast<float4 *>(&sm->red[buf][warp][rg * 128 + lane * 4]) =
       make_float4(acc[rg][0], acc[rg][1], acc[rg][2], acc[rg][3]);
   }
-  named_bar_sync(1, kConsumerThreads);
-  if (tid >= kReduceThreads) {
-    return;  // the first eight warps finish the tile
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(&sm->red_full[buf]);  // release: the warp's stores above are visible to the waiter
   }
-  float v = 0.f;
+  return true;
+}
+
+// Completion-warp side: warp rg (0, 1) finishes the 16-row group rg of the tile, lane (g, t) the
+// four sums the consumer lanes (g, t) hold: rows g and g + 8, MMA columns 2t and 2t + 1.
+// Returns false when a wait ran out (error recorded, abort flag raised).
+template <int WT, bool A16, int MPAD>
+__device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long long it0, long long it1, int S, int rg,
+                              int lane, unsigned n) {
+  using C = Cfg<WT, A16, MPAD>;
+  const int buf = n & 1;
+  const int g = lane >> 2, t = lane & 3;
+  // which token the lane's results belong to, and whether this lane writes them out
+  int  m0, m1;  // tokens of (column 2t, column 2t + 1); equal when the columns are pieces of one token
+  bool writer = true;
+  if constexpr (C::I8) {
+    m0 = m1 = t >> 1;
+    writer  = (t & 1) == 0;
+  } else if constexpr (C::SPLITCOL) {
+    m0 = m1 = t;
+  } else {
+    m0 = 2 * t, m1 = 2 * t + 1;
+  }
+  const bool arrived = mbar_wait_abort(&sm->red_full[buf], (n >> 1) & 1, &sm->abort_flag);
+  // (both completion warps leave together: the barriers further down need all 64 threads)
+  if (!named_bar_and(2, kReduceThreads, arrived)) {
+    record_error(p, kGemvErrConsumerWait);
+    sm->abort_flag = 1;
+    return false;
+  }
+  // per-token output scale of this operator (read before the buffer is handed back: a batched
+  // launch rebuilds the scales for its next operator only after that)
+  float inv0 = 1.f, inv1 = 1.f;
+  if constexpr (!A16 || C::I8) {
+    inv0 = sm->tok_inv[m0 & 7], inv1 = sm->tok_inv[m1 & 7];
+  }
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
   for (int w = 0; w < kConsumerWarps; ++w) {
-    v += red[w][tid];
+    const float4 r = *reinterpret_cast<const float4 *>(&sm->red[buf][w][rg * 128 + lane * 4]);
+    v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+  }
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(&sm->red_empty[buf]);
   }
 
   const long long first = p.item_base + tile * S, last = first + S - 1;
@@ -452,11 +529,12 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
     const int       c_first = (int) item_owner(first, T, G);
     const int       c_last  = (int) item_owner(last, T, G);
     const int       slot    = (first < it0) ? 0 : 1;
+    const int       off     = rg * 128 + lane * 4;
     float          *mine    = p.partials + ((size_t) blockIdx.x * 2 + slot) * 256;
-    __stcg(mine + tid, v);
+    __stcg(reinterpret_cast<float4 *>(mine + off), v);
     __threadfence();
     named_bar_sync(2, kReduceThreads);
-    if (tid == 0) {
+    if (rg == 0 && lane == 0) {
       const unsigned old  = atomicAdd(p.counters + c_first, 1u);
       const int      done = (old == (unsigned) (c_last - c_first));
       if (done) {
@@ -468,51 +546,47 @@ __device__ void flush_tile(const GemvArgs &p, Smem *sm, long long tile, long lon
     write_out = sm->last_flag != 0;
     if (write_out) {
       __threadfence();
-      v = 0.f;
+      v = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int c = c_first; c <= c_last; ++c) {
-        const int s = (c == c_first) ? 1 : 0;
-        v += __ldcg(p.partials + ((size_t) c * 2 + s) * 256 + tid);
+        const int    s = (c == c_first) ? 1 : 0;
+        const float4 r = __ldcg(reinterpret_cast<const float4 *>(p.partials + ((size_t) c * 2 + s) * 256 + off));
+        v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
       }
     }
-    named_bar_sync(2, kReduceThreads);  // last_flag may be rewritten by the next flush
+    named_bar_sync(2, kReduceThreads);  // last_flag may be rewritten by the next completion
   }
-  const int i = tid & 3, t = (tid >> 2) & 3, g = (tid >> 4) & 7, rg = tid >> 7;
-  if constexpr (C::SPLITCOL) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);  // hi-piece column + lo-piece column
-  }
+  // v.x, v.y: row g, columns 2t, 2t + 1;  v.z, v.w: row g + 8, same columns
+  float lo0 = v.x, lo1 = v.y, hi0 = v.z, hi1 = v.w;
   if constexpr (C::I8) {
-    // column 2t + (i & 1) = 4 m + digit: weigh the digit (2^(7 digit - 27)), add the four columns
-    const int digit = ((t & 1) << 1) | (i & 1);
-    v *= __int_as_float((127 + 7 * digit - 27) << 23);
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-  }
-  if (!write_out) {
-    return;
-  }
-  const int row = rg * 16 + g + 8 * (i >> 1);
-  int       m;
-  if constexpr (C::I8) {
-    if ((i & 1) || (t & 1)) {
-      return;
-    }
-    m = t >> 1;
+    // column 2t + c = 4 m + digit: weigh the digits (2^(7 digit - 27)) and add the four columns
+    const float w0 = __int_as_float((127 + 7 * ((t & 1) << 1) - 27) << 23);
+    const float w1 = __int_as_float((127 + 7 * (((t & 1) << 1) | 1) - 27) << 23);
+    lo0 = lo0 * w0 + lo1 * w1;
+    hi0 = hi0 * w0 + hi1 * w1;
+    lo0 += __shfl_xor_sync(0xffffffffu, lo0, 1);
+    hi0 += __shfl_xor_sync(0xffffffffu, hi0, 1);
   } else if constexpr (C::SPLITCOL) {
-    if (i & 1) {
-      return;
+    lo0 += lo1;  // hi-piece column + lo-piece column
+    hi0 += hi1;
+  }
+  if (!write_out || !writer) {
+    return true;
+  }
+  const long long row = tile * kGemvTileRows + rg * 16 + g;
+  auto            put = [&](int m, long long r, float val, float inv) {
+    if (m < p.M) {
+      float *dst = p.y + (long long) m * p.N + r;
+      val *= inv;
+      *dst = p.accumulate ? (*dst + val) : val;
     }
-    m = t;
-  } else {
-    m = 2 * t + (i & 1);
+  };
+  put(m0, row, lo0, inv0);
+  put(m0, row + 8, hi0, inv0);
+  if constexpr (!C::I8 && !C::SPLITCOL) {
+    put(m1, row, lo1, inv1);
+    put(m1, row + 8, hi1, inv1);
   }
-  if (m >= p.M) {
-    return;
-  }
-  if constexpr (!A16 || C::I8) {
-    v *= sm->tok_inv[m];
-  }
-  float *dst = p.y + (long long) m * p.N + tile * kGemvTileRows + row;
-  *dst       = p.accumulate ? (*dst + v) : v;
+  return true;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -537,6 +611,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&sm->full[s], 1);
       mbar_init(&sm->empty[s], kConsumerWarps);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm->red_full[i], kConsumerWarps);
+      mbar_init(&sm->red_empty[i], kReduceThreads / 32);
+    }
+    mbar_init(&sm->op_bar, kConsumerWarps);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -570,6 +649,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
+  } else if (warp >= kReduceWarp0) {
+    // ---------------- tile completion: the tiles this CTA touches, in order
+    pdl_wait_prior_grids();  // outputs and scratch belong to the stream order
+    if (it1 > it0) {
+      const long long last_tile = (it1 - 1) / S;
+      unsigned        n         = 0;
+      for (long long tile = it0 / S; tile <= last_tile; ++tile, ++n) {
+        if (!complete_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, warp - kReduceWarp0, lane, n)) {
+          break;
+        }
+      }
+    }
   } else {
     // ---------------- consumers
     const int tid = threadIdx.x;
@@ -591,7 +682,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     int       st   = (int) (it0 - tile * S);
     int       slot = 0, ph = 0;
     bool      ok   = true;
-    int       flush_parity = 0;
+    unsigned  n_done = 0;  // tiles completed so far
     // lanes whose MMA column is beyond the columns in use read a valid fragment of another column:
     // their output columns are never stored, so what they multiply is irrelevant
     const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
@@ -601,9 +692,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     // read another pair, their outputs are never stored
     const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
-      if (!mbar_wait(&sm->full[slot], ph)) {
+      if (!mbar_wait_abort(&sm->full[slot], ph, &sm->abort_flag)) {
         record_error(p, kGemvErrConsumerWait);
-        ok = false;
+        sm->abort_flag = 1;
+        ok             = false;
         break;
       }
       const int nblk = min(C::SB, p.kblocks - st * C::SB);
@@ -629,7 +721,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (++st == S) {
         st = 0;
         if (it + 1 < it1) {
-          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
+          if (!publish_tile(sm, acc, warp, lane, n_done++)) {
+            ok = false;
+            break;
+          }
 #pragma unroll
           for (int rg = 0; rg < 2; ++rg) {
 #pragma unroll
@@ -641,9 +736,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-    const long long cur_tile = tile;
     if (ok && it1 > it0) {
-      flush_tile<WT, A16, MPAD>(p, sm, cur_tile, it0, it1, S, acc, tid, flush_parity);
+      publish_tile(sm, acc, warp, lane, n_done++);
     }
   }
 }
@@ -716,6 +810,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
       mbar_init(&sm->full[s], 1);
       mbar_init(&sm->empty[s], kConsumerWarps);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm->red_full[i], kConsumerWarps);
+      mbar_init(&sm->red_empty[i], kReduceThreads / 32);
+    }
+    mbar_init(&sm->op_bar, kConsumerWarps);
     sm->abort_flag = 0;
     mbar_fence_init();
   }
@@ -727,6 +826,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
   while (oi + 1 < b.n_ops && b.ops[oi + 1].item_begin <= it0) {
     ++oi;
   }
+
+  auto op_args = [&](int i) {
+    GemvArgs p        = {};
+    p.y               = b.ops[i].y;
+    p.x               = b.ops[i].x;
+    p.x_k_off         = 0;
+    p.x_stride        = b.ops[i].x_stride;
+    p.M               = b.M;
+    p.N               = b.ops[i].N;
+    p.kblocks         = b.ops[i].kblocks;
+    p.accumulate      = 0;
+    p.stages_per_tile = b.ops[i].stages_per_tile;
+    p.item_base       = b.ops[i].item_begin;
+    p.total_items     = b.total_items;
+    p.partials        = b.partials;
+    p.counters        = b.counters;
+    p.err             = b.err;
+    return p;
+  };
 
   if (warp == kConsumerWarps) {
     // ---------------- producer
@@ -763,30 +881,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
         }
       }
     }
+  } else if (warp >= kReduceWarp0) {
+    // ---------------- tile completion: the (operator, tile) sequence of this CTA's item range
+    pdl_wait_prior_grids();
+    GemvArgs  p    = op_args(oi);
+    int       S    = p.stages_per_tile;
+    long long tile = (it0 - p.item_base) / S;
+    long long tiles_in_op = p.N / kGemvTileRows;
+    unsigned  n    = 0;
+    for (long long it = it0; it < it1; ++n) {
+      if (!complete_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, warp - kReduceWarp0, lane, n)) {
+        break;
+      }
+      it = p.item_base + (tile + 1) * S;  // first item after this tile
+      if (++tile == tiles_in_op && oi + 1 < b.n_ops) {
+        ++oi;
+        p           = op_args(oi);
+        tile        = 0;
+        S           = p.stages_per_tile;
+        tiles_in_op = p.N / kGemvTileRows;
+      }
+    }
   } else {
     // ---------------- consumers
     const int tid = threadIdx.x;
     const int g = lane >> 2, t = lane & 3;
     pdl_wait_prior_grids();
 
-    auto op_args = [&](int i) {
-      GemvArgs p        = {};
-      p.y               = b.ops[i].y;
-      p.x               = b.ops[i].x;
-      p.x_k_off         = 0;
-      p.x_stride        = b.ops[i].x_stride;
-      p.M               = b.M;
-      p.N               = b.ops[i].N;
-      p.kblocks         = b.ops[i].kblocks;
-      p.accumulate      = 0;
-      p.stages_per_tile = b.ops[i].stages_per_tile;
-      p.item_base       = b.ops[i].item_begin;
-      p.total_items     = b.total_items;
-      p.partials        = b.partials;
-      p.counters        = b.counters;
-      p.err             = b.err;
-      return p;
-    };
     GemvArgs p = op_args(oi);
     build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
     named_bar_sync(1, kConsumerThreads);
@@ -806,7 +927,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     long long tiles_in_op = p.N / kGemvTileRows;
     int       slot = 0, ph = 0;
     bool      ok   = true;
-    int       flush_parity = 0;
+    unsigned  n_done = 0;  // tiles completed so far
+    unsigned  n_ops_done = 0;  // operator changes so far
     const uint2   *frag_lane = frags + (g & (C::NC - 1)) * 4 + t;
     const uint8_t *warp_base = stages + g * C::PSTRIDE + warp * C::BPW * C::BB;
     const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW) * C::FRAG_U2;
@@ -814,9 +936,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     // read another pair, their outputs are never stored
     const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
-      if (!mbar_wait(&sm->full[slot], ph)) {
+      if (!mbar_wait_abort(&sm->full[slot], ph, &sm->abort_flag)) {
         atomicCAS(b.err, 0, kGemvErrConsumerWait);
-        ok = false;
+        sm->abort_flag = 1;
+        ok             = false;
         break;
       }
       const int nblk = min(C::SB, p.kblocks - st * C::SB);
@@ -842,7 +965,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
       if (++st == S) {
         st = 0;
         if (it + 1 < it1) {
-          flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
+          if (!publish_tile(sm, acc, warp, lane, n_done++)) {
+            ok = false;
+            break;
+          }
 #pragma unroll
           for (int rg = 0; rg < 2; ++rg) {
 #pragma unroll
@@ -851,16 +977,30 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
             }
           }
           if (++tile == tiles_in_op && oi + 1 < b.n_ops) {
-            // next operator: its activations replace the fragments (every consumer warp is past
-            // the completion barrier above, so the old ones are no longer read)
+            // next operator: its activations and token scales replace the old ones - once the
+            // completion warps have taken the last tile of this one (its token scales with it) and
+            // every consumer warp has stopped reading the fragments (the barriers below)
+            // (an mbarrier, not bar.sync: a warp that has given up a wait never gets here, and the
+            // others must not wait for it for ever)
+            bool go = mbar_wait_abort(&sm->red_empty[(n_done - 1) & 1], ((n_done - 1) >> 1) & 1, &sm->abort_flag);
+            if (go) {
+              __syncwarp();
+              if (lane == 0) {
+                mbar_arrive(&sm->op_bar);
+              }
+              go = mbar_wait_abort(&sm->op_bar, n_ops_done & 1, &sm->abort_flag);
+              ++n_ops_done;
+            }
+            if (!go) {
+              sm->abort_flag = 1;
+              ok             = false;
+              break;
+            }
             ++oi;
             p           = op_args(oi);
             tile        = 0;
             S           = p.stages_per_tile;
             tiles_in_op = p.N / kGemvTileRows;
-            if constexpr (A16) {
-              named_bar_sync(1, kConsumerThreads);  // the fp32 path starts with a barrier of its own
-            }
             build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
             named_bar_sync(1, kConsumerThreads);
           }
@@ -868,7 +1008,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
       }
     }
     if (ok && it1 > it0) {
-      flush_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, acc, tid, flush_parity);
+      publish_tile(sm, acc, warp, lane, n_done++);
     }
   }
 }

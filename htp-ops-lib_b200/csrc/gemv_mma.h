@@ -9,7 +9,7 @@ namespace htp {
 
 constexpr int kGemvTileRows    = 32;  // output rows per tile (two 16-row MMA groups)
 constexpr int kGemvMaxStages   = 8;
-constexpr int kGemvSmemHeader  = 33024;   // barriers, per-token scales, cross-warp reduction buffer
+constexpr int kGemvSmemHeader  = 33152;   // barriers, per-token scales, cross-warp reduction buffer
 constexpr int kGemvSmemBudget  = 232448;  // 227 KiB opt-in dynamic shared memory per CTA on sm_100
 constexpr int kGemvMaxGrid     = 1024;    // scratch is sized for this many CTAs
 
