@@ -228,8 +228,27 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
     run_case("cfg1_q8_0_gemv_11008x4096_m1", wl.CONFIGS["cfg1"], 0, 1, steps)
     run_case("cfg2_q4_0_prefill_14336x4096_m512", wl.CONFIGS["cfg2"], 0, 512, max(3, steps // 10))
     run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(3, steps // 10))
+    out["rms_norm_f32_4096x32768"] = measure_rms_norm(torch, lib, peaks, stream_ptr, stream, max(5, steps // 5))
     out.update(measure_decoder_stack(torch, pkg, lib, wl, peaks, quick))
     return out
+
+
+def measure_rms_norm(torch, lib, peaks, stream_ptr, stream, steps):
+    """RMSNorm over 32768 rows of 4096 floats (512 MB read + 512 MB written per launch, far beyond L2):
+    algorithmic bytes = 2 * 4 * ne0 * ne1."""
+    ne0, ne1 = 4096, 32768
+    dev = torch.device("cuda", torch.cuda.current_device())
+    x = torch.randn((ne1, ne0), device=dev, dtype=torch.float32)
+    y = torch.empty_like(x)
+
+    def step(i):
+        assert lib.htp_b200_rms_norm_f32(y.data_ptr(), x.data_ptr(), ne0, ne1, stream_ptr) == 0
+    for i in range(3):
+        step(i)
+    ms = time_region(torch, step, steps, stream) / steps
+    gb = 2.0 * 4 * ne0 * ne1 / (ms * 1e-3) / 1e9
+    return {"ms": round(ms, 5), "ne0": ne0, "ne1": ne1, "GBps": round(gb, 1),
+            "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4)}
 
 
 def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):

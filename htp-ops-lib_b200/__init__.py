@@ -48,6 +48,7 @@ EXPORTS = {
     "htp_b200_mul_mat_batch": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "htp_b200_mul_mat_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "htp_b200_block_sums": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "htp_b200_rms_norm_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     "htp_b200_weight_bytes": (_sz, [_i, _i64, _i64]),
     "htp_b200_stream_status": (_i, [_vp]),
     "htp_b200_set_option": (_i, [ctypes.c_char_p, _i]),
@@ -114,6 +115,12 @@ def pack_matmul_request(op: int, out: tuple[int, int], act: tuple[int, int], wei
     """RequestHeader{state=0,type=OP_COMPUTE} || OpComputeRequest{op} || MatMulParams - 48 bytes."""
     return struct.pack("<iiI9i", 0, REQUEST_TYPE_OP_COMPUTE, op, out[0], out[1], act[0], act[1], weight[0], weight[1],
                        m, k, n)
+
+
+def pack_rms_norm_request(dst: tuple[int, int], src: tuple[int, int], ne0: int, ne1: int) -> bytes:
+    """RequestHeader{state=0,type=OP_COMPUTE} || OpComputeRequest{RMS_NORM_F32} || RmsNormF32Params - 36 bytes."""
+    return struct.pack("<iiI6i", 0, REQUEST_TYPE_OP_COMPUTE, HTP_OPS_RMS_NORM_F32, dst[0], dst[1], src[0], src[1], ne0,
+                       ne1)
 
 
 def pack_map_request(puts: list[int], gets: list[int] | None = None) -> bytes:

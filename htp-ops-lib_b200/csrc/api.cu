@@ -407,6 +407,24 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
   return 0;
 }
 
+int htp_b200_rms_norm_f32(float *dst, const float *src, int ne0, int ne1, void *stream) {
+  // argument rules of the reference: src/dsp/ops/rms_norm.c:69-74
+  if (!dst || !src || ne0 <= 0 || ne1 <= 0) {
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 127u) {
+    return -1;
+  }
+  if (!current_device_ctx()) {
+    return -2;
+  }
+  if (rms_norm_f32_launch(dst, src, ne0, ne1, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    return -2;
+  }
+  count_launch();
+  return 0;
+}
+
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n) {
   const int wt = wt_index(weight_type);
   if (wt < 0 || k <= 0 || n <= 0 || k % 32 != 0) {

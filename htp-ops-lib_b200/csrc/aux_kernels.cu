@@ -160,4 +160,95 @@ cudaError_t block_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long lon
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- RMSNorm (fp32)
+//
+// Replaces the reference's hvx_rms_norm_f32 (src/dsp/ops/rms_norm.c:8-84; scalar statement
+// src/host/test.c:60-80): per row, scale = 1 / sqrt(sum(x^2) / ne0 + 1e-5), y = x * scale.  HBM-bound:
+// one CTA per row (grid-stride over rows), the row is read once into registers when it has at most
+// kRmsRegElems elements (16-byte loads), otherwise read twice.  The sum of squares is added in a
+// fixed order (per-thread strided partial sums, warp tree, then the warps in order), so results
+// do not depend on the launch.
+namespace {
+
+constexpr int kRmsThreads  = 256;
+constexpr int kRmsVecs     = 8;                               // float4 per thread kept in registers
+constexpr int kRmsRegElems = kRmsThreads * kRmsVecs * 4;      // 8192
+constexpr float kRmsEps    = 1e-5f;
+
+__device__ __forceinline__ float rms_block_sum(float v, float *warp_sums) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    v += __shfl_xor_sync(0xffffffffu, v, o);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // warp_sums may still be read by the previous row
+  if (lane == 0) {
+    warp_sums[warp] = v;
+  }
+  __syncthreads();
+  float s = 0.f;
+#pragma unroll
+  for (int w = 0; w < kRmsThreads / 32; ++w) {
+    s += warp_sums[w];
+  }
+  return s;
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kRmsThreads) rms_norm_f32_kernel(float *__restrict__ dst, const float *__restrict__ src,
+                                                                  int ne0, int ne1) {
+  __shared__ float warp_sums[kRmsThreads / 32];
+  for (int row = blockIdx.x; row < ne1; row += gridDim.x) {
+    const float *x = src + (long long) row * ne0;
+    float       *y = dst + (long long) row * ne0;
+    if constexpr (VEC) {
+      // ne0 % 4 == 0 and ne0 <= kRmsRegElems: the row lives in registers between the two passes
+      const int    nv = ne0 >> 2;
+      const float4 *xv = reinterpret_cast<const float4 *>(x);
+      float4       r[kRmsVecs];
+      float        ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < kRmsVecs; ++j) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        r[j]        = i < nv ? __ldcs(xv + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += r[j].x * r[j].x + r[j].y * r[j].y + r[j].z * r[j].z + r[j].w * r[j].w;
+      }
+      const float sum   = rms_block_sum(ss, warp_sums);
+      const float scale = 1.0f / sqrtf(sum / (float) ne0 + kRmsEps);
+      float4     *yv    = reinterpret_cast<float4 *>(y);
+#pragma unroll
+      for (int j = 0; j < kRmsVecs; ++j) {
+        const int i = threadIdx.x + j * kRmsThreads;
+        if (i < nv) {
+          __stcs(yv + i, make_float4(r[j].x * scale, r[j].y * scale, r[j].z * scale, r[j].w * scale));
+        }
+      }
+    } else {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < ne0; i += kRmsThreads) {
+        const float v = x[i];
+        ss += v * v;
+      }
+      const float sum   = rms_block_sum(ss, warp_sums);
+      const float scale = 1.0f / sqrtf(sum / (float) ne0 + kRmsEps);
+      for (int i = threadIdx.x; i < ne0; i += kRmsThreads) {
+        y[i] = x[i] * scale;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t rms_norm_f32_launch(float *dst, const float *src, int ne0, int ne1, cudaStream_t stream) {
+  const bool vec  = (ne0 % 4 == 0) && ne0 <= kRmsRegElems;
+  const int  grid = ne1 < 148 * 8 ? ne1 : 148 * 8;  // up to eight resident CTAs per SM, rows strided over them
+  if (vec) {
+    rms_norm_f32_kernel<true><<<grid, kRmsThreads, 0, stream>>>(dst, src, ne0, ne1);
+  } else {
+    rms_norm_f32_kernel<false><<<grid, kRmsThreads, 0, stream>>>(dst, src, ne0, ne1);
+  }
+  return cudaGetLastError();
+}
+
 }  // namespace htp

@@ -1,4 +1,5 @@
-// Launchers of the shape-agnostic fallback matmul and the integer block-sum probe (aux_kernels.cu).
+// Launchers of the shape-agnostic fallback matmul, the integer block-sum probe and RMSNorm
+// (aux_kernels.cu).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -11,5 +12,9 @@ cudaError_t mul_mat_generic_launch(float *y, const void *x, const uint8_t *w, in
 
 cudaError_t block_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long long n_blocks, int wt,
                               cudaStream_t stream);
+
+// y[j][i] = x[j][i] / sqrt(mean_i(x[j][i]^2) + 1e-5) for ne1 rows of ne0 floats (rows 16-byte aligned
+// when ne0 % 4 == 0, which selects the vector path).
+cudaError_t rms_norm_f32_launch(float *dst, const float *src, int ne0, int ne1, cudaStream_t stream);
 
 }  // namespace htp

@@ -192,6 +192,29 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   }
   uint32_t op;
   memcpy(&op, &req->op, sizeof(op));
+  if (op == HTP_OPS_RMS_NORM_F32) {
+    // op_executor.cc:81-93: one size for both buffers, ne0 * ne1 floats
+    RmsNormF32Params rp;
+    memcpy(&rp, req->payload, sizeof(rp));
+    if (rp.ne0 <= 0 || rp.ne1 <= 0) {
+      return -1;
+    }
+    const size_t bytes = (size_t) rp.ne0 * (size_t) rp.ne1 * sizeof(float);
+    uint8_t     *dst   = resolve(rp.dst, bytes);
+    uint8_t     *src   = resolve(rp.src, bytes);
+    if (!dst || !src) {
+      return -1;
+    }
+    if (!g.batch.ops.empty()) {
+      flush_batch();  // stream order then covers every dependence on the pending mat-vecs
+    }
+    const int rc = htp_b200_rms_norm_f32(reinterpret_cast<float *>(dst), reinterpret_cast<const float *>(src), rp.ne0,
+                                         rp.ne1, g.stream);
+    if (rc == 0) {
+      g.pending_out.add((uintptr_t) dst, (uintptr_t) dst + bytes);
+    }
+    return rc;
+  }
   int weight_type, act_type;
   switch (op) {
     case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32: weight_type = 2, act_type = HTP_B200_ACT_F32; break;
@@ -518,10 +541,21 @@ AEEResult htp_ops_destroy_channel(remote_handle64 handle) {
   return HTP_AEE_SUCCESS;
 }
 
+// Synchronous, like the FastRPC call it stands for (src/dsp/commu.c: htp_ops_rms_norm_f32 maps the
+// two buffers and runs hvx_rms_norm_f32): fd0/offset0 = dst, fd1/offset1 = src.
 AEEResult htp_ops_rms_norm_f32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1, int32_t offset1,
                                int32_t ne0, int32_t ne1) {
-  (void) handle, (void) fd0, (void) offset0, (void) fd1, (void) offset1, (void) ne0, (void) ne1;
-  return HTP_AEE_EUNSUPPORTED;
+  (void) handle;
+  if (!set_session_device() || !g.backend) {
+    return HTP_AEE_EFAILED;
+  }
+  alignas(8) uint8_t raw[sizeof(OpComputeRequest) + sizeof(RmsNormF32Params)];
+  OpComputeRequest  *req = reinterpret_cast<OpComputeRequest *>(raw);
+  req->op                = HTP_OPS_RMS_NORM_F32;
+  RmsNormF32Params rp;
+  rp.dst.fd = fd0, rp.dst.offset = offset0, rp.src.fd = fd1, rp.src.offset = offset1, rp.ne0 = ne0, rp.ne1 = ne1;
+  memcpy(req->payload, &rp, sizeof(rp));
+  return execute_op_simple(req) == 0 ? HTP_AEE_SUCCESS : HTP_AEE_EFAILED;
 }
 
 AEEResult htp_ops_mat_mul_permuted_w16a32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1,

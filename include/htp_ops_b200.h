@@ -82,6 +82,11 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
  * src/dsp/op_executor.cc:124-126) evaluated in 64 bits.  0 for an unknown type or k % 32 != 0. */
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
 
+/* RMSNorm over ne1 rows of ne0 floats: y = x / sqrt(mean(x^2) + 1e-5) (eps fixed as in the reference).
+ * Replaces hvx_rms_norm_f32 (reference include/dsp/ops.h:15, src/dsp/ops/rms_norm.c:68-84): same argument
+ * rules (non-null, non-zero sizes, 128-byte aligned pointers -> else -1), device pointers + stream. */
+int htp_b200_rms_norm_f32(float *dst, const float *src, int ne0, int ne1, void *stream);
+
 /* Waits for `stream`, then returns and clears the first error code a kernel recorded on it
  * (0 = none), or -2 when the stream itself is in error. */
 int htp_b200_stream_status(void *stream);

@@ -410,3 +410,39 @@ int htp_oracle_mul_mat_f32(float *y, const void *act, int act_is_f16, const uint
   free(act32);
   return 0;
 }
+
+/* ---------------------------------------------------------------- RMSNorm (next-row f1)
+ *
+ * Restates the reference's scalar statement rms_norm_f32_ref (src/host/test.c:60-80): per row
+ * sum of squares, mean = sum / ne0, scale = 1 / sqrt(mean + 1e-5), y = x * scale.  wide != 0
+ * accumulates the sum in double (the gate the GPU kernel is held to); wide == 0 is the reference's
+ * own float loop, term by term.  Argument rules as hvx_rms_norm_f32 (src/dsp/ops/rms_norm.c:69-71). */
+int htp_oracle_rms_norm_f32(float *dst, const float *src, int64_t ne0, int64_t ne1, int wide) {
+  if (!dst || !src || ne0 <= 0 || ne1 <= 0) {
+    return -1;
+  }
+  const float eps = 1e-5f;
+  for (int64_t j = 0; j < ne1; ++j) {
+    const float *x = src + j * ne0;
+    float       *y = dst + j * ne0;
+    float        scale;
+    if (wide) {
+      double sum = 0.0;
+      for (int64_t i = 0; i < ne0; ++i) {
+        sum += (double) x[i] * (double) x[i];
+      }
+      scale = (float) (1.0 / sqrt(sum / (double) ne0 + (double) eps));
+    } else {
+      float sum = 0;
+      for (int64_t i = 0; i < ne0; ++i) {
+        sum += x[i] * x[i];
+      }
+      const float mean = sum / ne0;
+      scale            = 1.0f / sqrtf(mean + eps);
+    }
+    for (int64_t i = 0; i < ne0; ++i) {
+      y[i] = x[i] * scale;
+    }
+  }
+  return 0;
+}

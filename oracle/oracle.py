@@ -53,6 +53,8 @@ def load(path: str | os.PathLike | None = None):
     lib.htp_oracle_block_sums.argtypes = [vp, vp, vp, i64, i32]
     lib.htp_oracle_mul_mat_f64.restype = i32
     lib.htp_oracle_mul_mat_f64.argtypes = [vp, vp, vp, i32, vp, i64, i64, i64, i32, i32]
+    lib.htp_oracle_rms_norm_f32.restype = i32
+    lib.htp_oracle_rms_norm_f32.argtypes = [vp, vp, i64, i64, i32]
     lib.htp_oracle_mul_mat_f32.restype = i32
     lib.htp_oracle_mul_mat_f32.argtypes = [vp, vp, i32, vp, i64, i64, i64, i32, i32]
     if path is None:
@@ -128,6 +130,24 @@ def mul_mat_f32(act: np.ndarray, wq: np.ndarray, n: int, wtype: int, threads: in
 
 # ----------------------------------------------------------------------------------------------
 # Independent numpy restatement (small cases): cross-checks the C code above in the CPU tests.
+
+def rms_norm_f32(x: np.ndarray, wide: bool = True) -> np.ndarray:
+    """RMSNorm of every row of x (fp32), eps 1e-5, as the reference's scalar statement
+    (src/host/test.c:60-80); wide=True accumulates the sum of squares in double."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.ndim == 2
+    y = np.empty_like(x)
+    rc = load().htp_oracle_rms_norm_f32(_ptr(y), _ptr(x), x.shape[1], x.shape[0], 1 if wide else 0)
+    assert rc == 0
+    return y
+
+
+def np_rms_norm_f32(x: np.ndarray) -> np.ndarray:
+    """Independent numpy restatement (double arithmetic, rounded once at the end)."""
+    xd = np.asarray(x, dtype=np.float64)
+    scale = 1.0 / np.sqrt((xd * xd).mean(axis=1, keepdims=True) + np.float64(np.float32(1e-5)))
+    return (xd * scale.astype(np.float32).astype(np.float64)).astype(np.float32)
+
 
 def np_unpack(wq: np.ndarray, n: int, k: int, wtype: int):
     """-> (values int8 [N][K], scales float32 [N][K/32]) from packed bytes."""

@@ -22,7 +22,7 @@ def test_session_lifecycle(pkg, lib):
     assert lib.execute_op_simple(None) == -1
     assert lib.htp_ops_init_backend(h) == 0
     assert lib.htp_ops_test_ops(h) == 0
-    assert lib.htp_ops_rms_norm_f32(h, 0, 0, 0, 0, 32, 1) != 0  # not on this path (yet)
+    assert lib.htp_ops_rms_norm_f32(h, 0, 0, 0, 0, 32, 1) != 0  # handle 0 names no buffer
     assert lib.htp_ops_rpc_mat_mul_permuted_w16a32(0, 0, 0, 0, 0, 0, 1, 32, 32) != 0
     fd = lib.htp_buf_alloc(1000)
     assert fd > 0 and lib.htp_buf_size(fd) == 1000 and lib.htp_buf_is_host(fd) == 0

@@ -144,3 +144,15 @@ def test_golden_cfg4_first_chunk(oracle, wl):
     y = oracle.mul_mat_f64(x, part, wl.ROW_CHUNK, cfg.ops[0].wtype)
     head = np.array(g["m1"]["oracle"]["head"])
     assert np.allclose(y[:, :head.shape[1]], head, rtol=0, atol=1e-12 * g["m1"]["oracle"]["max_abs"])
+
+
+def test_rms_norm_oracle_restatements_agree(oracle):
+    """C oracle (double accumulation), the reference's float loop and the numpy restatement on the
+    reference test's input range [-20, 20] (src/host/test.c:100-102), plus a known answer."""
+    rng = np.random.Generator(np.random.PCG64(5))
+    x = (rng.random((6, 1000), dtype=np.float32) * 40.0 - 20.0).astype(np.float32)
+    a, b, c = oracle.rms_norm_f32(x), oracle.np_rms_norm_f32(x), oracle.rms_norm_f32(x, wide=False)
+    assert np.abs(a - b).max() <= 2e-7 and np.abs(a - c).max() <= 1e-5
+    ones = np.full((1, 64), 3.0, dtype=np.float32)  # mean of squares 9 -> scale 1/sqrt(9.00001)
+    assert np.allclose(oracle.rms_norm_f32(ones), 3.0 / np.sqrt(9.0 + 1e-5), rtol=0, atol=1e-7)
+    assert (oracle.rms_norm_f32(np.zeros((2, 8), dtype=np.float32)) == 0).all()
