@@ -35,9 +35,10 @@ REQUEST_TYPE_OP_COMPUTE = 2
 
 TYPE_Q4_0 = 2
 TYPE_Q8_0 = 8
+TYPE_IQ4_NL = 20
 ACT_F32 = 0
 ACT_F16 = 1
-BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34}
+BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ4_NL: 18}
 
 # every symbol include/*.h declares, with (restype, argtypes)
 _vp, _i, _u, _sz, _i64, _u64 = (ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t, ctypes.c_int64,

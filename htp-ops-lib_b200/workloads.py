@@ -18,7 +18,9 @@ import numpy as np
 
 TYPE_Q4_0 = 2
 TYPE_Q8_0 = 8
-BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34}
+TYPE_IQ4_NL = 20
+BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ4_NL: 18}
+IQ4_NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.float32)
 
 
 def _round_half_away(x: np.ndarray) -> np.ndarray:
@@ -64,9 +66,30 @@ def quantize_q8_0(w: np.ndarray) -> np.ndarray:
     return out.reshape(-1)
 
 
+def quantize_iq4_nl(w: np.ndarray) -> np.ndarray:
+    """fp32 [N][K] -> uint8 [N * K/32 * 18]: d = (signed value of max |w|) / -127 as fp16, every element
+    takes the table entry nearest to w / d (first one on ties); the Q4_0 nibble order."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    assert k % 32 == 0
+    blk = w.reshape(n, k // 32, 32)
+    idx = np.abs(blk).argmax(axis=2)
+    vmax = np.take_along_axis(blk, idx[..., None], axis=2)[..., 0]
+    d16 = (vmax / np.float32(-127.0)).astype(np.float16)
+    d = d16.astype(np.float32)
+    safe = np.where(d == 0, np.float32(1), d)
+    t = blk / safe[..., None]
+    q = np.abs(t[..., None] - IQ4_NL_VALUES).argmin(axis=-1)
+    q = np.where(d[..., None] == 0, 8, q).astype(np.uint8)
+    out = np.empty((n, k // 32, 18), dtype=np.uint8)
+    out[..., :2] = d16.view(np.uint8).reshape(n, k // 32, 2)
+    out[..., 2:] = q[..., :16] | (q[..., 16:] << 4)
+    return out.reshape(-1)
+
+
 def quantize(w: np.ndarray, wtype: int, row_chunk: int = 4096) -> np.ndarray:
     """Packs in row chunks so that a 128256 x 4096 matrix does not need tens of GB of temporaries."""
-    fn = quantize_q4_0 if wtype == TYPE_Q4_0 else quantize_q8_0
+    fn = {TYPE_Q4_0: quantize_q4_0, TYPE_Q8_0: quantize_q8_0, TYPE_IQ4_NL: quantize_iq4_nl}[wtype]
     n = w.shape[0]
     if n <= row_chunk:
         return fn(w)

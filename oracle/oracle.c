@@ -202,14 +202,63 @@ static void quantize_rows_q8_0(void *p, int64_t r0, int64_t r1) {
   }
 }
 
-/* type: 2 = Q4_0, 8 = Q8_0 (ggml numbering).  Returns bytes written, or -1. */
+/* IQ4_NL: the 18-byte block of Q4_0 with a non-linear value table instead of q - 8
+ * (reference table: src/dsp/ops/mat_mul.c:29-32; it is ggml's kvalues_iq4nl). */
+static const int8_t kIq4nlValues[16] = { -127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113 };
+
+/* Packer for synthetic IQ4_NL weights: d = (signed value of max |w|) / -127 rounded to fp16, each
+ * element takes the table entry nearest to w / d (ggml's quantiser without its scale search). */
+static void quantize_rows_iq4_nl(void *p, int64_t r0, int64_t r1) {
+  struct quant_ctx *c  = (struct quant_ctx *) p;
+  const int64_t     nb = c->k / 32;
+  for (int64_t r = r0; r < r1; ++r) {
+    for (int64_t b = 0; b < nb; ++b) {
+      const float *x   = c->w + r * c->k + b * 32;
+      uint8_t     *blk = c->out + (r * nb + b) * 18;
+      float        amax = 0.0f, vmax = 0.0f;
+      for (int i = 0; i < 32; ++i) {
+        float a = fabsf(x[i]);
+        if (a > amax) {
+          amax = a;
+          vmax = x[i];
+        }
+      }
+      uint16_t dbits = f32_to_f16_bits(vmax / -127.0f);
+      float    d     = f16_bits_to_f32(dbits);
+      memcpy(blk, &dbits, 2);
+      uint8_t q[32];
+      for (int i = 0; i < 32; ++i) {
+        int best = 8;  /* value 1, the entry nearest to 0 */
+        if (d != 0.0f) {
+          const float t    = x[i] / d;
+          float       berr = fabsf(t - (float) kIq4nlValues[0]);
+          best             = 0;
+          for (int j = 1; j < 16; ++j) {
+            const float e = fabsf(t - (float) kIq4nlValues[j]);
+            if (e < berr) {
+              berr = e;
+              best = j;
+            }
+          }
+        }
+        q[i] = (uint8_t) best;
+      }
+      for (int i = 0; i < 16; ++i) {
+        blk[2 + i] = (uint8_t) (q[i] | (q[i + 16] << 4));
+      }
+    }
+  }
+}
+
+/* type: 2 = Q4_0, 8 = Q8_0, 20 = IQ4_NL (ggml numbering).  Returns bytes written, or -1. */
 int64_t htp_oracle_quantize(const float *w, uint8_t *out, int64_t n_rows, int64_t k, int type, int n_threads) {
-  if (k % 32 != 0 || (type != 2 && type != 8)) {
+  if (k % 32 != 0 || (type != 2 && type != 8 && type != 20)) {
     return -1;
   }
   struct quant_ctx c = { w, out, k };
-  parallel_ranges(type == 2 ? quantize_rows_q4_0 : quantize_rows_q8_0, &c, n_rows, n_threads);
-  return n_rows * (k / 32) * (type == 2 ? 18 : 34);
+  parallel_ranges(type == 2 ? quantize_rows_q4_0 : (type == 8 ? quantize_rows_q8_0 : quantize_rows_iq4_nl), &c, n_rows,
+                  n_threads);
+  return n_rows * (k / 32) * (type == 8 ? 34 : 18);
 }
 
 /* ---------------------------------------------------------------- unpack (the contract) */
@@ -223,6 +272,11 @@ static inline void unpack_block(const uint8_t *blk, int type, int8_t v[32], floa
       v[i]      = (int8_t) ((blk[2 + i] & 0x0F) - 8);
       v[i + 16] = (int8_t) ((blk[2 + i] >> 4) - 8);
     }
+  } else if (type == 20) {  /* same nibble order, table values (mat_mul.c:316, 583) */
+    for (int i = 0; i < 16; ++i) {
+      v[i]      = kIq4nlValues[blk[2 + i] & 0x0F];
+      v[i + 16] = kIq4nlValues[blk[2 + i] >> 4];
+    }
   } else {
     for (int i = 0; i < 32; ++i) {
       v[i] = (int8_t) blk[2 + i];
@@ -231,7 +285,7 @@ static inline void unpack_block(const uint8_t *blk, int type, int8_t v[32], floa
 }
 
 static inline int block_bytes(int type) {
-  return type == 2 ? 18 : (type == 8 ? 34 : 0);
+  return (type == 2 || type == 20) ? 18 : (type == 8 ? 34 : 0);
 }
 
 /* dequantise rows [0, n_rows) to fp32 (exact: |value| <= 128 times an fp16 fits fp32). */
@@ -369,7 +423,7 @@ static void mm_rows_f32(void *p, int64_t j0, int64_t j1) {
           wo[i + 16] = (float) ((int) (blk[2 + i] >> 4) - 8) * d;
         }
       }
-    } else {
+    } else if (c->type == 8) {
       for (int64_t b = 0; b < nb; ++b) {
         const uint8_t *blk = row + b * 34;
         uint16_t       dbits;
@@ -378,6 +432,15 @@ static void mm_rows_f32(void *p, int64_t j0, int64_t j1) {
         float      *wo = wrow + b * 32;
         for (int i = 0; i < 32; ++i) {
           wo[i] = (float) (int8_t) blk[2 + i] * d;
+        }
+      }
+    } else {
+      for (int64_t b = 0; b < nb; ++b) {
+        int8_t v[32];
+        float  d;
+        unpack_block(row + b * bb, c->type, v, &d);
+        for (int i = 0; i < 32; ++i) {
+          wrow[b * 32 + i] = (float) v[i] * d;
         }
       }
     }

@@ -19,7 +19,9 @@ import numpy as np
 HERE = Path(__file__).resolve().parent
 TYPE_Q4_0 = 2
 TYPE_Q8_0 = 8
-BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34}
+TYPE_IQ4_NL = 20
+BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ4_NL: 18}
+IQ4_NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int8)
 
 _lib = None
 
@@ -159,6 +161,8 @@ def np_unpack(wq: np.ndarray, n: int, k: int, wtype: int):
         lo = (qs & 0x0F).astype(np.int8) - 8
         hi = (qs >> 4).astype(np.int8) - 8
         vals = np.concatenate([lo, hi], axis=2)
+    elif wtype == TYPE_IQ4_NL:
+        vals = np.concatenate([IQ4_NL_VALUES[qs & 0x0F], IQ4_NL_VALUES[qs >> 4]], axis=2)
     else:
         vals = qs.view(np.int8)
     return vals.reshape(n, k), scales

@@ -156,3 +156,23 @@ def test_rms_norm_oracle_restatements_agree(oracle):
     ones = np.full((1, 64), 3.0, dtype=np.float32)  # mean of squares 9 -> scale 1/sqrt(9.00001)
     assert np.allclose(oracle.rms_norm_f32(ones), 3.0 / np.sqrt(9.0 + 1e-5), rtol=0, atol=1e-7)
     assert (oracle.rms_norm_f32(np.zeros((2, 8), dtype=np.float32)) == 0).all()
+
+
+def test_iq4_nl_unpack_known_answer_and_restatements(oracle, wl):
+    """IQ4_NL = the Q4_0 block with the reference's value table (src/dsp/ops/mat_mul.c:29-32) in the
+    same nibble order: every nibble value at a known position, C against numpy, packers agree."""
+    table = [-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113]
+    blk = np.zeros(18, dtype=np.uint8)
+    blk[:2] = np.array([2.0], dtype=np.float16).view(np.uint8)
+    blk[2:] = np.arange(16, dtype=np.uint8) | ((15 - np.arange(16, dtype=np.uint8)) << 4)
+    w = oracle.dequantize(blk, 1, 32, 20)[0]
+    assert w[:16].tolist() == [2.0 * v for v in table]  # element j < 16: low nibble of byte j
+    assert w[16:].tolist() == [2.0 * v for v in table[::-1]]  # element j + 16: high nibble of byte j
+    s, t = oracle.block_sums(blk, 20)
+    vals = table + table[::-1]
+    assert s[0] == sum(vals) and t[0] == sum((i + 1) * v for i, v in enumerate(vals))
+    rng = np.random.Generator(np.random.PCG64(21))
+    wf = rng.standard_normal((48, 512), dtype=np.float32) * np.float32(0.02)
+    assert (wl.quantize(wf, 20) == oracle.quantize(wf, 20)).all()
+    wq, x = wl.random_case(22, 20, False, 3, 512, 48)
+    assert np.abs(oracle.mul_mat_f64(x, wq, 48, 20) - oracle.np_mul_mat_f64(x, wq, 48, 20)).max() < 1e-12
