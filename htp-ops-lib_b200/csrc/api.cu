@@ -130,7 +130,7 @@ inline bool aligned128(const void *p) {
 }
 
 inline int wt_index(int weight_type) {
-  return weight_type == 2 ? 0 : (weight_type == 8 ? 1 : -1);
+  return weight_type == 2 ? 0 : (weight_type == 8 ? 1 : (weight_type == 20 ? 2 : -1));  // kQ4, kQ8, kIQ4
 }
 
 // Decode path: M <= 8 rows of activations per launch, K split into launches whose activation
@@ -141,15 +141,16 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
   if (!sc) {
     return -2;
   }
-  const int bb      = wt == 0 ? 18 : 34;
+  const int bb      = wt == 1 ? 34 : 18;
   const int kb_all  = k / 32;
   const int periods = kb_all / 8;
   const int stage   = kGemvTileRows * gemv_row_pitch(wt);
   const int budget  = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
   const int asz     = a16 ? 2 : 4;
 
-  for (int m0 = 0; m0 < m; m0 += 8) {
-    const int mm   = (m - m0) < 8 ? (m - m0) : 8;
+  const int slice = wt == 2 ? 2 : 8;  // IQ4_NL has the two-token integer path only
+  for (int m0 = 0; m0 < m; m0 += slice) {
+    const int mm   = (m - m0) < slice ? (m - m0) : slice;
     const int mpad = mm <= 1 ? 1 : (mm <= 2 ? 2 : (mm <= 4 ? 4 : 8));
     int       nchunks = 1, chunk_periods = periods, nst = 0;
     for (;; ++nchunks) {
@@ -268,7 +269,8 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
 
 bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type) {
   const int wt = wt_index(weight_type);
-  if (wt < 0 || m <= 0 || m > 8 || k <= 0 || n <= 0 || k % 256 != 0 || n % 32 != 0 || g_opt_force_generic) {
+  if (wt < 0 || m <= 0 || m > (wt == 2 ? 2 : 8) || k <= 0 || n <= 0 || k % 256 != 0 || n % 32 != 0 ||
+      g_opt_force_generic) {
     return false;
   }
   const bool a16 = act_type == HTP_B200_ACT_F16;
@@ -303,7 +305,7 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
   }
   const bool a16   = act_type == HTP_B200_ACT_F16;
   const int  mpad  = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
-  const int  bb    = wt == 0 ? 18 : 34;
+  const int  bb    = wt == 1 ? 34 : 18;
   const int  stage = kGemvTileRows * gemv_row_pitch(wt);
   const int  sb    = gemv_stage_blocks(wt);
   static thread_local GemvBatchArgs args;  // ~25 KB of kernel parameters, reused between launches
@@ -430,7 +432,7 @@ size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n) {
   if (wt < 0 || k <= 0 || n <= 0 || k % 32 != 0) {
     return 0;
   }
-  return (size_t) n * (size_t) (k / 32) * (wt == 0 ? 18u : 34u);
+  return (size_t) n * (size_t) (k / 32) * (wt == 1 ? 34u : 18u);
 }
 
 int htp_b200_stream_status(void *stream) {

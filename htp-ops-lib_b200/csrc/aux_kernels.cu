@@ -35,6 +35,19 @@ __device__ __forceinline__ void unpack_block_values(const uint8_t *blk, float (&
         v[q4_0_word_elem(t, r, 1)] = __high2float(p);
       }
     }
+  } else if constexpr (WT == kIQ4) {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      uint32_t r[2];
+      iq4nl_unpack_word(ld_word_2b(blk + 2 + 4 * t), r[0], r[1]);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[iq4nl_word_elem(t, h, i)] = (float) (int8_t) (r[h] >> (8 * i));
+        }
+      }
+    }
   } else {
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
@@ -135,6 +148,12 @@ cudaError_t mul_mat_generic_launch(float *y, const void *x, const uint8_t *w, in
     } else {
       mul_mat_generic_kernel<kQ4, false><<<grid, block, 0, stream>>>(y, x, w, M, K, N);
     }
+  } else if (wt == kIQ4) {
+    if (a16) {
+      mul_mat_generic_kernel<kIQ4, true><<<grid, block, 0, stream>>>(y, x, w, M, K, N);
+    } else {
+      mul_mat_generic_kernel<kIQ4, false><<<grid, block, 0, stream>>>(y, x, w, M, K, N);
+    }
   } else {
     if (a16) {
       mul_mat_generic_kernel<kQ8, true><<<grid, block, 0, stream>>>(y, x, w, M, K, N);
@@ -154,6 +173,8 @@ cudaError_t block_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long lon
   const long long grid    = (n_blocks + threads - 1) / threads;
   if (wt == kQ4) {
     block_sums_kernel<kQ4><<<(unsigned) grid, threads, 0, stream>>>(w, s, t, n_blocks);
+  } else if (wt == kIQ4) {
+    block_sums_kernel<kIQ4><<<(unsigned) grid, threads, 0, stream>>>(w, s, t, n_blocks);
   } else {
     block_sums_kernel<kQ8><<<(unsigned) grid, threads, 0, stream>>>(w, s, t, n_blocks);
   }

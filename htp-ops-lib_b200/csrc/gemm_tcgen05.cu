@@ -332,7 +332,30 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw, int q, u
     const uint32_t sw   = raw[off >> 2] ^ (WT == kQ8 ? 0x80808080u : 0u);
     const uint16_t sbit = (off & 2) ? (uint16_t) (sw >> 16) : (uint16_t) (sw & 0xffff);
     const __half2  d2   = __half2half2(__ushort_as_half(sbit));
-    if constexpr (WT == kQ4) {
+    if constexpr (WT == kIQ4) {
+      // table values as signed bytes (unpack.cuh), biased to 0..255, then the 0x6400 trick as for Q8_0
+      const __half2 k1152 = u32_as_h2(0x64806480u);
+      uint32_t      lo[8], hi[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int      o = off + 2 + 4 * i;
+        const uint32_t w = (o & 2) ? __byte_perm(raw[o >> 2], raw[(o >> 2) + 1], 0x5432) : raw[o >> 2];
+        uint32_t       r0, r1;  // r0 = elements (4i, 16+4i, 4i+1, 17+4i), r1 = (4i+2, 18+4i, 4i+3, 19+4i)
+        iq4nl_unpack_word(w, r0, r1);
+        r0 ^= 0x80808080u, r1 ^= 0x80808080u;
+        auto pair = [&](uint32_t r, uint32_t sel) {
+          return h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(r, 0x64646464u, sel)), k1152), d2));
+        };
+        lo[2 * i]     = pair(r0, 0x4240);  // bytes 0, 2
+        hi[2 * i]     = pair(r0, 0x4341);  // bytes 1, 3
+        lo[2 * i + 1] = pair(r1, 0x4240);
+        hi[2 * i + 1] = pair(r1, 0x4341);
+      }
+      out[4 * h + 0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      out[4 * h + 1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+      out[4 * h + 2] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      out[4 * h + 3] = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+    } else if constexpr (WT == kQ4) {
       uint32_t lo[8], hi[8];  // fp16 pairs in element order: lo = elements 0..15, hi = 16..31
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -987,6 +1010,9 @@ cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, c
   const bool one = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
   if (wt == kQ4) {
     return one ? launch<kQ4, 128, false>(args, sm_count, stream) : launch<kQ4, 256, true>(args, sm_count, stream);
+  }
+  if (wt == kIQ4) {
+    return one ? launch<kIQ4, 128, false>(args, sm_count, stream) : launch<kIQ4, 256, true>(args, sm_count, stream);
   }
   return one ? launch<kQ8, 128, false>(args, sm_count, stream) : launch<kQ8, 256, true>(args, sm_count, stream);
 }

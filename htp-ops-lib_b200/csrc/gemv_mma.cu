@@ -58,7 +58,8 @@ struct Cfg {
   // four signed base-128 digits of a 28-bit fixed-point value (column = 4 m + digit), one
   // m16n8k32 MMA covers a whole block, and the -8 offset of the format comes in through the MMA's
   // accumulator input.
-  static constexpr bool I8       = (WT == kQ4 && MPAD <= 2);
+  static constexpr bool I8       = ((WT == kQ4 || WT == kIQ4) && MPAD <= 2);
+  static_assert(WT != kIQ4 || I8, "IQ4_NL runs on the integer path only (two tokens per launch)");
   static constexpr int  CH       = I8 ? 1 : ((!A16 && MPAD == 8) ? 2 : 1);  // chained MMAs per k-step
   static constexpr int  NC       = I8 ? 4 * MPAD : (A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD));  // MMA columns in use
   static constexpr bool SPLITCOL = !I8 && (!A16 && MPAD < 8);             // column = 2 m + piece
@@ -172,7 +173,9 @@ __device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int 
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            int r = __float2int_rn(xval(m, b * 32 + 16 * h + 4 * t + i) * sc);
+            // block element that byte i of A register h (rows g / g + 8) of this lane position holds
+            const int e = WT == kIQ4 ? iq4nl_word_elem(t, h, i) : 16 * h + 4 * t + i;
+            int       r = __float2int_rn(xval(m, b * 32 + e) * sc);
 #pragma unroll
             for (int d = 0; d < 4; ++d) {
               const int dv = d < 3 ? ((r + 64) & 127) - 64 : r;
@@ -190,7 +193,8 @@ __device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int 
         sd += __shfl_xor_sync(0xffffffffu, sd, 1);
         sd += __shfl_xor_sync(0xffffffffu, sd, 2);
         if (t == 0) {
-          reinterpret_cast<int *>(dst + C::NC * 4)[4 * m + d] = kMagicBits - 8 * sd;
+          // (Q4_0: value = nibble - 8; IQ4_NL: the table values are used as they are)
+          reinterpret_cast<int *>(dst + C::NC * 4)[4 * m + d] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
         }
       }
     }
@@ -367,14 +371,25 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
     qa = lds32(ra + 2 + 4 * t);
     qb = lds32(rb + 2 + 4 * t);
   }
-  // byte i of the word: low nibble = element 4t + i, high nibble = element 16 + 4t + i
-  const uint32_t a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
-  const uint32_t a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
-  int            d0, d1, d2, d3;
-  asm volatile(
-    "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-    : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-    : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+  uint32_t a0, a1, a2, a3;
+  int      d0, d1, d2, d3;
+  if constexpr (WT == kIQ4) {
+    // table values as signed bytes, in the element order of iq4nl_word_elem
+    iq4nl_unpack_word(qa, a0, a2);
+    iq4nl_unpack_word(qb, a1, a3);
+    asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+  } else {
+    // byte i of the word: low nibble = element 4t + i, high nibble = element 16 + 4t + i
+    a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
+    a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+    asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+  }
   const float da = lds_scale(ra);
   const float db = lds_scale(rb);
   // int bits -> float: subtract the bias, two results per instruction (packed fp32 add)
@@ -417,7 +432,7 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
           block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, neg_magic2, acc[rg]);
         }
       }
-    } else {
+    } else if constexpr (WT != kIQ4) {
       uint2 bf[2][2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
@@ -1074,7 +1089,7 @@ EncodeTiledFn encode_tiled_fn() {
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
   size_t b;
-  if (wt == kQ4 && mpad <= 2) {  // integer path: 4 digit columns per token + their accumulator inputs
+  if ((wt == kQ4 || wt == kIQ4) && mpad <= 2) {  // integer path: 4 digit columns per token + their accumulator inputs
     const int nc = 4 * mpad;
     b            = (size_t) kblocks * (nc * 4 + nc / 2) * 8;
   } else {
@@ -1125,7 +1140,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
     return cudaErrorNotSupported;
   }
   CUtensorMap      wmap;
-  const int        bb         = wt == kQ4 ? 18 : 34;
+  const int        bb         = wt == kQ8 ? 34 : 18;
   const cuuint64_t gdim[2]    = { (cuuint64_t) kblocks * bb / 8, (cuuint64_t) n };
   const cuuint64_t gstride[1] = { (cuuint64_t) w_row_bytes };
   const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
@@ -1157,6 +1172,17 @@ cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, in
     return a16 ? launch_mpad<kQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
                : launch_mpad<kQ4, false>(args, wmap, mpad, grid, smem, stream, pdl);
   }
+  if (wt == kIQ4) {  // integer path only: the caller slices the tokens in pairs
+    if (mpad > 2) {
+      return cudaErrorInvalidValue;
+    }
+    if (mpad == 1) {
+      return a16 ? launch_one<kIQ4, true, 1>(args, wmap, grid, smem, stream, pdl)
+                 : launch_one<kIQ4, false, 1>(args, wmap, grid, smem, stream, pdl);
+    }
+    return a16 ? launch_one<kIQ4, true, 2>(args, wmap, grid, smem, stream, pdl)
+               : launch_one<kIQ4, false, 2>(args, wmap, grid, smem, stream, pdl);
+  }
   return a16 ? launch_mpad<kQ8, true>(args, wmap, mpad, grid, smem, stream, pdl)
              : launch_mpad<kQ8, false>(args, wmap, mpad, grid, smem, stream, pdl);
 }
@@ -1166,6 +1192,17 @@ cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, i
   if (wt == kQ4) {
     return a16 ? batch_mpad<kQ4, true>(args, mpad, grid, smem, stream, pdl)
                : batch_mpad<kQ4, false>(args, mpad, grid, smem, stream, pdl);
+  }
+  if (wt == kIQ4) {
+    if (mpad > 2) {
+      return cudaErrorInvalidValue;
+    }
+    if (mpad == 1) {
+      return a16 ? batch_one<kIQ4, true, 1>(args, grid, smem, stream, pdl)
+                 : batch_one<kIQ4, false, 1>(args, grid, smem, stream, pdl);
+    }
+    return a16 ? batch_one<kIQ4, true, 2>(args, grid, smem, stream, pdl)
+               : batch_one<kIQ4, false, 2>(args, grid, smem, stream, pdl);
   }
   return a16 ? batch_mpad<kQ8, true>(args, mpad, grid, smem, stream, pdl)
              : batch_mpad<kQ8, false>(args, mpad, grid, smem, stream, pdl);

@@ -16,16 +16,16 @@ constexpr int kGemvMaxGrid     = 1024;    // scratch is sized for this many CTAs
 constexpr int kGemvErrProducerWait = 101;
 constexpr int kGemvErrConsumerWait = 102;
 
-// 32-weight blocks per pipeline stage and row: 64 for Q4_0 (1152 B), 32 for Q8_0 (1088 B), so a
+// 32-weight blocks per pipeline stage and row: 64 for Q4_0 / IQ4_NL (1152 B), 32 for Q8_0 (1088 B), so a
 // stage of 32 rows is ~36 KB in either format.
 constexpr int gemv_stage_blocks(int wt) {
-  return wt == 0 ? 64 : 32;
+  return wt == 1 ? 32 : 64;
 }
 
 // Shared-memory pitch of one weight row inside a stage: the stage's bytes plus 16, an odd
 // multiple of 16, so that eight consecutive rows start in eight different 16-byte bank groups.
 constexpr int gemv_row_pitch(int wt) {
-  return wt == 0 ? 1168 /* 64*18 = 1152 -> 73*16 */ : 1104 /* 32*34 = 1088 -> 69*16 */;
+  return wt == 1 ? 1104 /* 32*34 = 1088 -> 69*16 */ : 1168 /* 64*18 = 1152 -> 73*16 */;
 }
 
 struct GemvArgs {

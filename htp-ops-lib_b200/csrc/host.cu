@@ -219,6 +219,7 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   switch (op) {
     case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32: weight_type = 2, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_PERMUTED_W8D16A32: weight_type = 8, act_type = HTP_B200_ACT_F32; break;
+    case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL: weight_type = 20, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_W4D16A16: weight_type = 2, act_type = HTP_B200_ACT_F16; break;
     case HTP_OPS_MAT_MUL_W8D16A16: weight_type = 8, act_type = HTP_B200_ACT_F16; break;
     default: return -1;  // unknown, or not built in this library
@@ -338,7 +339,14 @@ void servicer_loop() {
         }
         switch (rh->type) {
           case REQUEST_TYPE_OP_COMPUTE: {
-            if (rsize < sizeof(RequestHeader) + sizeof(OpComputeRequest) + sizeof(MatMulParams)) {
+            // the payload must hold the parameter block of the op it names
+            size_t need = sizeof(RequestHeader) + sizeof(OpComputeRequest);
+            if (rsize >= need) {
+              uint32_t op;
+              memcpy(&op, reinterpret_cast<const uint8_t *>(rh) + sizeof(RequestHeader), sizeof(op));
+              need += op == HTP_OPS_RMS_NORM_F32 ? sizeof(RmsNormF32Params) : sizeof(MatMulParams);
+            }
+            if (rsize < need) {
               rh->state = -1;
               break;
             }

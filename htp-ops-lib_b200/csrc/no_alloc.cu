@@ -94,7 +94,7 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
   }
   const bool   a16     = act_type == HTP_B200_ACT_F16;
   const int    mpad    = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
-  const int    bb      = wt == 0 ? 18 : 34;
+  const int    bb      = wt == 1 ? 34 : 18;
   const int    kblocks = k / 32;
   const int    stage   = kGemvTileRows * gemv_row_pitch(wt);
   const int    budget  = max_smem < kGemvSmemBudget ? max_smem : kGemvSmemBudget;

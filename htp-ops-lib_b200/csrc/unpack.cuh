@@ -14,8 +14,9 @@
 
 namespace htp {
 
-constexpr int kQ4 = 0;
-constexpr int kQ8 = 1;
+constexpr int kQ4  = 0;
+constexpr int kQ8  = 1;
+constexpr int kIQ4 = 2;  // IQ4_NL: the Q4_0 block with a 16-entry value table instead of q - 8
 
 template <int WT>
 struct BlockTraits;
@@ -26,6 +27,10 @@ struct BlockTraits<kQ4> {
 template <>
 struct BlockTraits<kQ8> {
   static constexpr int kBytes = 34;
+};
+template <>
+struct BlockTraits<kIQ4> {
+  static constexpr int kBytes = 18;
 };
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) {
@@ -67,6 +72,31 @@ __device__ __forceinline__ void q8_0_unpack_word(uint32_t w, uint32_t (&h)[2]) {
 // Element index of half `s` of output pair `r` when the word is quant word `u` (0..7).
 __device__ __host__ __forceinline__ constexpr int q8_0_word_elem(int u, int r, int s) {
   return 4 * u + 2 * r + s;
+}
+
+// IQ4_NL (reference table: src/dsp/ops/mat_mul.c:29-32): four 4-bit indices in the low 16 bits of
+// `idx16` (index j in bits 4j .. 4j+3) -> byte j of the result = table[index j] as a signed byte.
+// The table does not fit one byte permute (8 entries): the two halves are looked up with the low
+// three index bits and a third permute picks per byte by the fourth bit.
+__device__ __forceinline__ uint32_t iq4nl_lookup4(uint32_t idx16) {
+  constexpr uint32_t T0 = 0xBFAD9881u;  // -127 -104  -83  -65
+  constexpr uint32_t T1 = 0xF6EADDCFu;  //  -49  -35  -22  -10
+  constexpr uint32_t T2 = 0x26190D01u;  //    1   13   25   38
+  constexpr uint32_t T3 = 0x71594535u;  //   53   69   89  113
+  const uint32_t     s  = idx16 & 0x7777u;
+  const uint32_t     lo = __byte_perm(T0, T1, s);
+  const uint32_t     hi = __byte_perm(T2, T3, s);
+  return __byte_perm(lo, hi, 0x3210u + ((idx16 >> 1) & 0x4444u));  // byte j of lo, or byte j of hi (4 + j)
+}
+// Quant word `w` of a block (bytes 4t .. 4t+3; low nibble of byte j = element j, high nibble =
+// element j + 16) -> r0 = values of elements (4t, 16+4t, 4t+1, 17+4t), r1 = (4t+2, 18+4t, 4t+3, 19+4t).
+__device__ __forceinline__ void iq4nl_unpack_word(uint32_t w, uint32_t &r0, uint32_t &r1) {
+  r0 = iq4nl_lookup4(w);
+  r1 = iq4nl_lookup4(w >> 16);
+}
+// Element (0..31) of byte `i` of register `h` (0 = r0, 1 = r1) above, for quant word `t`.
+__device__ __host__ __forceinline__ constexpr int iq4nl_word_elem(int t, int h, int i) {
+  return 4 * t + 2 * h + (i >> 1) + ((i & 1) << 4);
 }
 
 // Which block element feeds the warp-MMA (m16n8k16) A fragment of the lane with thread-in-group
