@@ -229,7 +229,49 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
     run_case("cfg2_q4_0_prefill_14336x4096_m512", wl.CONFIGS["cfg2"], 0, 512, max(3, steps // 10))
     run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(3, steps // 10))
     out["rms_norm_f32_4096x32768"] = measure_rms_norm(torch, lib, peaks, stream_ptr, stream, max(5, steps // 5))
+    out.update(measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream, max(5, steps // 5)))
     out.update(measure_decoder_stack(torch, pkg, lib, wl, peaks, quick))
+    return out
+
+
+def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream, steps):
+    """Decode mat-vecs long enough (151 MB of 4-bit weights, two rotating copies) that launch and
+    pipeline fill stop dominating - Q4_0 and IQ4_NL - and the IQ4_NL prefill GEMM on config 2's shape.
+    Timing does not depend on the weight values: random block bytes with a small fp16 scale."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+
+    def blocks(wtype, k, n):
+        bb = wl.BLOCK_BYTES[wtype]
+        w = torch.randint(0, 256, (n * (k // 32), bb), dtype=torch.uint8, device=dev)
+        w[:, 0], w[:, 1] = 0, 0x20  # fp16 scale 2^-7
+        return w.reshape(-1)
+
+    for name, wtype, a16, m, k, n in (("q4_0_gemv_65536x4096_m1", wl.TYPE_Q4_0, False, 1, 4096, 65536),
+                                      ("iq4_nl_gemv_65536x4096_m1", wl.TYPE_IQ4_NL, False, 1, 4096, 65536),
+                                      ("iq4_nl_prefill_14336x4096_m512", wl.TYPE_IQ4_NL, True, 512, 4096, 14336)):
+        op = wl.MatMul(name, wtype, a16, k, n)
+        copies = 2 if m <= 8 else 1
+        ws = [blocks(wtype, k, n) for _ in range(copies)]
+        x = torch.randn((m, k), device=dev, dtype=torch.float16 if a16 else torch.float32)
+        y = torch.empty((m, n), device=dev, dtype=torch.float32)
+
+        def step(i):
+            assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, k, n, wtype,
+                                        pkg.ACT_F16 if a16 else pkg.ACT_F32, stream_ptr) == 0
+        for i in range(3):
+            step(i)
+        ms = time_region(torch, step, steps, stream) / steps
+        assert lib.htp_b200_stream_status(stream_ptr) == 0
+        r = {"ms": round(ms, 5), "m": m, "k": k, "n": n, "weight_copies": copies}
+        if m <= 8:
+            gb = wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9
+            r.update(GBps=round(gb, 1), frac_of_hbm_peak=round(gb / peaks["hbm_gbs"], 4))
+        else:
+            tf = wl.flops(op, m) / (ms * 1e-3) / 1e12
+            r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
+        out[name] = r
+        del ws
     return out
 
 
