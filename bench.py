@@ -503,7 +503,11 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q8_0,f16,M=1>", "achieved": round(achieved, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                          "peak_source": f"{peaks['source']} (copy bandwidth)", "ms_per_launch": round(k_ms, 5),
-                         "algorithmic_bytes_per_launch": k_bytes, "traffic": read_traffic("cfg4_m1_q8_0")},
+                         "algorithmic_bytes_per_launch": k_bytes,
+                         # the committed capture is of the whole matrix on one GPU; a rank's launch covers its
+                         # share of the rows, and the kernel's DRAM traffic is proportional to rows
+                         "traffic": (None if read_traffic("cfg4_m1_q8_0") is None
+                                     else int(read_traffic("cfg4_m1_q8_0") * k_bytes / total_bytes))},
             "e2e": e2e, "gpu_launches": int(first_launches), "clocks": clocks,
         }
     # single-GPU extras and the CPU baseline: rank 0 at N = 1 only
