@@ -148,7 +148,11 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
   const int budget  = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
   const int asz     = a16 ? 2 : 4;
 
-  const int slice = wt == 2 ? 2 : 8;  // IQ4_NL has the two-token integer path only
+  // Tokens per launch.  IQ4_NL has the two-token integer path only.  fp32 activations of more than
+  // four tokens would need two chained MMAs per k-step and 1 KB of activation fragments per block
+  // (K split over several launches): two launches of four tokens read the weights twice (the
+  // second time mostly from L2) but keep K whole and can join a batched launch.
+  const int slice = wt == 2 ? 2 : ((!a16 && m > 4) ? 4 : 8);
   for (int m0 = 0; m0 < m; m0 += slice) {
     const int mm   = (m - m0) < slice ? (m - m0) : slice;
     const int mpad = mm <= 1 ? 1 : (mm <= 2 ? 2 : (mm <= 4 ? 4 : 8));

@@ -241,9 +241,13 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   }
   const uintptr_t o0 = (uintptr_t) out, a0 = (uintptr_t) act, w0 = (uintptr_t) w;
   PendingBatch   &b  = g.batch;
-  const bool      batchable = htp::mul_mat_batchable(p.m, p.k, p.n, weight_type, act_type);
+  // eight fp32 tokens go in as two operators of four (see run_gemv in api.cu)
+  const bool split8    = act_type == HTP_B200_ACT_F32 && p.m == 8 && weight_type != 20 &&
+                      htp::mul_mat_batchable(4, p.k, p.n, weight_type, act_type);
+  const int  m_eff     = split8 ? 4 : p.m;
+  const bool batchable = split8 || htp::mul_mat_batchable(p.m, p.k, p.n, weight_type, act_type);
   if (!b.ops.empty()) {
-    const bool same_kind = batchable && b.m == p.m && b.weight_type == weight_type && b.act_type == act_type;
+    const bool same_kind = batchable && b.m == m_eff && b.weight_type == weight_type && b.act_type == act_type;
     const bool hazard    = b.writes.overlaps(a0, a0 + act_bytes) || b.writes.overlaps(w0, w0 + w_bytes) ||
                         b.writes.overlaps(o0, o0 + out_bytes) || b.reads.overlaps(o0, o0 + out_bytes);
     if (!same_kind || hazard) {
@@ -259,10 +263,15 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
     return rc;
   }
   if (b.ops.empty()) {
-    b.m = p.m, b.weight_type = weight_type, b.act_type = act_type;
+    b.m = m_eff, b.weight_type = weight_type, b.act_type = act_type;
   }
   b.ops.push_back(htp::MatMulDesc{ reinterpret_cast<float *>(out), act, w, p.k, p.n });
   b.owners.push_back(owner);
+  if (split8) {
+    b.ops.push_back(htp::MatMulDesc{ reinterpret_cast<float *>(out) + (size_t) 4 * p.n,
+                                     reinterpret_cast<const float *>(act) + (size_t) 4 * p.k, w, p.k, p.n });
+    b.owners.push_back(owner);
+  }
   b.writes.add(o0, o0 + out_bytes);
   b.reads.add(a0, a0 + act_bytes);
   b.reads.add(w0, w0 + w_bytes);
