@@ -510,6 +510,40 @@ def run_ours(args):
                                      else int(read_traffic("cfg4_m1_q8_0") * k_bytes / total_bytes))},
             "e2e": e2e, "gpu_launches": int(first_launches), "clocks": clocks,
         }
+    # the sharded prefill case of config 4 (M = 256): each rank multiplies its row shard on the tensor
+    # cores, then the [256][N / R] slabs are gathered into [256][N] on every rank
+    if world > 1:
+        m2, steps2 = 256, max(5, min(20, steps))
+        x2 = torch.randn((m2, op.k), device=dev, dtype=torch.float32, generator=torch.Generator(device=dev)
+                         .manual_seed(4)).to(torch.float16)
+        y2 = torch.empty((m2, n_loc), device=dev, dtype=torch.float32)
+        logits2 = torch.empty((m2, op.n), device=dev, dtype=torch.float32)
+
+        def kernel2(i):
+            assert lib.htp_b200_mul_mat(y2.data_ptr(), x2.data_ptr(), ws[i % copies].data_ptr(), m2, op.k, n_loc,
+                                        op.wtype, pkg.ACT_F16, sp) == 0
+
+        def step2(i):
+            kernel2(i)
+            sharding.all_gather_logits(dist, logits2, y2, m2, op.n, world)
+        for i in range(3):
+            step2(i)
+        barrier()
+        t = torch.tensor([time_region(torch, step2, steps2, stream) / steps2,
+                          time_region(torch, kernel2, steps2, stream) / steps2], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert lib.htp_b200_stream_status(sp) == 0
+        if rank == 0:
+            fl = wl.flops(op, m2)
+            line["prefill_m256"] = {
+                "ms_per_step": round(float(t[0]), 5), "TFLOPs": round(fl / (float(t[0]) * 1e-3) / 1e12, 2),
+                "kernel_ms_per_launch": round(float(t[1]), 5),
+                "kernel_TFLOPs_per_gpu": round(wl.flops(op, m2, n_loc) / (float(t[1]) * 1e-3) / 1e12, 2),
+                "frac_of_tensor_peak_per_gpu": round(wl.flops(op, m2, n_loc) / (float(t[1]) * 1e-3) / 1e12
+                                                     / peaks["tflops"], 4),
+                "gathered_bytes_per_step": m2 * op.n * 4,
+                "note": "whole-job TFLOP/s = 2*256*128256*4096 / max-over-ranks time of GEMM + all-gather"}
+        del x2, y2, logits2
     # single-GPU extras and the CPU baseline: rank 0 at N = 1 only
     if world == 1:
         del ws, w0
