@@ -413,6 +413,51 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
   return 0;
 }
 
+int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                               const void *weight, int m, int k, int n, int weight_type, int act_type, void *stream) {
+  if (!dsts || n_dst < 1 || n_dst > kGemmMaxDst || !activation || !weight || m <= 0 || n <= 0 || k <= 0) {
+    return -1;
+  }
+  const int wt = wt_index(weight_type);
+  // the tensor-core GEMM only: fp16 activations, enough tokens, 16-byte aligned weight rows
+  if (wt < 0 || act_type != HTP_B200_ACT_F16 || m < g_opt_gemm_min_m || k % 256 != 0 || n % 32 != 0) {
+    return -1;
+  }
+  if (dst_ld < n || dst_ld % 32 != 0 || dst_col0 < 0 || dst_col0 % 32 != 0 || dst_col0 + n > dst_ld) {
+    return -1;
+  }
+  if (!aligned128(activation) || !aligned128(weight)) {
+    return -1;
+  }
+  for (int d = 0; d < n_dst; ++d) {
+    if (!dsts[d] || !aligned128(dsts[d])) {
+      return -1;
+    }
+  }
+  DeviceCtx *ctx = current_device_ctx();
+  if (!ctx) {
+    return -2;
+  }
+  cudaStream_t   st = static_cast<cudaStream_t>(stream);
+  StreamScratch *sc = stream_scratch(ctx, st);
+  if (!sc) {
+    return -2;
+  }
+  GemmArgs a = {};
+  a.y = static_cast<float *>(dsts[0]), a.x = activation, a.w = static_cast<const uint8_t *>(weight);
+  a.M = m, a.N = n, a.K = k, a.err = sc->err;
+  a.n_dst = n_dst, a.y_ld = dst_ld, a.y_col0 = dst_col0;
+  for (int d = 1; d < n_dst; ++d) {
+    a.y_more[d - 1] = static_cast<float *>(dsts[d]);
+  }
+  if (gemm_tcgen05_launch(a, wt, ctx->sm_count, st) != cudaSuccess) {
+    cudaGetLastError();
+    return -2;
+  }
+  count_launch();
+  return 0;
+}
+
 int htp_b200_rms_norm_f32(float *dst, const float *src, int ne0, int ne1, void *stream) {
   // argument rules of the reference: src/dsp/ops/rms_norm.c:69-74
   if (!dst || !src || ne0 <= 0 || ne1 <= 0) {

@@ -88,6 +88,11 @@ struct GCfg {
 // One ring of kNAT K steps.  Slot i holds the activation tile (shared memory) and the dequantised
 // weight tile (tensor memory) of one K step; both are filled behind ONE barrier and released by
 // ONE tcgen05.commit, so the MMA issuer waits once and commits once per K step.
+// tensor maps of the output destinations (one per destination matrix, all of the same shape)
+struct GemmDstMaps {
+  CUtensorMap m[kGemmMaxDst];
+};
+
 struct GSmemBar {
   uint64_t full[kNAT], empty[kNAT];
   uint64_t acc_full, acc_empty;
@@ -225,11 +230,14 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[16]) {
                : "memory");
 }
 // 2-D tiled tensor store shared memory -> global through a tensor map (elements outside the
-// tensor are not written); completion is tracked by the issuing thread's bulk groups.
+// tensor are not written); completion is tracked by the issuing thread's bulk groups (bulk_commit).
 __device__ __forceinline__ void tma_store_2d(const void *tmap, int x, int y, uint32_t src_smem) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(x), "r"(y),
                "r"(src_smem)
                : "memory");
+}
+// closes the bulk group of the stores issued since the last commit
+__device__ __forceinline__ void bulk_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 // at most N of this thread's bulk groups still have to READ their shared-memory source
@@ -399,7 +407,7 @@ __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw, int q, u
 template <int WT, int BT, bool TWO>
 __global__ void __launch_bounds__(kThreads, 1)
   gemm_tcgen05_kernel(const GemmArgs p, const __grid_constant__ CUtensorMap xmap,
-                      const __grid_constant__ CUtensorMap ymap, const __grid_constant__ CUtensorMap pmap) {
+                      const __grid_constant__ GemmDstMaps ymaps, const __grid_constant__ CUtensorMap pmap) {
   using C = GCfg<WT, BT, TWO>;
   static_assert((!TWO && BT == 128) || (TWO && BT == 256), "token tile");
   constexpr int      NX        = C::NX;
@@ -594,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     unsigned  nbuf = 0;  // running count of staged chunks: buffer = nbuf & 1
     const uint32_t stage0 = smem_u32(sOut + q4 * (2 * kOutTok * 128));
     if (lane == 0) {
-      tma_prefetch_descriptor(&ymap);
+      tma_prefetch_descriptor(&ymaps.m[0]);
     }
 #ifdef HTP_GEMM_PROF
     long long prof[4] = {0, 0, 0, 0};
@@ -682,8 +690,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (is_tail) {
             tma_store_2d(&pmap, row_off + q4 * 32, worker * BT + c0, buf);
           } else if (col_ok) {
-            tma_store_2d(&ymap, col0, m0 + c0, buf);
+            // every destination gets the same box (the others are other GPUs' copies of the output)
+            for (int d = 0; d < p.n_dst; ++d) {
+              tma_store_2d(&ymaps.m[d], (int) p.y_col0 + col0, m0 + c0, buf);
+            }
           }
+          bulk_commit();
         }
       };
       auto release_acc = [&]() {
@@ -744,6 +756,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (lane == 0) {
       bulk_wait_all();  // the staging buffers stay valid until the copy engine is done with them
+      if (p.n_dst > 1) {
+        __threadfence_system();  // stores into other GPUs' memory are ordered before this kernel's end
+      }
     }
 #ifdef HTP_GEMM_PROF
     if (blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
@@ -922,7 +937,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   if (!enc) {
     return cudaErrorNotSupported;
   }
-  CUtensorMap xmap, ymap;
+  CUtensorMap xmap;
   {
     const cuuint64_t gdim[2] = { (cuuint64_t) a.K, (cuuint64_t) a.M };
     const cuuint64_t gstr[1] = { (cuuint64_t) a.K * 2 };
@@ -934,14 +949,32 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
       return cudaErrorInvalidValue;
     }
   }
-  {
-    // output y[M][N] fp32, stored in boxes of 32 weight rows (128 bytes) x 16 tokens
-    const cuuint64_t gdim[2] = { (cuuint64_t) a.N, (cuuint64_t) a.M };
-    const cuuint64_t gstr[1] = { (cuuint64_t) a.N * 4 };
+  GemmArgs args = a;
+  if (args.n_dst <= 0) {
+    args.n_dst = 1;
+  }
+  if (args.y_ld <= 0) {
+    args.y_ld = a.N, args.y_col0 = 0;
+  }
+  if (args.n_dst > kGemmMaxDst || args.y_col0 < 0 || args.y_col0 % 32 != 0 || args.y_col0 + a.N > args.y_ld ||
+      args.y_ld % 4 != 0) {
+    return cudaErrorInvalidValue;
+  }
+  GemmDstMaps ymaps;
+  for (int d = 0; d < kGemmMaxDst; ++d) {
+    if (d >= args.n_dst) {
+      ymaps.m[d] = ymaps.m[0];  // unused slots
+      continue;
+    }
+    // output [M][y_ld] fp32, stored in boxes of 32 weight rows (128 bytes) x 16 tokens
+    float *base = d == 0 ? a.y : a.y_more[d - 1];
+    const cuuint64_t gdim[2] = { (cuuint64_t) args.y_ld, (cuuint64_t) a.M };
+    const cuuint64_t gstr[1] = { (cuuint64_t) args.y_ld * 4 };
     const cuuint32_t box[2]  = { 32, kOutTok };
     const cuuint32_t es[2]   = { 1, 1 };
-    if (enc(&ymap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, a.y, gdim, gstr, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+    if (!base || enc(&ymaps.m[d], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, gdim, gstr, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
       return cudaErrorInvalidValue;
     }
   }
@@ -949,11 +982,10 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   const int tiles     = ((a.M + BT - 1) / BT) * ((a.N + rows_tile - 1) / rows_tile);
   const int max_w     = TWO ? sm_count / 2 : sm_count;
   const int workers   = tiles < max_w ? tiles : max_w;
-  GemmArgs  args      = a;
   // uneven tile counts: cut the work into equal ranges (needs the scratch)
   args.split = (a.part != nullptr && tiles > workers && tiles % workers != 0) ? 1 : 0;
   args.flags = a.part ? reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(a.part) + gemm_part_bytes(sm_count)) : nullptr;
-  CUtensorMap pmap = ymap;
+  CUtensorMap pmap = ymaps.m[0];
   if (args.split) {
     // partial tiles: [worker][token][weight row of the tile] fp32, stored in the same boxes as y
     const cuuint64_t gdim[2] = { (cuuint64_t) rows_tile, (cuuint64_t) BT * workers };
@@ -983,7 +1015,7 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs                = attr;
   cfg.numAttrs             = TWO ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kern, args, xmap, ymap, pmap);
+  return cudaLaunchKernelEx(&cfg, kern, args, xmap, ymaps, pmap);
 }
 
 }  // namespace

@@ -12,8 +12,10 @@ constexpr int kGemmErrEpilogue = 203;
 constexpr int kGemmErrDequant  = 204;
 constexpr int kGemmErrFixup    = 205;  // the other contributor of a split tile never raised its flag
 
+constexpr int kGemmMaxDst = 8;
+
 struct GemmArgs {
-  float         *y;  // [M][N] fp32
+  float         *y;  // [M][N] fp32 (destination 0)
   const void    *x;  // [M][K] fp16
   const uint8_t *w;  // N rows of K/32 blocks
   int            M, N, K;  // K a multiple of 256, N a multiple of 32
@@ -24,6 +26,13 @@ struct GemmArgs {
   float         *part;
   int           *flags;  // set by the launcher
   int            split;  // set by the launcher
+  // Output placement.  The result is stored into n_dst destination matrices (destination 0 = y,
+  // the others = y_more[0 .. n_dst - 2]; 0 means 1), each row-major with y_ld elements per token
+  // (0 means N), at column y_col0: this is how a rank of a row-sharded matmul writes its column
+  // band straight into every rank's full output (peer pointers), instead of a gather afterwards.
+  int            n_dst;
+  float         *y_more[kGemmMaxDst - 1];
+  long long      y_ld, y_col0;
 #ifdef HTP_GEMM_PROF
   int            dbg;      // instrumented builds only: bit mask of waits to skip (timing experiments)
 #endif

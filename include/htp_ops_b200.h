@@ -82,6 +82,18 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
  * src/dsp/op_executor.cc:124-126) evaluated in 64 bits.  0 for an unknown type or k % 32 != 0. */
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
 
+/* Prefill matmul (fp16 activations, m >= 64, k % 256 == 0: the tensor-core kernel) whose result
+ * y[m][n] is stored as the column band [dst_col0, dst_col0 + n) of n_dst (1..8) destination matrices
+ * of dst_ld floats per token: the fused form of "matmul on my row shard, then all-gather".  A rank of
+ * a row-sharded lm_head passes every rank's full logits buffer (its own and the peers' mapped
+ * pointers, e.g. from CUDA IPC or symmetric memory) with dst_col0 = its first row: the epilogue's
+ * tiled stores go to all of them while the next tile is being computed, and no gather kernel or copy
+ * follows - only a cross-rank barrier before the logits are read.  No counterpart in the reference
+ * (single DSP).  -1 for arguments outside this range; dst_ld, dst_col0 multiples of 32; every
+ * destination 128-byte aligned. */
+int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                               const void *weight, int m, int k, int n, int weight_type, int act_type, void *stream);
+
 /* RMSNorm over ne1 rows of ne0 floats: y = x / sqrt(mean(x^2) + 1e-5) (eps fixed as in the reference).
  * Replaces hvx_rms_norm_f32 (reference include/dsp/ops.h:15, src/dsp/ops/rms_norm.c:68-84): same argument
  * rules (non-null, non-zero sizes, 128-byte aligned pointers -> else -1), device pointers + stream. */

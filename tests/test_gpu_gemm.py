@@ -80,3 +80,36 @@ def test_gemm_matches_decode_kernel(dev, wl):
     finally:
         lib.htp_b200_set_option(b"gemm_min_m", 64)
     assert np.abs(y_gemm - y_gemv).max() <= 1e-3 * np.abs(y_gemv).max()
+
+
+@pytest.mark.parametrize("wtype", [2, 8])
+def test_gemm_multi_destination_band(dev, oracle, wl, wtype):
+    """The fused form of "matmul on a row shard, then all-gather": the result goes into the column band
+    [col0, col0 + n) of several destination matrices of ld floats per token.  Here both destinations
+    are buffers of this GPU (on a multi-GPU box they are the ranks' logits buffers): each band must
+    equal the plain result bit for bit and nothing outside the band may be touched."""
+    import ctypes
+
+    import torch
+    m, k, n, ld, col0 = 200, 1024, 736, 2048, 512
+    wq, x = wl.random_case(950, wtype, True, m, k, n)
+    plain = dev.matmul(x, wq, n, wtype)
+    tw, tx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    dsts = [torch.full((m, ld), -7.0, dtype=torch.float32, device="cuda") for _ in range(3)]
+    ptrs = (ctypes.c_void_p * 3)(*[d.data_ptr() for d in dsts])
+    st = torch.cuda.current_stream().cuda_stream
+    lib = dev.lib
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == 0
+    torch.cuda.synchronize()
+    assert lib.htp_b200_stream_status(st) == 0
+    for d in dsts:
+        h = d.cpu().numpy()
+        assert (h[:, col0:col0 + n] == plain).all()
+        assert (h[:, :col0] == -7.0).all() and (h[:, col0 + n:] == -7.0).all()
+    # outside the kernel's range: rejected, nothing launched
+    before = lib.htp_b200_launch_count()
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0 + 16, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, ld - 32, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 9, ld, col0, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), 8, k, n, wtype, 1, st) == -1
+    assert lib.htp_b200_launch_count() == before
