@@ -394,7 +394,7 @@ def run_ours(args):
                                   op.wtype, pkg.ACT_F16, sp)
         assert rc == 0
 
-    def step(i):
+    def step_gather(i):
         kernel(i)
         if world > 1:
             sharding.all_gather_logits(dist, logits, y_loc, m, op.n, world)
@@ -403,6 +403,39 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # Fused exchange (N > 1): the kernel's tile completion stores each rank's slice of the logits
+    # straight into EVERY rank's logits vector (peer pointers from torch's symmetric memory); a
+    # cross-rank barrier replaces the all-gather.  Used for the timed step when it is available and
+    # reproduces the gathered result bit for bit on every rank; otherwise the NCCL all-gather is.
+    step, exchange = step_gather, ("none" if world == 1 else "NCCL all-gather of fp32 logits")
+    if world > 1 and not args.no_fused:
+        try:
+            import ctypes
+
+            import torch.distributed._symmetric_memory as symm
+            ranges = [sharding.row_range(op.n, r, world) for r in range(world)]
+            if all(b - a == n_loc for a, b in ranges):
+                sym = symm.empty((m, op.n), dtype=torch.float32, device=dev)
+                hdl = symm.rendezvous(sym, dist.group.WORLD)
+                order = [rank] + [r for r in range(world) if r != rank]  # own copy first
+                arr = (ctypes.c_void_p * world)(*[int(hdl.buffer_ptrs[r]) for r in order])
+
+                def step_fused(i):
+                    assert lib.htp_b200_mul_mat_multi_dst(arr, world, op.n, r0, x.data_ptr(), ws[i % copies].data_ptr(),
+                                                          m, op.k, n_loc, op.wtype, pkg.ACT_F16, sp) == 0
+                    hdl.barrier()
+                sym.zero_()
+                hdl.barrier()
+                step_gather(0)
+                step_fused(0)
+                torch.cuda.synchronize()
+                same = torch.tensor([1 if bool((sym == logits).all().item()) else 0], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                if int(same[0]) == 1:
+                    step, exchange = step_fused, "fused: tile completion stores into every rank's logits (peer memory) + barrier"
+        except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing
+            sys.stderr.write(f"fused exchange unavailable: {type(e).__name__}: {e}\n")
 
     for i in range(warm):
         step(i)
@@ -433,6 +466,14 @@ def run_ours(args):
     ms_step_long = float(t[1]) / steps
     total_bytes = wl.algorithmic_bytes(op, m)
     value = total_bytes / (ms_step * 1e-3) / 1e9
+
+    # the NCCL all-gather path beside the fused one, for comparison
+    gather_ms = None
+    if world > 1 and step is not step_gather:
+        barrier()
+        t = torch.tensor([time_region(torch, step_gather, steps, stream) / steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather_ms = float(t[0])
 
     # kernel alone (no gather) for the roofline of the dominant kernel
     barrier()
@@ -495,11 +536,12 @@ def run_ours(args):
             "warmup": warm, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 x int8 -> f32", "data": "synthetic",
             "config": {"workload": "cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1, rows sharded over "
-                                   f"{world} GPU(s)" + (" + NCCL all-gather of fp32 logits" if world > 1 else ""),
+                                   f"{world} GPU(s)", "exchange": exchange,
                        "l2": f"rotating {copies} distinct weight copies per rank "
                              f"({slab * copies / 1e6:.0f} MB > 126 MB L2): every pass reads HBM",
                        "algorithmic_bytes_per_step": total_bytes,
-                       "ms_per_step_over_long_run": round(ms_step_long, 5)},
+                       "ms_per_step_over_long_run": round(ms_step_long, 5),
+                       **({"ms_per_step_with_nccl_all_gather": round(gather_ms, 5)} if gather_ms else {})},
             "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q8_0,f16,M=1>", "achieved": round(achieved, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
                          "peak_source": f"{peaks['source']} (copy bandwidth)", "ms_per_launch": round(k_ms, 5),
@@ -663,6 +705,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the brief single-GPU runs of the other configs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--quick", action="store_true", help="fewer repeats in the extra runs")
+    ap.add_argument("--no-fused", action="store_true",
+                    help="N > 1: assemble the logits with an NCCL all-gather instead of the kernel's own peer stores")
     ap.add_argument("--case", default=None, help="wtype,act,m,k,n: time one shape only (profiling aid)")
     args = ap.parse_args()
     if args.case:

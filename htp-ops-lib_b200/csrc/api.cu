@@ -135,8 +135,15 @@ inline int wt_index(int weight_type) {
 
 // Decode path: M <= 8 rows of activations per launch, K split into launches whose activation
 // fragments fit in shared memory next to at least three pipeline stages.
+// Placement of the output as a column band of several matrices (see GemvArgs); nullptr = plain.
+struct OutBand {
+  int          n_dst;
+  long long    ld, col0;
+  float *const *more;  // n_dst - 1 further destinations
+};
+
 int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int m, int k, int n, int wt, bool a16,
-             cudaStream_t stream, bool pdl) {
+             cudaStream_t stream, bool pdl, const OutBand *band = nullptr) {
   StreamScratch *sc = stream_scratch(ctx, stream);
   if (!sc) {
     return -2;
@@ -172,11 +179,20 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
         return -2;  // cannot happen on a device with >= 96 KiB of shared memory
       }
     }
+    if (band && nchunks > 1) {
+      return -1;  // K split over accumulating launches: not offered with several destinations
+    }
     for (int c = 0; c * chunk_periods < periods; ++c) {
       const int p0  = c * chunk_periods;
       const int pn  = (periods - p0) < chunk_periods ? (periods - p0) : chunk_periods;
       GemvArgs  a   = {};
-      a.y           = dst + (size_t) m0 * n;
+      a.y           = dst + (size_t) m0 * (band ? band->ld : n);
+      if (band) {
+        a.n_dst = band->n_dst, a.y_ld = band->ld, a.y_col0 = band->col0;
+        for (int d = 1; d < band->n_dst; ++d) {
+          a.y_more[d - 1] = band->more[d - 1] + (size_t) m0 * band->ld;
+        }
+      }
       a.x           = static_cast<const uint8_t *>(act) + (size_t) m0 * k * asz;
       a.w           = w;
       a.w_row_bytes = (long long) kb_all * bb;
@@ -418,9 +434,13 @@ int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int
   if (!dsts || n_dst < 1 || n_dst > kGemmMaxDst || !activation || !weight || m <= 0 || n <= 0 || k <= 0) {
     return -1;
   }
-  const int wt = wt_index(weight_type);
-  // the tensor-core GEMM only: fp16 activations, enough tokens, 16-byte aligned weight rows
-  if (wt < 0 || act_type != HTP_B200_ACT_F16 || m < g_opt_gemm_min_m || k % 256 != 0 || n % 32 != 0) {
+  const int  wt     = wt_index(weight_type);
+  const bool a16    = act_type == HTP_B200_ACT_F16;
+  const bool decode = m <= 8;
+  // the decode kernel (m <= 8) or the tensor-core GEMM (fp16 activations, m >= gemm_min_m); both want
+  // 16-byte aligned weight rows
+  if (wt < 0 || (act_type != HTP_B200_ACT_F32 && !a16) || k % 256 != 0 || n % 32 != 0 ||
+      (!decode && (!a16 || m < g_opt_gemm_min_m))) {
     return -1;
   }
   if (dst_ld < n || dst_ld % 32 != 0 || dst_col0 < 0 || dst_col0 % 32 != 0 || dst_col0 + n > dst_ld) {
@@ -442,6 +462,15 @@ int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int
   StreamScratch *sc = stream_scratch(ctx, st);
   if (!sc) {
     return -2;
+  }
+  if (decode) {
+    float *more[kGemmMaxDst - 1] = {};
+    for (int d = 1; d < n_dst; ++d) {
+      more[d - 1] = static_cast<float *>(dsts[d]);
+    }
+    const OutBand band = { n_dst, dst_ld, dst_col0, more };
+    return run_gemv(ctx, static_cast<float *>(dsts[0]), activation, static_cast<const uint8_t *>(weight), m, k, n, wt,
+                    a16, st, g_opt_pdl != 0, &band);
   }
   GemmArgs a = {};
   a.y = static_cast<float *>(dsts[0]), a.x = activation, a.w = static_cast<const uint8_t *>(weight);

@@ -588,11 +588,15 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
     return true;
   }
   const long long row = tile * kGemvTileRows + rg * 16 + g;
+  const long long ld  = p.y_ld > 0 ? p.y_ld : p.N;
   auto            put = [&](int m, long long r, float val, float inv) {
     if (m < p.M) {
-      float *dst = p.y + (long long) m * p.N + r;
+      const long long at = (long long) m * ld + p.y_col0 + r;
       val *= inv;
-      *dst = p.accumulate ? (*dst + val) : val;
+      p.y[at] = p.accumulate ? (p.y[at] + val) : val;
+      for (int d = 1; d < p.n_dst; ++d) {  // the other copies of the output (other GPUs' memory)
+        p.y_more[d - 1][at] = val;
+      }
     }
   };
   put(m0, row, lo0, inv0);
@@ -674,6 +678,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (!complete_tile<WT, A16, MPAD>(p, sm, tile, it0, it1, S, warp - kReduceWarp0, lane, n)) {
           break;
         }
+      }
+      if (p.n_dst > 1) {
+        __threadfence_system();  // stores into other GPUs' memory are ordered before this kernel's end
       }
     }
   } else {

@@ -46,6 +46,12 @@ struct GemvArgs {
   float         *partials;     // [grid][2][256] scratch for tiles cut by a CTA range boundary
   unsigned      *counters;     // [grid] arrival counters, zero between launches
   int           *err;          // first error code, 0 when none
+  // Output placement (single-operator launches): the result is stored as the column band
+  // [y_col0, y_col0 + N) of n_dst matrices of y_ld floats per token - y and y_more[0 .. n_dst - 2],
+  // e.g. every rank's copy of a row-sharded output.  n_dst = 0 / y_ld = 0: plain y[M][N].
+  int            n_dst;
+  long long      y_ld, y_col0;
+  float         *y_more[7];
 };
 
 // One operator of a batched launch: several independent mat-vecs of the same kind (weight format,

@@ -82,8 +82,8 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
  * src/dsp/op_executor.cc:124-126) evaluated in 64 bits.  0 for an unknown type or k % 32 != 0. */
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
 
-/* Prefill matmul (fp16 activations, m >= 64, k % 256 == 0: the tensor-core kernel) whose result
- * y[m][n] is stored as the column band [dst_col0, dst_col0 + n) of n_dst (1..8) destination matrices
+/* Matmul for m <= 8 (decode kernel, either activation type) or for fp16 activations with m >= 64
+ * (tensor-core kernel), k % 256 == 0, whose result y[m][n] is stored as the column band [dst_col0, dst_col0 + n) of n_dst (1..8) destination matrices
  * of dst_ld floats per token: the fused form of "matmul on my row shard, then all-gather".  A rank of
  * a row-sharded lm_head passes every rank's full logits buffer (its own and the peers' mapped
  * pointers, e.g. from CUDA IPC or symmetric memory) with dst_col0 = its first row: the epilogue's

@@ -311,3 +311,28 @@ def test_channel_batches_independent_requests(dev, oracle, wl):
     h = dev.get(fy[0], (1, 512))
     check(oracle, dev.get(fyd, (1, 128)), h, wdep, 128, 2)
     dev.free(*fw, *fx, *fy, fwd, fyd)
+
+
+@pytest.mark.parametrize("wtype,act_f16,m", [(2, False, 1), (2, True, 2), (8, True, 1), (8, False, 3), (2, False, 8)])
+def test_decode_multi_destination_band(dev, oracle, wl, wtype, act_f16, m):
+    """Decode output as the column band [col0, col0 + n) of several destination matrices (on a
+    multi-GPU box: every rank's copy of a row-sharded output): each band equals the plain result bit
+    for bit, nothing else is touched."""
+    import ctypes
+
+    import torch
+    k, n, ld, col0 = 1024, 608, 1536, 352
+    wq, x = wl.random_case(960 + m, wtype, act_f16, m, k, n)
+    plain = dev.matmul(x, wq, n, wtype)
+    tw, tx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    dsts = [torch.full((m, ld), -7.0, dtype=torch.float32, device="cuda") for _ in range(3)]
+    ptrs = (ctypes.c_void_p * 3)(*[d.data_ptr() for d in dsts])
+    st = torch.cuda.current_stream().cuda_stream
+    assert dev.lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype,
+                                              1 if act_f16 else 0, st) == 0
+    torch.cuda.synchronize()
+    assert dev.lib.htp_b200_stream_status(st) == 0
+    for d in dsts:
+        h = d.cpu().numpy()
+        assert (h[:, col0:col0 + n] == plain).all()
+        assert (h[:, :col0] == -7.0).all() and (h[:, col0 + n:] == -7.0).all()
