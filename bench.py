@@ -418,14 +418,26 @@ def run_ours(args):
             if all(b - a == n_loc for a, b in ranges):
                 sym = symm.empty((m, op.n), dtype=torch.float32, device=dev)
                 hdl = symm.rendezvous(sym, dist.group.WORLD)
+                symf = symm.empty((32,), dtype=torch.int32, device=dev)  # completion flags, one word per rank
+                hdlf = symm.rendezvous(symf, dist.group.WORLD)
                 order = [rank] + [r for r in range(world) if r != rank]  # own copy first
                 arr = (ctypes.c_void_p * world)(*[int(hdl.buffer_ptrs[r]) for r in order])
+                # this rank's flag word in every destination GPU's flag array
+                farr = (ctypes.c_void_p * world)(*[int(hdlf.buffer_ptrs[r]) + 4 * rank for r in order])
+                epoch = [0]
 
                 def step_fused(i):
-                    assert lib.htp_b200_mul_mat_multi_dst(arr, world, op.n, r0, x.data_ptr(), ws[i % copies].data_ptr(),
-                                                          m, op.k, n_loc, op.wtype, pkg.ACT_F16, sp) == 0
-                    hdl.barrier()
+                    # the kernel stores this rank's slice into every rank's logits and then raises its flag
+                    # on every GPU; the wait (a tiny kernel on this stream) returns when all ranks' flags of
+                    # this step are here - no all-gather, no separate barrier
+                    epoch[0] += 1
+                    assert lib.htp_b200_mul_mat_multi_dst_signal(arr, world, op.n, r0, x.data_ptr(),
+                                                                 ws[i % copies].data_ptr(), m, op.k, n_loc, op.wtype,
+                                                                 pkg.ACT_F16, farr, epoch[0], sp) == 0
+                    assert lib.htp_b200_wait_flags(symf.data_ptr(), world, epoch[0], sp) == 0
                 sym.zero_()
+                symf.zero_()
+                torch.cuda.synchronize()
                 hdl.barrier()
                 step_gather(0)
                 step_fused(0)
@@ -433,7 +445,8 @@ def run_ours(args):
                 same = torch.tensor([1 if bool((sym == logits).all().item()) else 0], device=dev)
                 dist.all_reduce(same, op=dist.ReduceOp.MIN)
                 if int(same[0]) == 1:
-                    step, exchange = step_fused, "fused: tile completion stores into every rank's logits (peer memory) + barrier"
+                    step, exchange = step_fused, ("fused: tile completion stores into every rank's logits (peer memory), completion flags "
+                                      "raised by the last CTA, bounded flag wait on every rank")
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing
             sys.stderr.write(f"fused exchange unavailable: {type(e).__name__}: {e}\n")
 

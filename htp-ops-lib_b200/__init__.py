@@ -51,6 +51,9 @@ EXPORTS = {
     "htp_b200_block_sums": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
     "htp_b200_rms_norm_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     "htp_b200_mul_mat_multi_dst": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "htp_b200_mul_mat_multi_dst_signal": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, ctypes.c_uint32,
+                                               _vp]),
+    "htp_b200_wait_flags": (_i, [_vp, _i, ctypes.c_uint32, _vp]),
     "htp_b200_weight_bytes": (_sz, [_i, _i64, _i64]),
     "htp_b200_stream_status": (_i, [_vp]),
     "htp_b200_set_option": (_i, [ctypes.c_char_p, _i]),

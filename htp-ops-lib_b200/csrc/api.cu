@@ -140,6 +140,8 @@ struct OutBand {
   int          n_dst;
   long long    ld, col0;
   float *const *more;  // n_dst - 1 further destinations
+  unsigned *const *flags = nullptr;  // optional completion flags, one per destination
+  unsigned     epoch     = 0;
 };
 
 int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int m, int k, int n, int wt, bool a16,
@@ -182,6 +184,9 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
     if (band && nchunks > 1) {
       return -1;  // K split over accumulating launches: not offered with several destinations
     }
+    if (band && band->flags && m > slice) {
+      return -1;  // the completion signal belongs to ONE launch
+    }
     for (int c = 0; c * chunk_periods < periods; ++c) {
       const int p0  = c * chunk_periods;
       const int pn  = (periods - p0) < chunk_periods ? (periods - p0) : chunk_periods;
@@ -191,6 +196,13 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
         a.n_dst = band->n_dst, a.y_ld = band->ld, a.y_col0 = band->col0;
         for (int d = 1; d < band->n_dst; ++d) {
           a.y_more[d - 1] = band->more[d - 1] + (size_t) m0 * band->ld;
+        }
+        if (band->flags) {
+          a.done_counter = reinterpret_cast<unsigned *>(sc->err) + 4;  // spare zeroed word of the scratch
+          a.epoch        = band->epoch;
+          for (int d = 0; d < band->n_dst; ++d) {
+            a.sig_flags[d] = band->flags[d];
+          }
         }
       }
       a.x           = static_cast<const uint8_t *>(act) + (size_t) m0 * k * asz;
@@ -429,8 +441,52 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
   return 0;
 }
 
+static int mul_mat_multi_dst_impl(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                                  const void *weight, int m, int k, int n, int weight_type, int act_type,
+                                  unsigned *const *flags, unsigned epoch, void *stream);
+
 int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                const void *weight, int m, int k, int n, int weight_type, int act_type, void *stream) {
+  return mul_mat_multi_dst_impl(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n, weight_type, act_type, nullptr,
+                                0, stream);
+}
+
+int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0,
+                                      const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                                      int act_type, uint32_t *const *flags, uint32_t epoch, void *stream) {
+  if (!flags || m > 8) {
+    return -1;
+  }
+  for (int d = 0; d < n_dst && d < kGemmMaxDst; ++d) {
+    if (!flags[d] || (reinterpret_cast<uintptr_t>(flags[d]) & 3u)) {
+      return -1;
+    }
+  }
+  return mul_mat_multi_dst_impl(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n, weight_type, act_type, flags,
+                                epoch, stream);
+}
+
+int htp_b200_wait_flags(const uint32_t *flags, int n, uint32_t epoch, void *stream) {
+  if (!flags || n < 1 || n > 32 || (reinterpret_cast<uintptr_t>(flags) & 3u)) {
+    return -1;
+  }
+  DeviceCtx *ctx = current_device_ctx();
+  if (!ctx) {
+    return -2;
+  }
+  cudaStream_t   st = static_cast<cudaStream_t>(stream);
+  StreamScratch *sc = stream_scratch(ctx, st);
+  if (!sc || flags_wait_launch(flags, n, epoch, sc->err, st) != cudaSuccess) {
+    cudaGetLastError();
+    return -2;
+  }
+  count_launch();
+  return 0;
+}
+
+static int mul_mat_multi_dst_impl(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                                  const void *weight, int m, int k, int n, int weight_type, int act_type,
+                                  unsigned *const *flags, unsigned epoch, void *stream) {
   if (!dsts || n_dst < 1 || n_dst > kGemmMaxDst || !activation || !weight || m <= 0 || n <= 0 || k <= 0) {
     return -1;
   }
@@ -468,7 +524,9 @@ int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int
     for (int d = 1; d < n_dst; ++d) {
       more[d - 1] = static_cast<float *>(dsts[d]);
     }
-    const OutBand band = { n_dst, dst_ld, dst_col0, more };
+    OutBand band = { n_dst, dst_ld, dst_col0, more };
+    band.flags   = flags;
+    band.epoch   = epoch;
     return run_gemv(ctx, static_cast<float *>(dsts[0]), activation, static_cast<const uint8_t *>(weight), m, k, n, wt,
                     a16, st, g_opt_pdl != 0, &band);
   }
@@ -531,7 +589,7 @@ int htp_b200_stream_status(void *stream) {
     return -2;
   }
   if (code != 0) {
-    cudaMemsetAsync(sc->err, 0, sizeof(int), st);
+    cudaMemsetAsync(sc->err, 0, 32, st);  // the error word and the launch-completion counter behind it
     // a kernel that gave up may have left arrival counters behind
     cudaMemsetAsync(sc->counters, 0, (size_t) kGemvMaxGrid * sizeof(unsigned), st);
     cudaStreamSynchronize(st);

@@ -683,6 +683,22 @@ __global__ void __launch_bounds__(kThreads, 1)
         __threadfence_system();  // stores into other GPUs' memory are ordered before this kernel's end
       }
     }
+    if (p.done_counter) {
+      // this CTA's bands are out (both completion warps, fenced above): count it; the last CTA of the
+      // launch tells every destination that this rank is done
+      named_bar_sync(2, kReduceThreads);
+      if (warp == kReduceWarp0 && lane == 0) {
+        __threadfence_system();
+        const unsigned old = atomicAdd(p.done_counter, 1u);
+        if (old == gridDim.x - 1) {
+          *p.done_counter = 0;  // ready for the next launch
+          __threadfence_system();
+          for (int d = 0; d < p.n_dst; ++d) {
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[d]), "r"(p.epoch) : "memory");
+          }
+        }
+      }
+    }
   } else {
     // ---------------- consumers
     const int tid = threadIdx.x;
@@ -803,6 +819,24 @@ cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int 
     case 4: return launch_one<WT, A16, 4>(a, wm, grid, smem, s, pdl);
     default: return launch_one<WT, A16, 8>(a, wm, grid, smem, s, pdl);
   }
+}
+
+// ------------------------------------------------------------------ completion flags
+
+__global__ void flags_wait_kernel(const unsigned *flags, int n, unsigned epoch, int *err) {
+  const int r = threadIdx.x;
+  if (r >= n) {
+    return;
+  }
+  for (uint32_t i = 0; i < (1u << 22); ++i) {  // about a second
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+    if ((int) (v - epoch) >= 0) {
+      return;
+    }
+    __nanosleep(200);
+  }
+  atomicCAS(err, 0, kGemvErrFlagWait);
 }
 
 // ------------------------------------------------------------------ the batched kernel
@@ -1093,6 +1127,11 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 }  // namespace
+
+cudaError_t flags_wait_launch(const unsigned *flags, int n, unsigned epoch, int *err, cudaStream_t stream) {
+  flags_wait_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, err);
+  return cudaGetLastError();
+}
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
   size_t b;

@@ -52,7 +52,20 @@ struct GemvArgs {
   int            n_dst;
   long long      y_ld, y_col0;
   float         *y_more[7];
+  // Completion signal (optional, with several destinations): when the LAST CTA of the launch has
+  // finished - every CTA's stores fenced at system scope - it writes `epoch` to sig_flags[d] for
+  // every destination d (a word in that destination GPU's memory), so that a waiter there knows this
+  // rank's band has landed.  done_counter: a zeroed word of this GPU, zero again afterwards.
+  unsigned      *done_counter;
+  unsigned      *sig_flags[8];
+  unsigned       epoch;
 };
+
+constexpr int kGemvErrFlagWait = 103;  // htp_b200_wait_flags: a peer's completion flag never arrived
+
+// Waits (bounded) on `stream` until flags[r] has reached `epoch` for r = 0 .. n - 1; records
+// kGemvErrFlagWait in *err when that does not happen.
+cudaError_t flags_wait_launch(const unsigned *flags, int n, unsigned epoch, int *err, cudaStream_t stream);
 
 // One operator of a batched launch: several independent mat-vecs of the same kind (weight format,
 // activation type, token count) streamed by ONE persistent kernel as a single item list, so that

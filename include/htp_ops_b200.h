@@ -94,6 +94,21 @@ size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
 int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                const void *weight, int m, int k, int n, int weight_type, int act_type, void *stream);
 
+/* Decode form (m <= 8, one launch) of the call above that also SIGNALS: when the whole launch has
+ * finished and its stores are visible system-wide, the kernel writes `epoch` to flags[d] for every
+ * destination d - a 4-byte word in that destination GPU's memory reserved for THIS rank.  Together
+ * with htp_b200_wait_flags on each GPU this replaces the all-gather AND the barrier of a row-sharded
+ * decode step: rank r passes flags[d] = &(flag array of the GPU that owns dsts[d])[r].  Epochs must
+ * increase from call to call (wrap-around safe).  No counterpart in the reference. */
+int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0,
+                                      const void *activation, const void *weight, int m, int k, int n, int weight_type,
+                                      int act_type, uint32_t *const *flags, uint32_t epoch, void *stream);
+
+/* Enqueues on `stream` a bounded wait until flags[r] has reached `epoch` for r = 0 .. n-1 (n <= 32):
+ * every rank's band of this step has landed in this GPU's copy.  If a flag does not arrive within
+ * about a second the stream's error word gets 103 (see htp_b200_stream_status); nothing hangs. */
+int htp_b200_wait_flags(const uint32_t *flags, int n, uint32_t epoch, void *stream);
+
 /* RMSNorm over ne1 rows of ne0 floats: y = x / sqrt(mean(x^2) + 1e-5) (eps fixed as in the reference).
  * Replaces hvx_rms_norm_f32 (reference include/dsp/ops.h:15, src/dsp/ops/rms_norm.c:68-84): same argument
  * rules (non-null, non-zero sizes, 128-byte aligned pointers -> else -1), device pointers + stream. */

@@ -336,3 +336,34 @@ def test_decode_multi_destination_band(dev, oracle, wl, wtype, act_f16, m):
         h = d.cpu().numpy()
         assert (h[:, col0:col0 + n] == plain).all()
         assert (h[:, :col0] == -7.0).all() and (h[:, col0 + n:] == -7.0).all()
+
+
+def test_decode_completion_flags(dev, wl):
+    """The signalling form: after the launch every destination's flag word holds the epoch; the wait
+    kernel passes for an epoch that has been reached and, for one that nothing raises, gives up
+    after its bounded wait with error 103 in the stream's error word (no hang, context intact)."""
+    import ctypes
+
+    import torch
+    m, k, n, ld = 1, 1024, 608, 1536
+    wq, x = wl.random_case(970, 8, True, m, k, n)
+    plain = dev.matmul(x, wq, n, 8)
+    tw, tx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    dsts = [torch.zeros((m, ld), dtype=torch.float32, device="cuda") for _ in range(2)]
+    flags = torch.zeros(32, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(*[d.data_ptr() for d in dsts])
+    fptrs = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr() + 4)
+    st = torch.cuda.current_stream().cuda_stream
+    lib = dev.lib
+    for epoch in (1, 2, 3):
+        assert lib.htp_b200_mul_mat_multi_dst_signal(ptrs, 2, ld, 0, tx.data_ptr(), tw.data_ptr(), m, k, n, 8, 1, fptrs,
+                                                     epoch, st) == 0
+        assert lib.htp_b200_wait_flags(flags.data_ptr(), 2, epoch, st) == 0
+        torch.cuda.synchronize()
+        assert flags[:2].tolist() == [epoch, epoch]
+    assert lib.htp_b200_stream_status(st) == 0
+    assert all((d.cpu().numpy()[:, :n] == plain).all() for d in dsts)
+    assert lib.htp_b200_wait_flags(flags.data_ptr(), 2, 4, st) == 0  # nobody raises epoch 4
+    assert lib.htp_b200_stream_status(st) == 103
+    assert lib.htp_b200_stream_status(st) == 0  # cleared; the stream still works
+    assert lib.htp_b200_wait_flags(flags.data_ptr(), 2, 3, st) == 0 and lib.htp_b200_stream_status(st) == 0
