@@ -444,7 +444,18 @@ def run_ours(args):
                 torch.cuda.synchronize()
                 same = torch.tensor([1 if bool((sym == logits).all().item()) else 0], device=dev)
                 dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                faster = False
                 if int(same[0]) == 1:
+                    # both paths give the same logits: take the faster one (agreed between the ranks)
+                    for f in (step_fused, step_gather):
+                        for i in range(3):
+                            f(i)
+                    barrier()
+                    tt = torch.tensor([time_region(torch, step_fused, 20, stream),
+                                       time_region(torch, step_gather, 20, stream)], device=dev, dtype=torch.float64)
+                    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                    faster = float(tt[0]) < float(tt[1])
+                if faster:
                     step, exchange = step_fused, ("fused: tile completion stores into every rank's logits (peer memory), completion flags "
                                       "raised by the last CTA, bounded flag wait on every rank")
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing

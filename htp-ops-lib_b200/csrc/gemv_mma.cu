@@ -823,18 +823,21 @@ cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int 
 
 // ------------------------------------------------------------------ completion flags
 
+// One warp; lane r watches flag r.  Launched with programmatic stream serialisation so that it is
+// already resident and polling while the mat-vec before it in the stream is still running (it depends
+// on that kernel only through the flags, this GPU's own included): no launch gap after the mat-vec.
 __global__ void flags_wait_kernel(const unsigned *flags, int n, unsigned epoch, int *err) {
   const int r = threadIdx.x;
   if (r >= n) {
     return;
   }
-  for (uint32_t i = 0; i < (1u << 22); ++i) {  // about a second
+  for (uint32_t i = 0; i < (1u << 23); ++i) {  // about a second
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
     if ((int) (v - epoch) >= 0) {
       return;
     }
-    __nanosleep(200);
+    __nanosleep(100);
   }
   atomicCAS(err, 0, kGemvErrFlagWait);
 }
@@ -1129,8 +1132,16 @@ EncodeTiledFn encode_tiled_fn() {
 }  // namespace
 
 cudaError_t flags_wait_launch(const unsigned *flags, int n, unsigned epoch, int *err, cudaStream_t stream) {
-  flags_wait_kernel<<<1, 32, 0, stream>>>(flags, n, epoch, err);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim            = dim3(1);
+  cfg.blockDim           = dim3(32);
+  cfg.stream             = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs                                          = attr;
+  cfg.numAttrs                                       = 1;
+  return cudaLaunchKernelEx(&cfg, flags_wait_kernel, flags, n, epoch, err);
 }
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
