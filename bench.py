@@ -455,6 +455,9 @@ def run_ours(args):
                                        time_region(torch, step_gather, 20, stream)], device=dev, dtype=torch.float64)
                     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                     faster = float(tt[0]) < float(tt[1])
+                    if rank == 0:
+                        sys.stderr.write(f"exchange: fused {float(tt[0]) / 20 * 1e3:.1f} us per step, NCCL all-gather "
+                                         f"{float(tt[1]) / 20 * 1e3:.1f} us per step\n")
                 if faster:
                     step, exchange = step_fused, ("fused: tile completion stores into every rank's logits (peer memory), completion flags "
                                       "raised by the last CTA, bounded flag wait on every rank")

@@ -827,6 +827,9 @@ cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int 
 // already resident and polling while the mat-vec before it in the stream is still running (it depends
 // on that kernel only through the flags, this GPU's own included): no launch gap after the mat-vec.
 __global__ void flags_wait_kernel(const unsigned *flags, int n, unsigned epoch, int *err) {
+  // the next kernel in the stream may start its own prologue (a mat-vec prefetches weights) while this
+  // one waits; whatever it does behind its own griddepcontrol.wait still comes after this kernel
+  pdl_launch_dependents();
   const int r = threadIdx.x;
   if (r >= n) {
     return;
