@@ -111,5 +111,6 @@ def test_gemm_multi_destination_band(dev, oracle, wl, wtype):
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0 + 16, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, ld - 32, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 9, ld, col0, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
-    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), 8, k, n, wtype, 1, st) == -1
+    # between the decode kernel's range (m <= 8) and the tensor-core kernel's (m >= 64)
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), 32, k, n, wtype, 1, st) == -1
     assert lib.htp_b200_launch_count() == before
