@@ -19,6 +19,7 @@ namespace htp {
 int g_opt_pdl           = getenv("HTP_OPS_NO_PDL") ? 0 : 1;  // programmatic dependent launch
 int g_opt_force_generic = 0;
 int g_opt_gemm_min_m     = 64;
+int g_opt_gemv_whole_tiles = getenv("HTP_OPS_NO_WHOLE_TILES") ? 0 : 1;  // small mat-vecs: one whole tile per CTA
 // Cut the GEMM's work into equal K ranges when the tile count is uneven.  Off by default: on the
 // shapes measured (112 to 4008 tiles on 74 CTA pairs) the whole-tile schedule was 1-9 % faster -
 // the SMs left idle in the last wave let the busy ones clock higher, and the split adds an
@@ -222,6 +223,13 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       long long grid = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
       if (grid > a.total_items) {
         grid = a.total_items;
+      }
+      // A matrix with no more tiles than SMs: one whole tile per CTA.  Equal item ranges would cut
+      // nearly every tile in two, and the exchange of partial sums through scratch (stores, fences,
+      // an atomic, a re-read by the last arriver) costs more than the few idle SMs.
+      const long long tiles = n / kGemvTileRows;
+      if (tiles <= grid && g_opt_gemv_whole_tiles) {
+        grid = tiles;
       }
       const long long per_cta = (a.total_items + grid - 1) / grid;
       a.n_stages              = nst;
