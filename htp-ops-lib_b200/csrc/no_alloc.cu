@@ -21,6 +21,7 @@
 #include <cstdio>
 #include <mutex>
 
+#include "device_ctx.h"
 #include "gemv_mma.h"
 #include "htp_ops_b200.h"
 
@@ -127,6 +128,10 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
   long long grid    = sm_count < kStaticMaxGrid ? sm_count : kStaticMaxGrid;
   if (grid > a.total_items) {
     grid = a.total_items;
+  }
+  // the same work split as htp_b200_mul_mat: one whole tile per CTA when there are no more tiles than SMs
+  if (n / kGemvTileRows <= grid && g_opt_gemv_whole_tiles) {
+    grid = n / kGemvTileRows;
   }
   const long long per_cta = (a.total_items + grid - 1) / grid;
   a.n_stages              = nst > per_cta ? (int) (per_cta < 2 ? 2 : per_cta) : nst;
