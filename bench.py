@@ -230,6 +230,7 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
     run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(3, steps // 10))
     out["rms_norm_f32_4096x32768"] = measure_rms_norm(torch, lib, peaks, stream_ptr, stream, max(5, steps // 5))
     out.update(measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream, max(5, steps // 5)))
+    out.update(measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, max(5, steps // 5)))
     out.update(measure_decoder_stack(torch, pkg, lib, wl, peaks, quick))
     return out
 
@@ -271,6 +272,44 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
             tf = wl.flops(op, m) / (ms * 1e-3) / 1e12
             r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
         out[name] = r
+        del ws
+    return out
+
+
+def measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, steps):
+    """One-token mat-vecs over weights in the reference's tile order, read in place: the fp16 tiles of the
+    W16A32 op (32768 x 4096, 268 MB) and the permuted Q4_0 / Q8_0 super-blocks (65536 x 4096, 151 / 285 MB),
+    two rotating copies each.  Algorithmic bytes = weight buffer + activation + output."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out = {}
+    for name, fmt, k, n in (("w16a32_tiled_gemv_32768x4096_m1", wl.WT_F16_TILED, 4096, 32768),
+                            ("permuted_q4_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q4_0, 4096, 65536),
+                            ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 4096, 65536)):
+        nbytes = wl.weight_bytes(fmt, k, n)
+        assert nbytes == lib.htp_b200_weight_bytes(fmt, k, n)
+        ws = []
+        for _ in range(2):
+            if fmt == wl.WT_F16_TILED:
+                w = (torch.randn(nbytes // 2, device=dev, dtype=torch.float16) * 0.02).view(torch.uint8)
+            else:
+                sbb = wl.TILE_BYTES[fmt] // 4
+                w = torch.randint(0, 256, (nbytes // sbb, sbb), dtype=torch.uint8, device=dev)
+                w[:, 0:16:2], w[:, 1:16:2] = 0, 0x20  # eight fp16 scales of 2^-7
+                w = w.reshape(-1)
+            ws.append(w)
+        x = torch.randn((1, k), device=dev, dtype=torch.float32)
+        y = torch.empty((1, n), device=dev, dtype=torch.float32)
+
+        def step(i):
+            assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % 2].data_ptr(), 1, k, n, fmt, pkg.ACT_F32,
+                                        stream_ptr) == 0
+        for i in range(3):
+            step(i)
+        ms = time_region(torch, step, steps, stream) / steps
+        assert lib.htp_b200_stream_status(stream_ptr) == 0
+        gb = (nbytes + 4 * k + 4 * n) / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "m": 1, "k": k, "n": n, "weight_copies": 2, "GBps": round(gb, 1),
+                     "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4)}
         del ws
     return out
 

@@ -36,6 +36,8 @@ REQUEST_TYPE_OP_COMPUTE = 2
 TYPE_Q4_0 = 2
 TYPE_Q8_0 = 8
 TYPE_IQ4_NL = 20
+WT_F16_TILED = 1  # fp16 weights in the reference's tile order (HTP_B200_WT_F16_TILED)
+WT_PERMUTED = 0x100  # | TYPE_*: the reference-private permuted super-blocks (HTP_B200_WT_PERMUTED)
 ACT_F32 = 0
 ACT_F16 = 1
 BLOCK_BYTES = {TYPE_Q4_0: 18, TYPE_Q8_0: 34, TYPE_IQ4_NL: 18}

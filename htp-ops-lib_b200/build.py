@@ -13,7 +13,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "libhtp_ops_b200.so"
 
 # Every translation unit of the library.
-SOURCES = ["api.cu", "gemv_mma.cu", "aux_kernels.cu", "host.cu", "no_alloc.cu", "gemm_tcgen05.cu"]
+SOURCES = ["api.cu", "gemv_mma.cu", "aux_kernels.cu", "host.cu", "no_alloc.cu", "gemm_tcgen05.cu", "tiled_weights.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -13,6 +13,7 @@
 #include "device_ctx.h"
 #include "gemm_tcgen05.h"
 #include "gemv_mma.h"
+#include "tiled_weights.h"
 
 namespace htp {
 
@@ -25,6 +26,9 @@ int g_opt_gemv_whole_tiles = getenv("HTP_OPS_NO_WHOLE_TILES") ? 0 : 1;  // small
 // the SMs left idle in the last wave let the busy ones clock higher, and the split adds an
 // epilogue that nothing overlaps.
 int g_opt_gemm_split     = getenv("HTP_OPS_GEMM_SPLIT") ? 1 : 0;
+// Op indices 2, 3 and 4 of the dispatcher read the reference's permuted super-blocks (1) instead of
+// standard ggml blocks (0).
+int g_opt_permuted_weights = 0;
 int g_opt_gemm_tile_n    = 0;   // tokens per GEMM tile: 0 = by M, else 128 or 256  // fp16 activations with at least this many tokens go to the tensor-core GEMM
 
 namespace {
@@ -128,6 +132,17 @@ namespace {
 
 inline bool aligned128(const void *p) {
   return (reinterpret_cast<uintptr_t>(p) & 127u) == 0;
+}
+
+// Tile-order formats (tiled_weights.h) behind their weight_type codes, -1 for the row-major ones.
+inline int tile_fmt_index(int weight_type) {
+  switch (weight_type) {
+    case HTP_B200_WT_F16_TILED: return kTileF16;
+    case HTP_B200_WT_PERMUTED | 2: return kTileQ4;
+    case HTP_B200_WT_PERMUTED | 8: return kTileQ8;
+    case HTP_B200_WT_PERMUTED | 20: return kTileIQ4;
+    default: return -1;
+  }
 }
 
 inline int wt_index(int weight_type) {
@@ -268,8 +283,9 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
   if (!aligned128(dst) || !aligned128(activation) || !aligned128(weight)) {
     return -1;
   }
-  const int wt = wt_index(weight_type);
-  if (wt < 0 || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
+  const int wt   = wt_index(weight_type);
+  const int tfmt = tile_fmt_index(weight_type);
+  if ((wt < 0 && tfmt < 0) || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
     return -1;
   }
   DeviceCtx *ctx = current_device_ctx();
@@ -277,6 +293,16 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     return -2;
   }
   const bool a16 = act_type == HTP_B200_ACT_F16;
+  if (tfmt >= 0) {
+    // weights in the reference's tile order: streamed in place by the tile-order kernel
+    if (tiled_mul_mat_launch(static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n,
+                             tfmt, a16, st) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    count_launch();
+    return 0;
+  }
   if (g_opt_force_generic || k % 256 != 0) {
     if (mul_mat_generic_launch(static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n,
                                wt, a16, st) != cudaSuccess) {
@@ -572,6 +598,13 @@ int htp_b200_rms_norm_f32(float *dst, const float *src, int ne0, int ne1, void *
 }
 
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n) {
+  const int tfmt = tile_fmt_index(weight_type);
+  if (tfmt >= 0) {
+    if (k <= 0 || n <= 0 || k % 32 != 0 || n % 32 != 0) {
+      return 0;
+    }
+    return (size_t) (n / 32) * (size_t) (k / 32) * (size_t) tile_bytes(tfmt);
+  }
   const int wt = wt_index(weight_type);
   if (wt < 0 || k <= 0 || n <= 0 || k % 32 != 0) {
     return 0;
@@ -623,6 +656,8 @@ int htp_b200_set_option(const char *name, int value) {
     slot = &g_opt_gemm_tile_n;
   } else if (!strcmp(name, "gemm_split")) {
     slot = &g_opt_gemm_split;
+  } else if (!strcmp(name, "permuted_weights")) {
+    slot = &g_opt_permuted_weights;
   }
   if (!slot) {
     return -1;

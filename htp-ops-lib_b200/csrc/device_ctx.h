@@ -53,6 +53,7 @@ extern int      g_opt_gemm_min_m;
 extern int      g_opt_gemm_tile_n;
 extern int      g_opt_gemm_split;
 extern int      g_opt_gemv_whole_tiles;
+extern int      g_opt_permuted_weights;
 void            count_launch(int n = 1);
 
 }  // namespace htp

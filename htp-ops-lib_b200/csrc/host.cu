@@ -217,12 +217,17 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   }
   int weight_type, act_type;
   switch (op) {
+    case HTP_OPS_MAT_MUL_PERMUTED_W16A32: weight_type = HTP_B200_WT_F16_TILED, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32: weight_type = 2, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_PERMUTED_W8D16A32: weight_type = 8, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL: weight_type = 20, act_type = HTP_B200_ACT_F32; break;
     case HTP_OPS_MAT_MUL_W4D16A16: weight_type = 2, act_type = HTP_B200_ACT_F16; break;
     case HTP_OPS_MAT_MUL_W8D16A16: weight_type = 8, act_type = HTP_B200_ACT_F16; break;
     default: return -1;  // unknown, or not built in this library
+  }
+  if (htp::g_opt_permuted_weights && op >= HTP_OPS_MAT_MUL_PERMUTED_W4D16A32 &&
+      op <= HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL) {
+    weight_type |= HTP_B200_WT_PERMUTED;  // the reference's own buffers for these op numbers
   }
   MatMulParams p;
   memcpy(&p, req->payload, sizeof(p));
@@ -578,9 +583,18 @@ AEEResult htp_ops_rms_norm_f32(remote_handle64 handle, int32_t fd0, int32_t offs
 AEEResult htp_ops_mat_mul_permuted_w16a32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1,
                                           int32_t offset1, int32_t fd2, int32_t offset2, int32_t m, int32_t k,
                                           int32_t n) {
-  (void) handle, (void) fd0, (void) offset0, (void) fd1, (void) offset1, (void) fd2, (void) offset2;
-  (void) m, (void) k, (void) n;
-  return HTP_AEE_EUNSUPPORTED;
+  (void) handle;
+  if (!set_session_device() || !g.backend) {
+    return HTP_AEE_EFAILED;
+  }
+  alignas(8) uint8_t raw[sizeof(OpComputeRequest) + sizeof(MatMulParams)];
+  OpComputeRequest  *req = reinterpret_cast<OpComputeRequest *>(raw);
+  req->op                = HTP_OPS_MAT_MUL_PERMUTED_W16A32;
+  MatMulParams p;
+  p.output.fd = fd0, p.output.offset = offset0, p.activation.fd = fd1, p.activation.offset = offset1;
+  p.weight.fd = fd2, p.weight.offset = offset2, p.m = m, p.k = k, p.n = n;
+  memcpy(req->payload, &p, sizeof(p));
+  return execute_op_simple(req) == 0 ? HTP_AEE_SUCCESS : HTP_AEE_EFAILED;
 }
 
 AEEResult htp_ops_test_ops(remote_handle64 handle) {

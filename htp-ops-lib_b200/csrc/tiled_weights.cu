@@ -1,0 +1,324 @@
+// Matmul over weights kept in the reference's 32 x 32 TILE ORDER, read in place (no repack):
+//
+//   * fp16 tiles - the weight format of hmx_mat_mul_permuted_w16a32 (reference
+//     src/dsp/ops/mat_mul.c:758-855; the layout is written out by its host test,
+//     src/host/test.c:303-313): tile (n/32, k/32) is tile number (n/32) * (K/32) + k/32, 1024
+//     halfwords each; element (k, n) of the tile sits at halfword (k & ~1) * 32 + n * 2 + (k & 1),
+//     i.e. 16 row-pairs of 128 bytes, each a run of 32 {k even, k odd} pairs, one per column.
+//   * permuted super-blocks my_block_q4_0 (144 B) / my_block_q8_0 (272 B) (reference
+//     include/dsp/quants.h:16-19, 28-31): 8 fp16 scales, then the quants of 256 consecutive
+//     halfword SLOTS of the same tile order, four super-blocks per tile
+//     (mat_mul.c:308-405 and :407-510 expand them slot by slot).  Slot t of a super-block is
+//     k-row 2 * (t / 64) + (t & 1) of its eight k-rows and column (t % 64) / 2; its scale is
+//     scales[t / 32] (the index tables at mat_mul.c:318-325), so one scale covers 2 k-rows x 16
+//     columns.  Q8_0: slot t = (int8) quants[t].  Q4_0 / IQ4_NL: with s = t % 64, the slots of
+//     k-row pairs 0..3 come from quants[2s] & 15, quants[2s+1] & 15, quants[2s] >> 4,
+//     quants[2s+1] >> 4 (the 16-entry lookup sends even bytes to the first and odd bytes to the
+//     second result vector, mat_mul.c:386-387, 402-405).
+//
+// The kernel is a streaming mat-vec: HBM-bound for a few tokens, which is the case the reference
+// exercises (m = 1, test.c:281).  One CTA per 32 output columns; its 16 warps walk the k-tiles of
+// that column tile (contiguous bytes), every lane owning 4 columns and a share of the k-rows, so
+// a warp-wide load instruction covers a contiguous 256..512-byte run.  Products and sums are
+// fp32; nothing is rounded to fp16 (the reference rounds activations and outputs, the contract
+// here is the exact dequantise-then-dot).  Partial sums meet in a fixed order (lane shuffles,
+// then warps in index order): results do not depend on scheduling.
+#include "tiled_weights.h"
+
+#include <cuda_fp16.h>
+
+#include "unpack.cuh"
+
+namespace htp {
+
+namespace {
+
+constexpr int kWarps   = 16;
+constexpr int kThreads = kWarps * 32;
+
+// Two consecutive activations (idx even) as fp32.
+template <bool A16>
+__device__ __forceinline__ float2 ld_act2(const void *x, size_t idx) {
+  if constexpr (A16) {
+    return __half22float2(__ldg(reinterpret_cast<const __half2 *>(static_cast<const __half *>(x) + idx)));
+  } else {
+    return __ldg(reinterpret_cast<const float2 *>(static_cast<const float *>(x) + idx));
+  }
+}
+
+// Eight consecutive activations (idx a multiple of 8) as fp32.
+template <bool A16>
+__device__ __forceinline__ void ld_act8(const void *x, size_t idx, float (&a)[8]) {
+  if constexpr (A16) {
+    const uint4 v = __ldg(reinterpret_cast<const uint4 *>(static_cast<const __half *>(x) + idx));
+    const float2 p0 = __half22float2(u32_as_h2(v.x)), p1 = __half22float2(u32_as_h2(v.y));
+    const float2 p2 = __half22float2(u32_as_h2(v.z)), p3 = __half22float2(u32_as_h2(v.w));
+    a[0] = p0.x, a[1] = p0.y, a[2] = p1.x, a[3] = p1.y, a[4] = p2.x, a[5] = p2.y, a[6] = p3.x, a[7] = p3.y;
+  } else {
+    const float4 *p = reinterpret_cast<const float4 *>(static_cast<const float *>(x) + idx);
+    const float4  u = __ldg(p), v = __ldg(p + 1);
+    a[0] = u.x, a[1] = u.y, a[2] = u.z, a[3] = u.w, a[4] = v.x, a[5] = v.y, a[6] = v.z, a[7] = v.w;
+  }
+}
+
+__device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+// Four 4-bit table indices, one in the low nibble of each byte of `x`, gathered into the low 16
+// bits (index of byte j in bits 4j .. 4j+3), the form iq4nl_lookup4 takes.
+__device__ __forceinline__ uint32_t gather_nibbles(uint32_t x) {
+  const uint32_t y = (x | (x >> 4)) & 0x00FF00FFu;
+  return (y | (y >> 8)) & 0xFFFFu;
+}
+
+// Raw bytes one lane holds of one tile, per format.
+template <int FMT>
+struct LaneTile;
+template <>
+struct LaneTile<kTileF16> {
+  uint4 q[4];  // load j: row-pair 4j + lane/8, columns 4 * (lane % 8) .. +3 as {k even, k odd} pairs
+};
+template <>
+struct LaneTile<kTileQ8> {
+  uint2  q[4];  // super-block sb: slots 8 * lane .. +7 = row-pair lane/8, columns 4 * (lane % 8) .. +3
+  __half d[4];  // scales[lane / 4] of super-block sb
+};
+template <>
+struct LaneTile<kTileQ4> {
+  uint4 q;  // super-block lane/8, quants 16 * (lane % 8) .. +15: all 8 k-rows of columns 4 * (lane % 8) .. +3
+  uint4 d;  // that super-block's eight scales
+};
+template <>
+struct LaneTile<kTileIQ4> : LaneTile<kTileQ4> {};
+
+template <int FMT>
+__device__ __forceinline__ void load_tile(const uint8_t *tile, int lane, LaneTile<FMT> &t) {
+  if constexpr (FMT == kTileF16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      t.q[j] = __ldcs(reinterpret_cast<const uint4 *>(tile + j * 512 + lane * 16));
+    }
+  } else if constexpr (FMT == kTileQ8) {
+#pragma unroll
+    for (int sb = 0; sb < 4; ++sb) {
+      t.q[sb] = __ldcs(reinterpret_cast<const uint2 *>(tile + sb * 272 + 16 + lane * 8));
+      t.d[sb] = __ldg(reinterpret_cast<const __half *>(tile + sb * 272) + (lane >> 2));
+    }
+  } else {
+    const uint8_t *sb = tile + (lane >> 3) * 144;
+    t.q               = __ldcs(reinterpret_cast<const uint4 *>(sb + 16 + (lane & 7) * 16));
+    t.d               = __ldg(reinterpret_cast<const uint4 *>(sb));
+  }
+}
+
+// acc[mm][i] += sum over this lane's k-rows of tile `kt` of x[token mm][k] * W[k][4 * (lane % 8) + i].
+template <int FMT, bool A16, int MT>
+__device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lane, const void *x,
+                                         const size_t (&xrow)[MT], float (&acc)[MT][4]) {
+  if constexpr (FMT == kTileF16) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int k0 = kt * 32 + 2 * (4 * j + (lane >> 3));
+      float2    wv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        wv[i] = __half22float2(u32_as_h2(word_of(t.q[j], i)));
+      }
+#pragma unroll
+      for (int mm = 0; mm < MT; ++mm) {
+        const float2 a = ld_act2<A16>(x, xrow[mm] + k0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[mm][i] = fmaf(a.x, wv[i].x, fmaf(a.y, wv[i].y, acc[mm][i]));
+        }
+      }
+    }
+  } else if constexpr (FMT == kTileQ8) {
+#pragma unroll
+    for (int sb = 0; sb < 4; ++sb) {
+      const int   k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
+      const float d  = __half2float(t.d[sb]);
+      float       we[4], wo[4];  // k even / k odd value of column i, scale applied
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t w = (i < 2 ? t.q[sb].x : t.q[sb].y) >> (16 * (i & 1));
+        we[i]            = (float) (int8_t) (w & 0xFFu) * d;
+        wo[i]            = (float) (int8_t) ((w >> 8) & 0xFFu) * d;
+      }
+#pragma unroll
+      for (int mm = 0; mm < MT; ++mm) {
+        const float2 a = ld_act2<A16>(x, xrow[mm] + k0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[mm][i] = fmaf(a.x, we[i], fmaf(a.y, wo[i], acc[mm][i]));
+        }
+      }
+    }
+  } else {
+    const int  k0 = kt * 32 + (lane >> 3) * 8;
+    const bool hi = (lane & 7) >= 4;  // columns 16..31 use the odd scales
+    float      d[4];                  // scale of k-rows 2v, 2v+1
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      const __half2 p = u32_as_h2(word_of(t.d, v));
+      d[v]            = hi ? __high2float(p) : __low2float(p);
+    }
+    float wv[4][8];  // [column][k-row], scale applied
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t w = word_of(t.q, i);
+      if constexpr (FMT == kTileQ4) {
+        // bytes B0..B3 of the word: k-rows (0, 4) (2, 6) (1, 5) (3, 7) as (low, high) nibbles;
+        // the unpack returns pairs {lo B0, lo B2} {lo B1, lo B3} {hi B0, hi B2} {hi B1, hi B3},
+        // which is k-row order 0..7.
+        uint32_t h[4];
+        q4_0_unpack_word(w, h);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float2 p = __half22float2(u32_as_h2(h[v]));
+          wv[i][2 * v]     = p.x * d[v];
+          wv[i][2 * v + 1] = p.y * d[v];
+        }
+      } else {
+        const uint32_t lo = iq4nl_lookup4(gather_nibbles(w & 0x0F0F0F0Fu));         // k-rows 0 2 1 3
+        const uint32_t up = iq4nl_lookup4(gather_nibbles((w >> 4) & 0x0F0F0F0Fu));  // k-rows 4 6 5 7
+        wv[i][0] = (float) (int8_t) (lo & 0xFFu) * d[0];
+        wv[i][2] = (float) (int8_t) ((lo >> 8) & 0xFFu) * d[1];
+        wv[i][1] = (float) (int8_t) ((lo >> 16) & 0xFFu) * d[0];
+        wv[i][3] = (float) (int8_t) (lo >> 24) * d[1];
+        wv[i][4] = (float) (int8_t) (up & 0xFFu) * d[2];
+        wv[i][6] = (float) (int8_t) ((up >> 8) & 0xFFu) * d[3];
+        wv[i][5] = (float) (int8_t) ((up >> 16) & 0xFFu) * d[2];
+        wv[i][7] = (float) (int8_t) (up >> 24) * d[3];
+      }
+    }
+#pragma unroll
+    for (int mm = 0; mm < MT; ++mm) {
+      float a[8];
+      ld_act8<A16>(x, xrow[mm] + k0, a);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float s = acc[mm][i];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          s = fmaf(a[r], wv[i][r], s);
+        }
+        acc[mm][i] = s;
+      }
+    }
+  }
+}
+
+// Tiles a warp fetches before it starts on their arithmetic: enough bytes in flight per warp
+// (2 KB) whatever the tile size.
+template <int FMT>
+__host__ __device__ constexpr int tiles_in_flight() {
+  return FMT == kTileF16 ? 1 : (FMT == kTileQ8 ? 2 : 4);
+}
+
+template <int FMT, bool A16, int MT>
+__global__ void __launch_bounds__(kThreads)
+    tiled_mul_mat_kernel(float *__restrict__ y, const void *__restrict__ x, const uint8_t *__restrict__ w, int M, int K,
+                         int N) {
+  __shared__ float red[kWarps][MT][32];
+  constexpr int    U    = tiles_in_flight<FMT>();
+  const int        lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int        KT   = K >> 5;
+  const int        nt   = blockIdx.x;
+  const int        m0   = blockIdx.y * MT;
+  const uint8_t   *wt   = w + (size_t) nt * (size_t) KT * tile_bytes(FMT);
+
+  size_t xrow[MT];  // first element of each token's activation row; tokens past M repeat the last
+#pragma unroll
+  for (int mm = 0; mm < MT; ++mm) {
+    const int tok = m0 + mm < M ? m0 + mm : M - 1;
+    xrow[mm]      = (size_t) tok * (size_t) K;
+  }
+  float acc[MT][4];
+#pragma unroll
+  for (int mm = 0; mm < MT; ++mm) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[mm][i] = 0.f;
+    }
+  }
+
+  for (int kt0 = warp * U; kt0 < KT; kt0 += kWarps * U) {
+    LaneTile<FMT> t[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kt0 + u < KT) {  // warp-uniform
+        load_tile<FMT>(wt + (size_t) (kt0 + u) * tile_bytes(FMT), lane, t[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kt0 + u < KT) {
+        fma_tile<FMT, A16, MT>(t[u], kt0 + u, lane, x, xrow, acc);
+      }
+    }
+  }
+
+  // lanes l, l ^ 8, l ^ 16, l ^ 24 hold the same four columns over different k-rows
+#pragma unroll
+  for (int mm = 0; mm < MT; ++mm) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = acc[mm][i];
+      v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
+      v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
+      if (lane < 8) {
+        red[warp][mm][lane * 4 + i] = v;
+      }
+    }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < MT * 32; t += kThreads) {
+    const int mm = t >> 5, c = t & 31;
+    float     s  = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < kWarps; ++wi) {
+      s += red[wi][mm][c];
+    }
+    if (m0 + mm < M) {
+      y[(size_t) (m0 + mm) * (size_t) N + (size_t) nt * 32 + c] = s;
+    }
+  }
+}
+
+template <int FMT, bool A16>
+cudaError_t launch_fmt(float *y, const void *x, const uint8_t *w, int M, int K, int N, cudaStream_t stream) {
+  const int mt = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
+  dim3      grid((unsigned) (N / 32), (unsigned) ((M + mt - 1) / mt));
+  switch (mt) {
+    case 1: tiled_mul_mat_kernel<FMT, A16, 1><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
+    case 2: tiled_mul_mat_kernel<FMT, A16, 2><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
+    case 4: tiled_mul_mat_kernel<FMT, A16, 4><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
+    default: tiled_mul_mat_kernel<FMT, A16, 8><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
+  }
+  return cudaGetLastError();
+}
+
+template <int FMT>
+cudaError_t launch_act(float *y, const void *x, const uint8_t *w, int M, int K, int N, bool a16, cudaStream_t stream) {
+  return a16 ? launch_fmt<FMT, true>(y, x, w, M, K, N, stream) : launch_fmt<FMT, false>(y, x, w, M, K, N, stream);
+}
+
+}  // namespace
+
+cudaError_t tiled_mul_mat_launch(float *y, const void *x, const uint8_t *w, int M, int K, int N, int fmt, bool a16,
+                                 cudaStream_t stream) {
+  if (M <= 0 || K <= 0 || N <= 0 || K % 32 != 0 || N % 32 != 0 || (M + 7) / 8 > 65535) {
+    return cudaErrorInvalidValue;
+  }
+  switch (fmt) {
+    case kTileF16: return launch_act<kTileF16>(y, x, w, M, K, N, a16, stream);
+    case kTileQ4: return launch_act<kTileQ4>(y, x, w, M, K, N, a16, stream);
+    case kTileQ8: return launch_act<kTileQ8>(y, x, w, M, K, N, a16, stream);
+    case kTileIQ4: return launch_act<kTileIQ4>(y, x, w, M, K, N, a16, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace htp

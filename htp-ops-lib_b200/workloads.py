@@ -97,7 +97,62 @@ def quantize(w: np.ndarray, wtype: int, row_chunk: int = 4096) -> np.ndarray:
 
 
 def weight_bytes(wtype: int, k: int, n: int) -> int:
+    if wtype in TILE_BYTES:
+        return (n // 32) * (k // 32) * TILE_BYTES[wtype]
     return n * (k // 32) * BLOCK_BYTES[wtype]
+
+
+# ----------------------------------------------------------------------------------------------
+# Weights in the reference's 32 x 32 tile order (weight_type codes of include/htp_ops_b200.h).
+# Tile (n/32, k/32) is tile number (n/32) * (K/32) + k/32; element (k, n) of a tile is halfword slot
+# (k & ~1) * 32 + n * 2 + (k & 1) (reference src/host/test.c:303-313).
+
+WT_F16_TILED = 1
+WT_PERMUTED = 0x100
+TILE_BYTES = {WT_F16_TILED: 2048, WT_PERMUTED | TYPE_Q4_0: 576, WT_PERMUTED | TYPE_Q8_0: 1088,
+              WT_PERMUTED | TYPE_IQ4_NL: 576}
+
+
+def _tile_slots(w_kn: np.ndarray) -> np.ndarray:
+    """[K][N] -> [N/32][K/32][super-block 4][k-row pair 4][slot 64], slot = 2 * column + (k & 1)."""
+    k, n = w_kn.shape
+    assert k % 32 == 0 and n % 32 == 0
+    a = w_kn.reshape(k // 32, 4, 4, 2, n // 32, 32)  # k-tile, super-block, row pair, parity, n-tile, column
+    return np.ascontiguousarray(a.transpose(4, 0, 1, 2, 5, 3)).reshape(n // 32, k // 32, 4, 4, 64)
+
+
+def pack_f16_tiles(w_kn: np.ndarray) -> np.ndarray:
+    """fp16-representable weights W[K][N] -> the fp16 tile buffer of the W16A32 op (uint8 view)."""
+    return _tile_slots(np.asarray(w_kn).astype(np.float16)).view(np.uint8).reshape(-1)
+
+
+def quantize_permuted(w_kn: np.ndarray, wtype: int) -> np.ndarray:
+    """fp32 W[K][N] -> the reference-private permuted super-blocks (my_block_q4_0 144 B / my_block_q8_0
+    272 B, four per tile; wtype = TYPE_Q4_0, TYPE_Q8_0 or TYPE_IQ4_NL).  A scale group is 32 consecutive
+    slots = 2 k-rows x 16 columns; each group is quantised by the same rule as a standard block, then the
+    quants are laid out as the reference's expansion reads them (src/dsp/ops/mat_mul.c:373-405, 472-506)."""
+    slots = _tile_slots(np.asarray(w_kn, dtype=np.float32))
+    groups = slots.reshape(-1, 32)
+    blocks = quantize(groups, wtype).reshape(groups.shape[0], BLOCK_BYTES[wtype])
+    n_sb = groups.shape[0] // 8
+    scales = blocks[:, :2].reshape(n_sb, 16)
+    if wtype == TYPE_Q8_0:
+        return np.concatenate([scales, blocks[:, 2:].reshape(n_sb, 256)], axis=1).reshape(-1)
+    qs = blocks[:, 2:]
+    q = np.concatenate([qs & 15, qs >> 4], axis=1).reshape(n_sb, 4, 64)  # [super-block][row pair][slot]
+    out = np.empty((n_sb, 64, 2), dtype=np.uint8)
+    out[:, :, 0] = q[:, 0] | (q[:, 2] << 4)
+    out[:, :, 1] = q[:, 1] | (q[:, 3] << 4)
+    return np.concatenate([scales, out.reshape(n_sb, 128)], axis=1).reshape(-1)
+
+
+def tiled_random_case(seed: int, fmt: int, act_f16: bool, m: int, k: int, n: int, scale: float = 0.02):
+    """Seeded case in a tile-order format: (weight buffer, activations [m][k])."""
+    rng = _rng(seed, fmt, int(act_f16), m, k, n)
+    w = rng.standard_normal((k, n), dtype=np.float32) * np.float32(scale)
+    x = rng.standard_normal((m, k), dtype=np.float32)
+    wq = pack_f16_tiles(w) if fmt == WT_F16_TILED else quantize_permuted(w, fmt & 0xFF)
+    return wq, (x.astype(np.float16) if act_f16 else x)
 
 
 @dataclasses.dataclass(frozen=True)

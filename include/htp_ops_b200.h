@@ -25,6 +25,24 @@ extern "C" {
 #define HTP_B200_ACT_F16 1
 
 /*
+ * weight_type codes.  2, 8 and 20 are ggml's type numbers (Q4_0, Q8_0, IQ4_NL) and mean standard
+ * ggml blocks, n rows of k/32 blocks.  The codes below mean weights in the reference's own 32 x 32
+ * TILE ORDER, tile (n/32, k/32) at tile number (n/32) * (k_total/32) + k/32, read in place:
+ *   HTP_B200_WT_F16_TILED        fp16 tiles of 2048 B, element (k, n) of a tile at halfword
+ *                                (k & ~1) * 32 + n * 2 + (k & 1) - the weight buffer of
+ *                                hmx_mat_mul_permuted_w16a32 (reference src/dsp/ops/mat_mul.c:758-855,
+ *                                layout written by src/host/test.c:303-313);
+ *   HTP_B200_WT_PERMUTED | type  the reference-private super-blocks my_block_q4_0 (144 B) /
+ *                                my_block_q8_0 (272 B), four per tile (reference
+ *                                include/dsp/quants.h:16-31, expanded at mat_mul.c:308-510) - the
+ *                                buffers the reference's own ops 2, 3 and 4 consume; type = 2, 8 or 20.
+ * These go through htp_b200_mul_mat only (any m, either activation type; a streaming kernel
+ * sized for a few tokens); the batch, multi-destination and static-scratch calls reject them.
+ */
+#define HTP_B200_WT_F16_TILED 1
+#define HTP_B200_WT_PERMUTED 0x100
+
+/*
  * dst[m][n] (fp32) = activation[m][k] . weight[n][k]^T, weight in standard ggml Q4_0
  * (weight_type 2) or Q8_0 (weight_type 8) blocks, n rows of k/32 blocks.
  * Replaces hmx_mat_mul_permuted_qk_0_d16a32 (reference include/dsp/ops.h:19-20,
@@ -123,7 +141,9 @@ int htp_b200_stream_status(void *stream);
  * (fp16-activation matmuls with at least this many tokens use the tensor-core GEMM, default 64),
  * "gemm_tile_n" (tokens per GEMM tile: 0 = automatic, 128 or 256), "gemm_split" (when the GEMM's
  * tiles do not divide evenly among the SMs, cut the work into equal K ranges and finish the split
- * tiles through a scratch area, default 0).  Returns the previous value, or -1 for an unknown name. */
+ * tiles through a scratch area, default 0), "permuted_weights" (op indices 2, 3 and 4 of
+ * execute_op_simple / the message channel read HTP_B200_WT_PERMUTED buffers, as the reference's
+ * ops of those numbers do, instead of standard ggml blocks; default 0).  Returns the previous value, or -1 for an unknown name. */
 int htp_b200_set_option(const char *name, int value);
 
 /* Number of kernel launches this process has issued through the library (all devices). */

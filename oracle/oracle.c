@@ -394,6 +394,117 @@ int htp_oracle_mul_mat_f64(double *y, double *absdot, const void *act, int act_i
   return 0;
 }
 
+/* ---------------------------------------------------------------- weights in tile order
+ *
+ * The reference's own weight buffers are stored in 32 x 32 tile order: tile (n/32, k/32) is tile
+ * number (n/32) * (K/32) + k/32, and inside a tile element (k, n) is halfword slot
+ * T = (k & ~1) * 32 + n * 2 + (k & 1) (src/host/test.c:303-313 writes fp16 weights that way for
+ * hmx_mat_mul_permuted_w16a32; src/dsp/ops/mat_mul.c:594-605 scatters dequantised groups the same
+ * way).  Formats, by the library's weight_type code:
+ *   1      fp16 tiles, 2048 B each: the slot holds the weight.
+ *   0x102  my_block_q4_0 (include/dsp/quants.h:16-19): 144-byte super-blocks, four per tile, each
+ *          8 fp16 scales then quants[128] covering slots T = 256 * sb + t.  With v = t / 64 and
+ *          s = t % 64 the nibble of slot t is quants[2s] & 15 (v = 0), quants[2s + 1] & 15 (v = 1),
+ *          quants[2s] >> 4 (v = 2), quants[2s + 1] >> 4 (v = 3): mat_mul.c:373-376 looks up the low
+ *          and the high nibbles of all 128 bytes, the lookup returns even bytes in its first and odd
+ *          bytes in its second vector, and :402-405 stores the four vectors in that order.  value =
+ *          nibble - 8 (table at :25-27), scale = scales[t / 32] (index tables :318-325, :396-400).
+ *   0x114  the same block with the IQ4_NL table (:29-32, selected at :316).
+ *   0x108  my_block_q8_0 (quants.h:28-31): 272-byte super-blocks, 8 fp16 scales then quants[256];
+ *          slot t = (int8) quants[t] in order (:472-489), scale = scales[t / 32].
+ * PARITY UNPINNED for the three permuted formats: no producer, test or fixture of them exists in
+ * the reference; the slot order above is read off the vector code and rests on the lookup
+ * instruction's even/odd split, which the un-coalesced branch of the same function (:345-372,
+ * eight standard groups -> four vectors) agrees with.  The fp16 format is pinned by test.c's
+ * index formula.
+ */
+static int tiled_tile_bytes(int fmt) {
+  return fmt == 1 ? 2048 : (fmt == 0x108 ? 1088 : ((fmt == 0x102 || fmt == 0x114) ? 576 : 0));
+}
+
+/* out[j * k + l] (fp32, exact) = weight of input l for output j, for all n outputs. */
+int htp_oracle_tiled_dequantize(const uint8_t *w, float *out, int64_t k, int64_t n, int fmt) {
+  const int tb = tiled_tile_bytes(fmt);
+  if (!tb || k <= 0 || n <= 0 || k % 32 || n % 32) {
+    return -1;
+  }
+  const int64_t kt_n = k / 32;
+  for (int64_t nt = 0; nt < n / 32; ++nt) {
+    for (int64_t kt = 0; kt < kt_n; ++kt) {
+      const uint8_t *tile = w + (nt * kt_n + kt) * tb;
+      for (int T = 0; T < 1024; ++T) {
+        const int r = (T / 64) * 2 + (T & 1); /* k within the tile */
+        const int c = (T % 64) / 2;           /* n within the tile */
+        float     val;
+        if (fmt == 1) {
+          uint16_t h;
+          memcpy(&h, tile + 2 * T, 2);
+          val = f16_bits_to_f32(h);
+        } else {
+          const int      sb   = T / 256, t = T % 256;
+          const int      sbb  = tb / 4;
+          const uint8_t *blk  = tile + sb * sbb;
+          uint16_t       dbits;
+          memcpy(&dbits, blk + 2 * (t / 32), 2);
+          const float d = f16_bits_to_f32(dbits);
+          int         q;
+          if (fmt == 0x108) {
+            q = (int8_t) blk[16 + t];
+          } else {
+            const int     v = t / 64, s = t % 64;
+            const uint8_t b   = blk[16 + 2 * s + (v & 1)];
+            const int     nib = v < 2 ? (b & 0x0F) : (b >> 4);
+            q = fmt == 0x102 ? nib - 8 : kIq4nlValues[nib];
+          }
+          val = (float) q * d;
+        }
+        out[(nt * 32 + c) * k + kt * 32 + r] = val;
+      }
+    }
+  }
+  return 0;
+}
+
+struct mmd_ctx {
+  const float *wd;
+  const void  *act;
+  int          act_is_f16;
+  double      *y, *absdot;
+  int64_t      m, k, n;
+};
+
+static void mmd_rows_f64(void *p, int64_t j0, int64_t j1) {
+  struct mmd_ctx *c = (struct mmd_ctx *) p;
+  for (int64_t j = j0; j < j1; ++j) {
+    for (int64_t i = 0; i < c->m; ++i) {
+      double acc = 0.0, aabs = 0.0;
+      for (int64_t l = 0; l < c->k; ++l) {
+        const double a = c->act_is_f16 ? (double) f16_bits_to_f32(((const uint16_t *) c->act)[i * c->k + l])
+                                       : (double) ((const float *) c->act)[i * c->k + l];
+        const double t = a * (double) c->wd[j * c->k + l];
+        acc += t;
+        aabs += fabs(t);
+      }
+      c->y[i * c->n + j] = acc;
+      if (c->absdot) {
+        c->absdot[i * c->n + j] = aabs;
+      }
+    }
+  }
+}
+
+/* fp64 oracle over a dense fp32 weight matrix wd[n][k] (as htp_oracle_tiled_dequantize returns):
+ * y[m][n] = act[m][k] . wd^T in the loop shape of src/host/test.c:319-327, double accumulate. */
+int htp_oracle_mul_mat_dense_f64(double *y, double *absdot, const void *act, int act_is_f16, const float *wd,
+                                 int64_t m, int64_t k, int64_t n, int n_threads) {
+  if (m <= 0 || n <= 0 || k <= 0) {
+    return -1;
+  }
+  struct mmd_ctx c = { wd, act, act_is_f16, y, absdot, m, k, n };
+  parallel_ranges(mmd_rows_f64, &c, n, n_threads);
+  return 0;
+}
+
 /* Timed CPU baseline: same dequantise-then-dot, fp32 weights and fp32 accumulation, threads
  * over output rows.  The activation rows are converted to fp32 once up front. */
 struct mm32_ctx {

@@ -59,6 +59,10 @@ def load(path: str | os.PathLike | None = None):
     lib.htp_oracle_rms_norm_f32.argtypes = [vp, vp, i64, i64, i32]
     lib.htp_oracle_mul_mat_f32.restype = i32
     lib.htp_oracle_mul_mat_f32.argtypes = [vp, vp, i32, vp, i64, i64, i64, i32, i32]
+    lib.htp_oracle_tiled_dequantize.restype = i32
+    lib.htp_oracle_tiled_dequantize.argtypes = [vp, vp, i64, i64, i32]
+    lib.htp_oracle_mul_mat_dense_f64.restype = i32
+    lib.htp_oracle_mul_mat_dense_f64.argtypes = [vp, vp, vp, i32, vp, i64, i64, i64, i32]
     if path is None:
         _lib = lib
     return lib
@@ -128,6 +132,29 @@ def mul_mat_f32(act: np.ndarray, wq: np.ndarray, n: int, wtype: int, threads: in
     if r != 0:
         raise ValueError("bad arguments")
     return y
+
+
+def tiled_dequantize(w: np.ndarray, k: int, n: int, fmt: int) -> np.ndarray:
+    """Weights in the reference's tile order (fmt = the library's weight_type code: 1 fp16 tiles, 0x102 /
+    0x108 / 0x114 permuted Q4_0 / Q8_0 / IQ4_NL super-blocks) -> dense fp32 [n][k], slot by slot."""
+    out = np.empty((n, k), dtype=np.float32)
+    if load().htp_oracle_tiled_dequantize(_ptr(w), _ptr(out), k, n, fmt) != 0:
+        raise ValueError("bad arguments")
+    return out
+
+
+def tiled_mul_mat_f64(act: np.ndarray, w: np.ndarray, n: int, fmt: int, threads: int = 0, want_absdot: bool = False):
+    """The parity oracle for tile-order weights: dequantise exactly, then the fp64 dot."""
+    m, k = act.shape
+    wd = tiled_dequantize(w, k, n, fmt)
+    a, is16 = _act_args(act)
+    y = np.empty((m, n), dtype=np.float64)
+    ad = np.empty((m, n), dtype=np.float64) if want_absdot else None
+    r = load().htp_oracle_mul_mat_dense_f64(_ptr(y), _ptr(ad) if want_absdot else None, _ptr(a), is16, _ptr(wd), m, k,
+                                            n, threads)
+    if r != 0:
+        raise ValueError("bad arguments")
+    return (y, ad) if want_absdot else y
 
 
 # ----------------------------------------------------------------------------------------------

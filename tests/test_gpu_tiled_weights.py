@@ -1,0 +1,110 @@
+"""GPU parity of the matmul over weights in the reference's tile order: the fp16 tiles of
+hmx_mat_mul_permuted_w16a32 (op index 1 and the RPC-named call; the shape of the reference's own
+test, src/host/test.c:275-317, is among the cases) and the permuted Q4_0 / Q8_0 / IQ4_NL
+super-blocks that the reference's ops 2, 3 and 4 consume (option "permuted_weights").  Gates as for
+the standard-layout path: 1e-5 (fp32 activations) / 1e-3 (fp16) against the fp64 oracle, relative to
+the largest output and to sum |x w| per output."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+Q4, Q8, IQ4 = 2, 8, 20
+PERM = 0x100
+FMTS = [1, PERM | Q4, PERM | Q8, PERM | IQ4]
+SHAPES = [(1, 1024, 1024), (1, 256, 32), (2, 2048, 480), (3, 1024, 224), (7, 512, 96), (8, 4096, 256),
+          (1, 14336, 64), (20, 512, 64), (1, 96, 64), (5, 32, 32)]
+
+
+def _check(oracle, y, x, wq, n, fmt, tol):
+    ref, absdot = oracle.tiled_mul_mat_f64(x, wq, n, fmt, want_absdot=True)
+    e = oracle.error_metrics(y, ref, absdot)
+    assert np.isfinite(y).all()
+    assert e["max_rel_to_max"] <= tol and e["max_cond_rel"] <= tol, e
+
+
+def _raw(dev, x, wq, n, fmt):
+    import torch
+    m, k = x.shape
+    tw = torch.from_numpy(wq).cuda()
+    tx = torch.from_numpy(x).cuda()
+    ty = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    before = dev.lib.htp_b200_launch_count()
+    rc = dev.lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, fmt,
+                                  1 if x.dtype == np.float16 else 0, st)
+    assert rc == 0
+    assert dev.lib.htp_b200_launch_count() == before + 1
+    assert dev.lib.htp_b200_stream_status(st) == 0
+    return ty.cpu().numpy()
+
+
+@pytest.mark.parametrize("act_f16", [False, True])
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,k,n", SHAPES)
+def test_tile_order_matmul_matches_oracle(dev, oracle, wl, fmt, act_f16, m, k, n):
+    wq, x = wl.tiled_random_case(50, fmt, act_f16, m, k, n)
+    assert wq.size == dev.lib.htp_b200_weight_bytes(fmt, k, n)
+    _check(oracle, _raw(dev, x, wq, n, fmt), x, wq, n, fmt, 1e-3 if act_f16 else 1e-5)
+
+
+def test_w16a32_rpc_named_call_on_the_reference_test_shape(dev, oracle, wl):
+    """m = 1, k = 1024, n = 1024, inputs uniform in [0, 1) as in src/host/test.c:281-313; the call is the
+    one that test makes (htp_ops_mat_mul_permuted_w16a32 on three mapped buffers)."""
+    m, k, n = 1, 1024, 1024
+    rng = np.random.Generator(np.random.PCG64(51))
+    x = rng.random((m, k), dtype=np.float32)
+    w = rng.random((k, n), dtype=np.float32)
+    wq = wl.pack_f16_tiles(w)
+    fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
+    assert dev.lib.htp_ops_mat_mul_permuted_w16a32(dev.lib.get_global_handle(), fy, 0, fx, 0, fw, 0, m, k, n) == 0
+    y = dev.get(fy, (m, n))
+    _check(oracle, y, x, wq, n, 1, 1e-5)
+    # and against plain fp64 on the fp16-rounded matrix, the reference test's own "f32" column
+    ref = x.astype(np.float64) @ w.astype(np.float16).astype(np.float64)
+    assert np.abs(y - ref).max() <= 1e-5 * np.abs(ref).max()
+    # the wrapper of include/host/op_export.h and the op registry give the same bytes
+    fz = dev.buf(m * n * 4)
+    assert dev.lib.htp_ops_rpc_mat_mul_permuted_w16a32(fz, 0, fx, 0, fw, 0, m, k, n) == 0
+    assert (dev.get(fz, (m, n)) == y).all()
+    assert dev.execute(dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W16A32, (fz, 0), (fx, 0), (fw, 0), m, k, n) == 0
+    assert (dev.get(fz, (m, n)) == y).all()
+    # the reference's argument rules: k % 32, n % 32, buffer sizes
+    assert dev.lib.htp_ops_mat_mul_permuted_w16a32(dev.lib.get_global_handle(), fy, 0, fx, 0, fw, 0, m, k, n + 16) != 0
+    assert dev.lib.htp_ops_mat_mul_permuted_w16a32(dev.lib.get_global_handle(), fy, 0, fx, 0, fw, 0, m, k + 8, n) != 0
+    assert dev.lib.htp_ops_mat_mul_permuted_w16a32(dev.lib.get_global_handle(), fy, 0, fx, 0, fw, 0, m, k, 2 * n) != 0
+    dev.free(fw, fx, fy, fz)
+
+
+@pytest.mark.parametrize("wtype,op_name", [(Q4, "HTP_OPS_MAT_MUL_PERMUTED_W4D16A32"),
+                                           (Q8, "HTP_OPS_MAT_MUL_PERMUTED_W8D16A32"),
+                                           (IQ4, "HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL")])
+def test_ops_2_3_4_read_permuted_super_blocks_when_asked(dev, oracle, wl, wtype, op_name):
+    m, k, n = 2, 1024, 256
+    wq, x = wl.tiled_random_case(52, PERM | wtype, False, m, k, n)
+    fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
+    op = getattr(dev.pkg, op_name)
+    prev = dev.lib.htp_b200_set_option(b"permuted_weights", 1)
+    try:
+        assert dev.execute(op, (fy, 0), (fx, 0), (fw, 0), m, k, n) == 0
+        y = dev.get(fy, (m, n))
+    finally:
+        dev.lib.htp_b200_set_option(b"permuted_weights", prev)
+    _check(oracle, y, x, wq, n, PERM | wtype, 1e-5)
+    dev.free(fw, fx, fy)
+
+
+def test_tile_order_formats_are_rejected_where_not_supported(dev, wl):
+    import torch
+    m, k, n = 1, 256, 64
+    wq, x = wl.tiled_random_case(53, 1, False, m, k, n)
+    tw, tx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    ty = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    lib = dev.lib
+    assert lib.htp_b200_mul_mat_static_scratch(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, 1, 0, None) != 0
+    assert lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, PERM | 3, 0, None) == -1
+    assert lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k + 16, n, 1, 0, None) == -1
+    assert lib.htp_b200_weight_bytes(1, 256, 48) == 0 and lib.htp_b200_weight_bytes(PERM | 8, 256, 64) == 16 * 1088
+    torch.cuda.synchronize()
