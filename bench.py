@@ -276,6 +276,18 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
     return out
 
 
+def tile_order_device_weights(torch, wl, fmt: int, k: int, n: int, dev):
+    """A device-resident weight buffer in one of the tile-order formats.  Timing does not depend on the
+    values: fp16 tiles hold N(0, 0.02^2), super-blocks hold random quant bytes under scales of 2^-7."""
+    nbytes = wl.weight_bytes(fmt, k, n)
+    if fmt == wl.WT_F16_TILED:
+        return (torch.randn(nbytes // 2, device=dev, dtype=torch.float16) * 0.02).view(torch.uint8)
+    sbb = wl.TILE_BYTES[fmt] // 4
+    w = torch.randint(0, 256, (nbytes // sbb, sbb), dtype=torch.uint8, device=dev)
+    w[:, 0:16:2], w[:, 1:16:2] = 0, 0x20
+    return w.reshape(-1)
+
+
 def measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, steps):
     """One-token mat-vecs over weights in the reference's tile order, read in place: the fp16 tiles of the
     W16A32 op (32768 x 4096, 268 MB) and the permuted Q4_0 / Q8_0 super-blocks (65536 x 4096, 151 / 285 MB),
@@ -287,16 +299,7 @@ def measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, st
                             ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 4096, 65536)):
         nbytes = wl.weight_bytes(fmt, k, n)
         assert nbytes == lib.htp_b200_weight_bytes(fmt, k, n)
-        ws = []
-        for _ in range(2):
-            if fmt == wl.WT_F16_TILED:
-                w = (torch.randn(nbytes // 2, device=dev, dtype=torch.float16) * 0.02).view(torch.uint8)
-            else:
-                sbb = wl.TILE_BYTES[fmt] // 4
-                w = torch.randint(0, 256, (nbytes // sbb, sbb), dtype=torch.uint8, device=dev)
-                w[:, 0:16:2], w[:, 1:16:2] = 0, 0x20  # eight fp16 scales of 2^-7
-                w = w.reshape(-1)
-            ws.append(w)
+        ws = [tile_order_device_weights(torch, wl, fmt, k, n, dev) for _ in range(2)]
         x = torch.randn((1, k), device=dev, dtype=torch.float32)
         y = torch.empty((1, n), device=dev, dtype=torch.float32)
 
@@ -717,7 +720,8 @@ def run_ours(args):
 
 def run_case(args):
     """One matmul shape, device-resident, rotating weight copies: the small case the ncu captures
-    use (`--case q8_0,f16,1,4096,32768`)."""
+    use (`--case q8_0,f16,1,4096,32768`; weight kinds q4_0, q8_0, and the tile-order ones w16_tiled, pq4_0, pq8_0,
+    piq4_nl)."""
     import torch
 
     pkg = entry.load_package()
@@ -725,7 +729,9 @@ def run_case(args):
     lib = pkg.load()
     wt_s, act_s, m, k, n = args.case.split(",")
     m, k, n = int(m), int(k), int(n)
-    wtype = {"q4_0": wl.TYPE_Q4_0, "q8_0": wl.TYPE_Q8_0}[wt_s]
+    wtype = {"q4_0": wl.TYPE_Q4_0, "q8_0": wl.TYPE_Q8_0, "w16_tiled": wl.WT_F16_TILED,
+             "pq4_0": wl.WT_PERMUTED | wl.TYPE_Q4_0, "pq8_0": wl.WT_PERMUTED | wl.TYPE_Q8_0,
+             "piq4_nl": wl.WT_PERMUTED | wl.TYPE_IQ4_NL}[wt_s]
     a16 = act_s == "f16"
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
@@ -733,7 +739,7 @@ def run_case(args):
     op = cfg.ops[0]
     slab = wl.weight_bytes(wtype, k, n)
     copies = max(2, -(-L2_BYTES // slab) + 1) if m <= 8 else 1
-    w0 = wl.make_weight_torch(cfg, dev)
+    w0 = tile_order_device_weights(torch, wl, wtype, k, n, dev) if wtype in wl.TILE_BYTES else wl.make_weight_torch(cfg, dev)
     ws = [w0] + [w0.clone() for _ in range(copies - 1)]
     x = torch.randn((m, k), device=dev, dtype=torch.float32)
     x = x.to(torch.float16) if a16 else x

@@ -50,6 +50,25 @@ def test_tile_order_matmul_matches_oracle(dev, oracle, wl, fmt, act_f16, m, k, n
     _check(oracle, _raw(dev, x, wq, n, fmt), x, wq, n, fmt, 1e-3 if act_f16 else 1e-5)
 
 
+def test_tile_order_matmul_matches_committed_golden_samples(dev):
+    """The committed fixtures (tests/golden/golden_tiled.json): same seeded inputs, GPU output against the
+    stored fp64 samples."""
+    import json
+    from pathlib import Path
+
+    from test_tiled_formats import golden_module
+    gm = golden_module()
+    golden = json.loads((Path(__file__).parent / "golden" / "golden_tiled.json").read_text())
+    for name, want in golden.items():
+        fmt, n, wq, x = gm.make_case(name)
+        assert gm.wl.sha256(wq) == want["w_sha256"]
+        y = _raw(dev, x, wq, n, fmt)
+        tol = 1e-3 if x.dtype == np.float16 else 1e-5
+        scale = max(np.abs(np.array(want["head"])).max(), np.abs(np.array(want["tail"])).max())
+        assert np.abs(y[:, :16] - np.array(want["head"])).max() <= tol * scale
+        assert np.abs(y[:, -16:] - np.array(want["tail"])).max() <= tol * scale
+
+
 def test_w16a32_rpc_named_call_on_the_reference_test_shape(dev, oracle, wl):
     """m = 1, k = 1024, n = 1024, inputs uniform in [0, 1) as in src/host/test.c:281-313; the call is the
     one that test makes (htp_ops_mat_mul_permuted_w16a32 on three mapped buffers)."""

@@ -6,8 +6,23 @@ one, and packer -> reader round trips.  No reference test or fixture holds these
 permuted ones stay "parity unpinned"."""
 from __future__ import annotations
 
+import importlib.util
+import json
+from pathlib import Path
+
 import numpy as np
 import pytest
+
+GOLDEN_DIR = Path(__file__).parent / "golden"
+GOLDEN = json.loads((GOLDEN_DIR / "golden_tiled.json").read_text())
+
+
+def golden_module():
+    spec = importlib.util.spec_from_file_location("make_golden_tiled", GOLDEN_DIR / "make_golden_tiled.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
 
 Q4, Q8, IQ4 = 2, 8, 20
 PERM = 0x100
@@ -120,3 +135,14 @@ def test_tiled_oracle_matmul_equals_dense_fp64(wl, oracle):
         assert (absdot >= np.abs(y) - 1e-12).all()
     with pytest.raises(ValueError):
         oracle.tiled_dequantize(wq, 48, 64, fmt)
+
+
+@pytest.mark.parametrize("name", sorted(GOLDEN))
+def test_golden_tile_order_cases(name):
+    """Packer and oracle reproduce the committed fixtures bit for bit (hashes) / to 1e-12 (fp64 samples)."""
+    g = golden_module().entry_of(name)
+    want = GOLDEN[name]
+    assert g["w_sha256"] == want["w_sha256"] and g["x_sha256"] == want["x_sha256"]
+    for key in ("head", "tail"):
+        assert np.allclose(np.array(g[key]), np.array(want[key]), rtol=1e-12, atol=0)
+    assert abs(g["abs_sum"] - want["abs_sum"]) <= 1e-10 * want["abs_sum"]
