@@ -17,17 +17,22 @@
 //     second result vector, mat_mul.c:386-387, 402-405).
 //
 // The kernel is a streaming mat-vec: HBM-bound for a few tokens, which is the case the reference
-// exercises (m = 1, test.c:281).  One CTA per 32 output columns; its 16 warps walk the k-tiles of
-// that column tile (contiguous bytes), every lane owning 4 columns and a share of the k-rows, so
+// exercises (m = 1, test.c:281).  One CTA per 32 output columns (a cluster of up to 8 CTAs that
+// split K when the matrix has few column tiles); its 16 warps walk the k-tiles of that column
+// tile (contiguous bytes), every lane owning 4 columns and a share of the k-rows, so
 // a warp-wide load instruction covers a contiguous 256..512-byte run.  Products and sums are
 // fp32; nothing is rounded to fp16 (the reference rounds activations and outputs, the contract
 // here is the exact dequantise-then-dot).  Partial sums meet in a fixed order (lane shuffles,
-// then warps in index order): results do not depend on scheduling.
+// warps in index order, then the cluster's CTAs in rank order through distributed shared
+// memory): results do not depend on scheduling, and the kernel needs no scratch memory.
 #include "tiled_weights.h"
 
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include "unpack.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace htp {
 
@@ -217,16 +222,22 @@ __host__ __device__ constexpr int tiles_in_flight() {
   return FMT == kTileF16 ? 1 : (FMT == kTileQ8 ? 2 : 4);
 }
 
+// grid = (N / 32, token groups, S).  S > 1: the launch is made of clusters of S CTAs along z that
+// share one column tile and token group and split its k-tiles into S contiguous ranges; their
+// partial sums meet in the first CTA through distributed shared memory, in rank order.
 template <int FMT, bool A16, int MT>
 __global__ void __launch_bounds__(kThreads)
     tiled_mul_mat_kernel(float *__restrict__ y, const void *__restrict__ x, const uint8_t *__restrict__ w, int M, int K,
                          int N) {
   __shared__ float red[kWarps][MT][32];
+  __shared__ float part[MT][32];
   constexpr int    U    = tiles_in_flight<FMT>();
   const int        lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int        KT   = K >> 5;
   const int        nt   = blockIdx.x;
   const int        m0   = blockIdx.y * MT;
+  const int        S    = gridDim.z, rank = blockIdx.z;
+  const int        kt_begin = (int) ((long long) KT * rank / S), kt_end = (int) ((long long) KT * (rank + 1) / S);
   const uint8_t   *wt   = w + (size_t) nt * (size_t) KT * tile_bytes(FMT);
 
   size_t xrow[MT];  // first element of each token's activation row; tokens past M repeat the last
@@ -244,17 +255,17 @@ __global__ void __launch_bounds__(kThreads)
     }
   }
 
-  for (int kt0 = warp * U; kt0 < KT; kt0 += kWarps * U) {
+  for (int kt0 = kt_begin + warp * U; kt0 < kt_end; kt0 += kWarps * U) {
     LaneTile<FMT> t[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (kt0 + u < KT) {  // warp-uniform
+      if (kt0 + u < kt_end) {  // warp-uniform
         load_tile<FMT>(wt + (size_t) (kt0 + u) * tile_bytes(FMT), lane, t[u]);
       }
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      if (kt0 + u < KT) {
+      if (kt0 + u < kt_end) {
         fma_tile<FMT, A16, MT>(t[u], kt0 + u, lane, x, xrow, acc);
       }
     }
@@ -274,30 +285,88 @@ __global__ void __launch_bounds__(kThreads)
     }
   }
   __syncthreads();
-  for (int t = threadIdx.x; t < MT * 32; t += kThreads) {
-    const int mm = t >> 5, c = t & 31;
-    float     s  = 0.f;
+  float s = 0.f;
+  if (threadIdx.x < MT * 32) {  // MT * 32 <= 256 < kThreads: one output per thread
+    const int mm = threadIdx.x >> 5, c = threadIdx.x & 31;
 #pragma unroll
     for (int wi = 0; wi < kWarps; ++wi) {
       s += red[wi][mm][c];
     }
+    part[mm][c] = s;
+  }
+  if (S > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every CTA's part[][] is written
+    if (rank == 0 && threadIdx.x < MT * 32) {
+      for (int r = 1; r < S; ++r) {
+        const float *peer = cluster.map_shared_rank(&part[0][0], r);
+        s += peer[threadIdx.x];
+      }
+    }
+    cluster.sync();  // peers keep their shared memory until it has been read
+    if (rank != 0) {
+      return;
+    }
+  }
+  if (threadIdx.x < MT * 32) {
+    const int mm = threadIdx.x >> 5, c = threadIdx.x & 31;
     if (m0 + mm < M) {
       y[(size_t) (m0 + mm) * (size_t) N + (size_t) nt * 32 + c] = s;
     }
   }
 }
 
+// CTAs per cluster along K: enough CTAs to fill the GPU about three times over when the matrix has
+// few column tiles, while every CTA keeps at least one round of tiles for each of its warps.
+template <int FMT>
+int k_split(int ctas, int KT, int sm_count) {
+  int s = 1;
+  while (s < 8 && ctas * s * 2 <= 3 * sm_count && KT / (s * 2) >= kWarps * tiles_in_flight<FMT>()) {
+    s *= 2;
+  }
+  return s;
+}
+
+template <int FMT, bool A16, int MT>
+cudaError_t launch_mt(float *y, const void *x, const uint8_t *w, int M, int K, int N, int sm_count,
+                      cudaStream_t stream) {
+  const int groups = (M + MT - 1) / MT;
+  const int split  = k_split<FMT>((N / 32) * groups, K / 32, sm_count);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim          = dim3((unsigned) (N / 32), (unsigned) groups, (unsigned) split);
+  cfg.blockDim         = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream           = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id               = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = (unsigned) split;
+  cfg.attrs    = attr;
+  cfg.numAttrs = split > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, tiled_mul_mat_kernel<FMT, A16, MT>, y, x, w, M, K, N);
+}
+
 template <int FMT, bool A16>
 cudaError_t launch_fmt(float *y, const void *x, const uint8_t *w, int M, int K, int N, cudaStream_t stream) {
-  const int mt = M == 1 ? 1 : (M == 2 ? 2 : (M <= 4 ? 4 : 8));
-  dim3      grid((unsigned) (N / 32), (unsigned) ((M + mt - 1) / mt));
-  switch (mt) {
-    case 1: tiled_mul_mat_kernel<FMT, A16, 1><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
-    case 2: tiled_mul_mat_kernel<FMT, A16, 2><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
-    case 4: tiled_mul_mat_kernel<FMT, A16, 4><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
-    default: tiled_mul_mat_kernel<FMT, A16, 8><<<grid, kThreads, 0, stream>>>(y, x, w, M, K, N); break;
+  int dev = 0, sm_count = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) {
+    e = cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
-  return cudaGetLastError();
+  if (e != cudaSuccess) {
+    return e;
+  }
+  if (M == 1) {
+    return launch_mt<FMT, A16, 1>(y, x, w, M, K, N, sm_count, stream);
+  }
+  if (M == 2) {
+    return launch_mt<FMT, A16, 2>(y, x, w, M, K, N, sm_count, stream);
+  }
+  if (M <= 4) {
+    return launch_mt<FMT, A16, 4>(y, x, w, M, K, N, sm_count, stream);
+  }
+  return launch_mt<FMT, A16, 8>(y, x, w, M, K, N, sm_count, stream);
 }
 
 template <int FMT>
