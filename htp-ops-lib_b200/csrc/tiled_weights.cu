@@ -144,19 +144,19 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
     for (int sb = 0; sb < 4; ++sb) {
       const int   k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
       const float d  = __half2float(t.d[sb]);
-      float       we[4], wo[4];  // k even / k odd value of column i, scale applied
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t w = (i < 2 ? t.q[sb].x : t.q[sb].y) >> (16 * (i & 1));
-        we[i]            = (float) (int8_t) (w & 0xFFu) * d;
-        wo[i]            = (float) (int8_t) ((w >> 8) & 0xFFu) * d;
-      }
+      // bytes {k even, k odd} of columns 0, 1 (q.x) and 2, 3 (q.y) -> exact fp16 pairs -> fp32
+      uint32_t hx[2], hy[2];
+      q8_0_unpack_word(t.q[sb].x, hx);
+      q8_0_unpack_word(t.q[sb].y, hy);
+      const float2 wv[4] = { __half22float2(u32_as_h2(hx[0])), __half22float2(u32_as_h2(hx[1])),
+                             __half22float2(u32_as_h2(hy[0])), __half22float2(u32_as_h2(hy[1])) };
 #pragma unroll
       for (int mm = 0; mm < MT; ++mm) {
-        const float2 a = ld_act2<A16>(x, xrow[mm] + k0);
+        float2 a = ld_act2<A16>(x, xrow[mm] + k0);
+        a.x *= d, a.y *= d;  // the scale goes onto the two activations, not onto the eight weights
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          acc[mm][i] = fmaf(a.x, we[i], fmaf(a.y, wo[i], acc[mm][i]));
+          acc[mm][i] = fmaf(a.x, wv[i].x, fmaf(a.y, wv[i].y, acc[mm][i]));
         }
       }
     }
@@ -169,7 +169,7 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
       const __half2 p = u32_as_h2(word_of(t.d, v));
       d[v]            = hi ? __high2float(p) : __low2float(p);
     }
-    float wv[4][8];  // [column][k-row], scale applied
+    float wv[4][8];  // [column][k-row], integer values; the scales go onto the activations
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t w = word_of(t.q, i);
@@ -181,27 +181,29 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
         q4_0_unpack_word(w, h);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          const float2 p = __half22float2(u32_as_h2(h[v]));
-          wv[i][2 * v]     = p.x * d[v];
-          wv[i][2 * v + 1] = p.y * d[v];
+          const float2 p   = __half22float2(u32_as_h2(h[v]));
+          wv[i][2 * v]     = p.x;
+          wv[i][2 * v + 1] = p.y;
         }
       } else {
-        const uint32_t lo = iq4nl_lookup4(gather_nibbles(w & 0x0F0F0F0Fu));         // k-rows 0 2 1 3
-        const uint32_t up = iq4nl_lookup4(gather_nibbles((w >> 4) & 0x0F0F0F0Fu));  // k-rows 4 6 5 7
-        wv[i][0] = (float) (int8_t) (lo & 0xFFu) * d[0];
-        wv[i][2] = (float) (int8_t) ((lo >> 8) & 0xFFu) * d[1];
-        wv[i][1] = (float) (int8_t) ((lo >> 16) & 0xFFu) * d[0];
-        wv[i][3] = (float) (int8_t) (lo >> 24) * d[1];
-        wv[i][4] = (float) (int8_t) (up & 0xFFu) * d[2];
-        wv[i][6] = (float) (int8_t) ((up >> 8) & 0xFFu) * d[3];
-        wv[i][5] = (float) (int8_t) ((up >> 16) & 0xFFu) * d[2];
-        wv[i][7] = (float) (int8_t) (up >> 24) * d[3];
+        // table bytes of k-rows (0 2 1 3) and (4 6 5 7), then signed bytes -> exact fp16 pairs
+        uint32_t hl[2], hu[2];
+        q8_0_unpack_word(iq4nl_lookup4(gather_nibbles(w & 0x0F0F0F0Fu)), hl);         // {0, 2} {1, 3}
+        q8_0_unpack_word(iq4nl_lookup4(gather_nibbles((w >> 4) & 0x0F0F0F0Fu)), hu);  // {4, 6} {5, 7}
+        const float2 p0 = __half22float2(u32_as_h2(hl[0])), p1 = __half22float2(u32_as_h2(hl[1]));
+        const float2 p2 = __half22float2(u32_as_h2(hu[0])), p3 = __half22float2(u32_as_h2(hu[1]));
+        wv[i][0] = p0.x, wv[i][2] = p0.y, wv[i][1] = p1.x, wv[i][3] = p1.y;
+        wv[i][4] = p2.x, wv[i][6] = p2.y, wv[i][5] = p3.x, wv[i][7] = p3.y;
       }
     }
 #pragma unroll
     for (int mm = 0; mm < MT; ++mm) {
       float a[8];
       ld_act8<A16>(x, xrow[mm] + k0, a);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        a[r] *= d[r >> 1];
+      }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float s = acc[mm][i];
@@ -216,10 +218,14 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
 }
 
 // Tiles a warp fetches before it starts on their arithmetic: enough bytes in flight per warp
-// (2 KB) whatever the tile size.
+// (2 KB) whatever the tile size.  HTP_TILE_F16_INFLIGHT is a build-time knob for the fp16 format
+// (each further tile costs 16 registers per thread).
+#ifndef HTP_TILE_F16_INFLIGHT
+#define HTP_TILE_F16_INFLIGHT 1
+#endif
 template <int FMT>
 __host__ __device__ constexpr int tiles_in_flight() {
-  return FMT == kTileF16 ? 1 : (FMT == kTileQ8 ? 2 : 4);
+  return FMT == kTileF16 ? HTP_TILE_F16_INFLIGHT : (FMT == kTileQ8 ? 2 : 4);
 }
 
 // grid = (N / 32, token groups, S).  S > 1: the launch is made of clusters of S CTAs along z that
