@@ -77,6 +77,16 @@ __device__ __forceinline__ uint32_t gather_nibbles(uint32_t x) {
   return (y | (y >> 8)) & 0xFFFFu;
 }
 
+// 2^23 + byte j of x as an fp32 number: the byte lands in the low mantissa bits of 0x4B000000
+// (2^23, whose unit in the last place is 1).  Subtracting 2^23 (+ the offset of the encoding) is
+// exact.  One byte permute and one fp32 add on the full-rate pipes; an integer-to-float or
+// half-to-float conversion instruction runs at a quarter of that rate, and with one conversion per
+// weight that pipe, not HBM, set the pace of the 4- and 8-bit formats (ncu: 0.40 / 0.72 of the
+// copy bandwidth).
+__device__ __forceinline__ float biased_byte(uint32_t x, int j) {
+  return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u | (uint32_t) j));
+}
+
 // Raw bytes one lane holds of one tile, per format.
 template <int FMT>
 struct LaneTile;
@@ -144,12 +154,13 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
     for (int sb = 0; sb < 4; ++sb) {
       const int   k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
       const float d  = __half2float(t.d[sb]);
-      // bytes {k even, k odd} of columns 0, 1 (q.x) and 2, 3 (q.y) -> exact fp16 pairs -> fp32
-      uint32_t hx[2], hy[2];
-      q8_0_unpack_word(t.q[sb].x, hx);
-      q8_0_unpack_word(t.q[sb].y, hy);
-      const float2 wv[4] = { __half22float2(u32_as_h2(hx[0])), __half22float2(u32_as_h2(hx[1])),
-                             __half22float2(u32_as_h2(hy[0])), __half22float2(u32_as_h2(hy[1])) };
+      // bytes {k even, k odd} of columns 0, 1 (q.x) and 2, 3 (q.y); byte + 128 is unsigned
+      const uint32_t ux = t.q[sb].x ^ 0x80808080u, uy = t.q[sb].y ^ 0x80808080u;
+      constexpr float kBias = 8388608.f + 128.f;
+      const float2 wv[4] = { make_float2(biased_byte(ux, 0) - kBias, biased_byte(ux, 1) - kBias),
+                             make_float2(biased_byte(ux, 2) - kBias, biased_byte(ux, 3) - kBias),
+                             make_float2(biased_byte(uy, 0) - kBias, biased_byte(uy, 1) - kBias),
+                             make_float2(biased_byte(uy, 2) - kBias, biased_byte(uy, 3) - kBias) };
 #pragma unroll
       for (int mm = 0; mm < MT; ++mm) {
         float2 a = ld_act2<A16>(x, xrow[mm] + k0);
@@ -173,28 +184,18 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t w = word_of(t.q, i);
-      if constexpr (FMT == kTileQ4) {
-        // bytes B0..B3 of the word: k-rows (0, 4) (2, 6) (1, 5) (3, 7) as (low, high) nibbles;
-        // the unpack returns pairs {lo B0, lo B2} {lo B1, lo B3} {hi B0, hi B2} {hi B1, hi B3},
-        // which is k-row order 0..7.
-        uint32_t h[4];
-        q4_0_unpack_word(w, h);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const float2 p   = __half22float2(u32_as_h2(h[v]));
-          wv[i][2 * v]     = p.x;
-          wv[i][2 * v + 1] = p.y;
-        }
-      } else {
-        // table bytes of k-rows (0 2 1 3) and (4 6 5 7), then signed bytes -> exact fp16 pairs
-        uint32_t hl[2], hu[2];
-        q8_0_unpack_word(iq4nl_lookup4(gather_nibbles(w & 0x0F0F0F0Fu)), hl);         // {0, 2} {1, 3}
-        q8_0_unpack_word(iq4nl_lookup4(gather_nibbles((w >> 4) & 0x0F0F0F0Fu)), hu);  // {4, 6} {5, 7}
-        const float2 p0 = __half22float2(u32_as_h2(hl[0])), p1 = __half22float2(u32_as_h2(hl[1]));
-        const float2 p2 = __half22float2(u32_as_h2(hu[0])), p3 = __half22float2(u32_as_h2(hu[1]));
-        wv[i][0] = p0.x, wv[i][2] = p0.y, wv[i][1] = p1.x, wv[i][3] = p1.y;
-        wv[i][4] = p2.x, wv[i][6] = p2.y, wv[i][5] = p3.x, wv[i][7] = p3.y;
+      // bytes B0..B3 of the word hold k-rows (0, 4) (2, 6) (1, 5) (3, 7) as (low, high) nibbles
+      uint32_t lo = w & 0x0F0F0F0Fu, up = (w >> 4) & 0x0F0F0F0Fu;  // k-rows 0 2 1 3 / 4 6 5 7
+      float    bias = 8388608.f + 8.f;                             // value = nibble - 8
+      if constexpr (FMT == kTileIQ4) {
+        lo   = iq4nl_lookup4(gather_nibbles(lo)) ^ 0x80808080u;  // table bytes + 128
+        up   = iq4nl_lookup4(gather_nibbles(up)) ^ 0x80808080u;
+        bias = 8388608.f + 128.f;
       }
+      wv[i][0] = biased_byte(lo, 0) - bias, wv[i][2] = biased_byte(lo, 1) - bias;
+      wv[i][1] = biased_byte(lo, 2) - bias, wv[i][3] = biased_byte(lo, 3) - bias;
+      wv[i][4] = biased_byte(up, 0) - bias, wv[i][6] = biased_byte(up, 1) - bias;
+      wv[i][5] = biased_byte(up, 2) - bias, wv[i][7] = biased_byte(up, 3) - bias;
     }
 #pragma unroll
     for (int mm = 0; mm < MT; ++mm) {
