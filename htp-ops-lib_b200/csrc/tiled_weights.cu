@@ -127,10 +127,13 @@ __device__ __forceinline__ void load_tile(const uint8_t *tile, int lane, LaneTil
   }
 }
 
-// acc[mm][i] += sum over this lane's k-rows of tile `kt` of x[token mm][k] * W[k][4 * (lane % 8) + i].
+// acc[mm][i] += { even k-rows, odd k-rows } of this lane's share of tile `kt`:
+// x[token mm][k] * W[k][4 * (lane % 8) + i].  Weights and activations sit in registers as
+// {k even, k odd} pairs, so every multiply-add is the packed two-lane fp32 instruction of sm_100
+// (fma.rn.f32x2): half the instructions of scalar FMAs; the two halves are added once at the end.
 template <int FMT, bool A16, int MT>
 __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lane, const void *x,
-                                         const size_t (&xrow)[MT], float (&acc)[MT][4]) {
+                                         const size_t (&xrow)[MT], float2 (&acc)[MT][4]) {
   if constexpr (FMT == kTileF16) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -145,74 +148,75 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
         const float2 a = ld_act2<A16>(x, xrow[mm] + k0);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          acc[mm][i] = fmaf(a.x, wv[i].x, fmaf(a.y, wv[i].y, acc[mm][i]));
+          acc[mm][i] = __ffma2_rn(wv[i], a, acc[mm][i]);
         }
       }
     }
   } else if constexpr (FMT == kTileQ8) {
+    const float2 nbias = make_float2(-(8388608.f + 128.f), -(8388608.f + 128.f));
 #pragma unroll
     for (int sb = 0; sb < 4; ++sb) {
-      const int   k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
-      const float d  = __half2float(t.d[sb]);
+      const int    k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
+      const float  d  = __half2float(t.d[sb]);
+      const float2 d2 = make_float2(d, d);
       // bytes {k even, k odd} of columns 0, 1 (q.x) and 2, 3 (q.y); byte + 128 is unsigned
       const uint32_t ux = t.q[sb].x ^ 0x80808080u, uy = t.q[sb].y ^ 0x80808080u;
-      constexpr float kBias = 8388608.f + 128.f;
-      const float2 wv[4] = { make_float2(biased_byte(ux, 0) - kBias, biased_byte(ux, 1) - kBias),
-                             make_float2(biased_byte(ux, 2) - kBias, biased_byte(ux, 3) - kBias),
-                             make_float2(biased_byte(uy, 0) - kBias, biased_byte(uy, 1) - kBias),
-                             make_float2(biased_byte(uy, 2) - kBias, biased_byte(uy, 3) - kBias) };
+      const float2   wv[4] = { __fadd2_rn(make_float2(biased_byte(ux, 0), biased_byte(ux, 1)), nbias),
+                               __fadd2_rn(make_float2(biased_byte(ux, 2), biased_byte(ux, 3)), nbias),
+                               __fadd2_rn(make_float2(biased_byte(uy, 0), biased_byte(uy, 1)), nbias),
+                               __fadd2_rn(make_float2(biased_byte(uy, 2), biased_byte(uy, 3)), nbias) };
 #pragma unroll
       for (int mm = 0; mm < MT; ++mm) {
-        float2 a = ld_act2<A16>(x, xrow[mm] + k0);
-        a.x *= d, a.y *= d;  // the scale goes onto the two activations, not onto the eight weights
+        // the scale goes onto the two activations, not onto the eight weights
+        const float2 a = __fmul2_rn(ld_act2<A16>(x, xrow[mm] + k0), d2);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          acc[mm][i] = fmaf(a.x, wv[i].x, fmaf(a.y, wv[i].y, acc[mm][i]));
+          acc[mm][i] = __ffma2_rn(wv[i], a, acc[mm][i]);
         }
       }
     }
   } else {
     const int  k0 = kt * 32 + (lane >> 3) * 8;
     const bool hi = (lane & 7) >= 4;  // columns 16..31 use the odd scales
-    float      d[4];                  // scale of k-rows 2v, 2v+1
+    float2     d2[4];                 // scale of k-rows 2v, 2v+1, twice
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       const __half2 p = u32_as_h2(word_of(t.d, v));
-      d[v]            = hi ? __high2float(p) : __low2float(p);
+      const float   d = hi ? __high2float(p) : __low2float(p);
+      d2[v]           = make_float2(d, d);
     }
-    float wv[4][8];  // [column][k-row], integer values; the scales go onto the activations
+    const float  bias  = FMT == kTileIQ4 ? 8388608.f + 128.f : 8388608.f + 8.f;  // value = nibble - 8 / table byte
+    const float2 nbias = make_float2(-bias, -bias);
+    float2       wv[4][4];  // [column][k-row pair] = {row 2v, row 2v + 1}, integer values
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t w = word_of(t.q, i);
       // bytes B0..B3 of the word hold k-rows (0, 4) (2, 6) (1, 5) (3, 7) as (low, high) nibbles
       uint32_t lo = w & 0x0F0F0F0Fu, up = (w >> 4) & 0x0F0F0F0Fu;  // k-rows 0 2 1 3 / 4 6 5 7
-      float    bias = 8388608.f + 8.f;                             // value = nibble - 8
       if constexpr (FMT == kTileIQ4) {
-        lo   = iq4nl_lookup4(gather_nibbles(lo)) ^ 0x80808080u;  // table bytes + 128
-        up   = iq4nl_lookup4(gather_nibbles(up)) ^ 0x80808080u;
-        bias = 8388608.f + 128.f;
+        lo = iq4nl_lookup4(gather_nibbles(lo)) ^ 0x80808080u;  // table bytes + 128
+        up = iq4nl_lookup4(gather_nibbles(up)) ^ 0x80808080u;
       }
-      wv[i][0] = biased_byte(lo, 0) - bias, wv[i][2] = biased_byte(lo, 1) - bias;
-      wv[i][1] = biased_byte(lo, 2) - bias, wv[i][3] = biased_byte(lo, 3) - bias;
-      wv[i][4] = biased_byte(up, 0) - bias, wv[i][6] = biased_byte(up, 1) - bias;
-      wv[i][5] = biased_byte(up, 2) - bias, wv[i][7] = biased_byte(up, 3) - bias;
+      wv[i][0] = __fadd2_rn(make_float2(biased_byte(lo, 0), biased_byte(lo, 2)), nbias);
+      wv[i][1] = __fadd2_rn(make_float2(biased_byte(lo, 1), biased_byte(lo, 3)), nbias);
+      wv[i][2] = __fadd2_rn(make_float2(biased_byte(up, 0), biased_byte(up, 2)), nbias);
+      wv[i][3] = __fadd2_rn(make_float2(biased_byte(up, 1), biased_byte(up, 3)), nbias);
     }
 #pragma unroll
     for (int mm = 0; mm < MT; ++mm) {
       float a[8];
       ld_act8<A16>(x, xrow[mm] + k0, a);
+      float2 a2[4];
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        a[r] *= d[r >> 1];
+      for (int v = 0; v < 4; ++v) {
+        a2[v] = __fmul2_rn(make_float2(a[2 * v], a[2 * v + 1]), d2[v]);
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float s = acc[mm][i];
 #pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          s = fmaf(a[r], wv[i][r], s);
+        for (int v = 0; v < 4; ++v) {
+          acc[mm][i] = __ffma2_rn(wv[i][v], a2[v], acc[mm][i]);
         }
-        acc[mm][i] = s;
       }
     }
   }
@@ -257,12 +261,12 @@ __global__ void __launch_bounds__(kThreads)
     const int tok = m0 + mm < M ? m0 + mm : M - 1;
     xrow[mm]      = (size_t) tok * (size_t) K;
   }
-  float acc[MT][4];
+  float2 acc[MT][4];  // {sum over even k-rows, sum over odd k-rows}
 #pragma unroll
   for (int mm = 0; mm < MT; ++mm) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      acc[mm][i] = 0.f;
+      acc[mm][i] = make_float2(0.f, 0.f);
     }
   }
 
@@ -287,7 +291,7 @@ __global__ void __launch_bounds__(kThreads)
   for (int mm = 0; mm < MT; ++mm) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      float v = acc[mm][i];
+      float v = acc[mm][i].x + acc[mm][i].y;
       v += __shfl_xor_sync(0xFFFFFFFFu, v, 8);
       v += __shfl_xor_sync(0xFFFFFFFFu, v, 16);
       if (lane < 8) {
@@ -297,7 +301,7 @@ __global__ void __launch_bounds__(kThreads)
   }
   __syncthreads();
   float s = 0.f;
-  if (threadIdx.x < MT * 32) {  // MT * 32 <= 256 < kThreads: one output per thread
+  if (threadIdx.x < MT * 32) {  // MT * 32 <= 128 < kThreads: one output per thread
     const int mm = threadIdx.x >> 5, c = threadIdx.x & 31;
 #pragma unroll
     for (int wi = 0; wi < kWarps; ++wi) {
@@ -374,10 +378,7 @@ cudaError_t launch_fmt(float *y, const void *x, const uint8_t *w, int M, int K, 
   if (M == 2) {
     return launch_mt<FMT, A16, 2>(y, x, w, M, K, N, sm_count, stream);
   }
-  if (M <= 4) {
-    return launch_mt<FMT, A16, 4>(y, x, w, M, K, N, sm_count, stream);
-  }
-  return launch_mt<FMT, A16, 8>(y, x, w, M, K, N, sm_count, stream);
+  return launch_mt<FMT, A16, 4>(y, x, w, M, K, N, sm_count, stream);
 }
 
 template <int FMT>
@@ -389,7 +390,7 @@ cudaError_t launch_act(float *y, const void *x, const uint8_t *w, int M, int K, 
 
 cudaError_t tiled_mul_mat_launch(float *y, const void *x, const uint8_t *w, int M, int K, int N, int fmt, bool a16,
                                  cudaStream_t stream) {
-  if (M <= 0 || K <= 0 || N <= 0 || K % 32 != 0 || N % 32 != 0 || (M + 7) / 8 > 65535) {
+  if (M <= 0 || K <= 0 || N <= 0 || K % 32 != 0 || N % 32 != 0 || (M + 3) / 4 > 65535) {
     return cudaErrorInvalidValue;
   }
   switch (fmt) {

@@ -19,7 +19,7 @@ __host__ __device__ constexpr int tile_bytes(int fmt) {
 }
 
 // y[M][N] (fp32) = x[M][K] . W, W[k][n] read from tile order.  K % 32 == 0, N % 32 == 0, x and w
-// 16-byte aligned.  Any M: tokens are taken eight at a time (grid.y), each group re-reading W.
+// 16-byte aligned.  Any M: tokens are taken four at a time (grid.y), each group re-reading W.
 cudaError_t tiled_mul_mat_launch(float *y, const void *x, const uint8_t *w, int M, int K, int N, int fmt, bool a16,
                                  cudaStream_t stream);
 
