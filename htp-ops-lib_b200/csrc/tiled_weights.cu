@@ -232,9 +232,17 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
 #ifndef HTP_TILE_Q8_INFLIGHT
 #define HTP_TILE_Q8_INFLIGHT 2
 #endif
+#ifndef HTP_TILE_Q4_INFLIGHT
+#define HTP_TILE_Q4_INFLIGHT 4
+#endif
+#ifndef HTP_TILE_IQ4_INFLIGHT
+#define HTP_TILE_IQ4_INFLIGHT 4
+#endif
 template <int FMT>
 __host__ __device__ constexpr int tiles_in_flight() {
-  return FMT == kTileF16 ? HTP_TILE_F16_INFLIGHT : (FMT == kTileQ8 ? HTP_TILE_Q8_INFLIGHT : 4);
+  return FMT == kTileF16 ? HTP_TILE_F16_INFLIGHT
+                         : (FMT == kTileQ8 ? HTP_TILE_Q8_INFLIGHT
+                                           : (FMT == kTileQ4 ? HTP_TILE_Q4_INFLIGHT : HTP_TILE_IQ4_INFLIGHT));
 }
 
 // grid = (N / 32, token groups, S).  S > 1: the launch is made of clusters of S CTAs along z that
