@@ -458,7 +458,26 @@ int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activ
 }
 
 int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream) {
-  const int wt = wt_index(weight_type);
+  const int wt   = wt_index(weight_type);
+  const int tfmt = tile_fmt_index(weight_type);
+  if (tfmt > kTileF16) {
+    // permuted super-blocks: a "block" is a scale group (32 slots), eight per super-block
+    if (!weight || !s || !t || n_blocks < 0 || n_blocks % 8 != 0 || (reinterpret_cast<uintptr_t>(weight) & 15u)) {
+      return -1;
+    }
+    if (!current_device_ctx()) {
+      return -2;
+    }
+    if (tiled_group_sums_launch(static_cast<const uint8_t *>(weight), s, t, n_blocks / 8, tfmt,
+                                static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    if (n_blocks > 0) {
+      count_launch();
+    }
+    return 0;
+  }
   if (!weight || !s || !t || n_blocks < 0 || wt < 0 || (reinterpret_cast<uintptr_t>(weight) & 1u)) {
     return -1;
   }

@@ -87,6 +87,35 @@ __device__ __forceinline__ float biased_byte(uint32_t x, int j) {
   return __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540u | (uint32_t) j));
 }
 
+// Eight consecutive slots of a Q8_0 super-block (one row pair, four columns) -> out[i] =
+// {k even, k odd} of column i as exact fp32 integers.  Shared by the matmul and the integer probe.
+__device__ __forceinline__ void decode_byte_pairs(uint2 q, float2 (&out)[4]) {
+  const float2   nbias = make_float2(-(8388608.f + 128.f), -(8388608.f + 128.f));
+  const uint32_t ux = q.x ^ 0x80808080u, uy = q.y ^ 0x80808080u;  // byte + 128 is unsigned
+  out[0] = __fadd2_rn(make_float2(biased_byte(ux, 0), biased_byte(ux, 1)), nbias);
+  out[1] = __fadd2_rn(make_float2(biased_byte(ux, 2), biased_byte(ux, 3)), nbias);
+  out[2] = __fadd2_rn(make_float2(biased_byte(uy, 0), biased_byte(uy, 1)), nbias);
+  out[3] = __fadd2_rn(make_float2(biased_byte(uy, 2), biased_byte(uy, 3)), nbias);
+}
+
+// One quant word of a 4-bit super-block (quants[4c .. 4c+3]: column c, all eight k-rows) -> out[v] =
+// {k-row 2v, k-row 2v + 1} as exact fp32 integers.  Bytes B0..B3 of the word hold k-rows (0, 4)
+// (2, 6) (1, 5) (3, 7) as (low, high) nibbles.  Shared by the matmul and the integer probe.
+template <int FMT>
+__device__ __forceinline__ void decode_nibble_word(uint32_t w, float2 (&out)[4]) {
+  uint32_t lo = w & 0x0F0F0F0Fu, up = (w >> 4) & 0x0F0F0F0Fu;  // k-rows 0 2 1 3 / 4 6 5 7
+  if constexpr (FMT == kTileIQ4) {
+    lo = iq4nl_lookup4(gather_nibbles(lo)) ^ 0x80808080u;  // table bytes + 128
+    up = iq4nl_lookup4(gather_nibbles(up)) ^ 0x80808080u;
+  }
+  const float  bias  = FMT == kTileIQ4 ? 8388608.f + 128.f : 8388608.f + 8.f;  // value = table byte / nibble - 8
+  const float2 nbias = make_float2(-bias, -bias);
+  out[0] = __fadd2_rn(make_float2(biased_byte(lo, 0), biased_byte(lo, 2)), nbias);
+  out[1] = __fadd2_rn(make_float2(biased_byte(lo, 1), biased_byte(lo, 3)), nbias);
+  out[2] = __fadd2_rn(make_float2(biased_byte(up, 0), biased_byte(up, 2)), nbias);
+  out[3] = __fadd2_rn(make_float2(biased_byte(up, 1), biased_byte(up, 3)), nbias);
+}
+
 // Raw bytes one lane holds of one tile, per format.
 template <int FMT>
 struct LaneTile;
@@ -153,18 +182,13 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
       }
     }
   } else if constexpr (FMT == kTileQ8) {
-    const float2 nbias = make_float2(-(8388608.f + 128.f), -(8388608.f + 128.f));
 #pragma unroll
     for (int sb = 0; sb < 4; ++sb) {
       const int    k0 = kt * 32 + sb * 8 + 2 * (lane >> 3);
       const float  d  = __half2float(t.d[sb]);
       const float2 d2 = make_float2(d, d);
-      // bytes {k even, k odd} of columns 0, 1 (q.x) and 2, 3 (q.y); byte + 128 is unsigned
-      const uint32_t ux = t.q[sb].x ^ 0x80808080u, uy = t.q[sb].y ^ 0x80808080u;
-      const float2   wv[4] = { __fadd2_rn(make_float2(biased_byte(ux, 0), biased_byte(ux, 1)), nbias),
-                               __fadd2_rn(make_float2(biased_byte(ux, 2), biased_byte(ux, 3)), nbias),
-                               __fadd2_rn(make_float2(biased_byte(uy, 0), biased_byte(uy, 1)), nbias),
-                               __fadd2_rn(make_float2(biased_byte(uy, 2), biased_byte(uy, 3)), nbias) };
+      float2       wv[4];  // {k even, k odd} of columns 0..3
+      decode_byte_pairs(t.q[sb], wv);
 #pragma unroll
       for (int mm = 0; mm < MT; ++mm) {
         // the scale goes onto the two activations, not onto the eight weights
@@ -185,22 +209,10 @@ __device__ __forceinline__ void fma_tile(const LaneTile<FMT> &t, int kt, int lan
       const float   d = hi ? __high2float(p) : __low2float(p);
       d2[v]           = make_float2(d, d);
     }
-    const float  bias  = FMT == kTileIQ4 ? 8388608.f + 128.f : 8388608.f + 8.f;  // value = nibble - 8 / table byte
-    const float2 nbias = make_float2(-bias, -bias);
-    float2       wv[4][4];  // [column][k-row pair] = {row 2v, row 2v + 1}, integer values
+    float2 wv[4][4];  // [column][k-row pair] = {row 2v, row 2v + 1}, integer values
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t w = word_of(t.q, i);
-      // bytes B0..B3 of the word hold k-rows (0, 4) (2, 6) (1, 5) (3, 7) as (low, high) nibbles
-      uint32_t lo = w & 0x0F0F0F0Fu, up = (w >> 4) & 0x0F0F0F0Fu;  // k-rows 0 2 1 3 / 4 6 5 7
-      if constexpr (FMT == kTileIQ4) {
-        lo = iq4nl_lookup4(gather_nibbles(lo)) ^ 0x80808080u;  // table bytes + 128
-        up = iq4nl_lookup4(gather_nibbles(up)) ^ 0x80808080u;
-      }
-      wv[i][0] = __fadd2_rn(make_float2(biased_byte(lo, 0), biased_byte(lo, 2)), nbias);
-      wv[i][1] = __fadd2_rn(make_float2(biased_byte(lo, 1), biased_byte(lo, 3)), nbias);
-      wv[i][2] = __fadd2_rn(make_float2(biased_byte(up, 0), biased_byte(up, 2)), nbias);
-      wv[i][3] = __fadd2_rn(make_float2(biased_byte(up, 1), biased_byte(up, 3)), nbias);
+      decode_nibble_word<FMT>(word_of(t.q, i), wv[i]);
     }
 #pragma unroll
     for (int mm = 0; mm < MT; ++mm) {
@@ -390,6 +402,61 @@ cudaError_t launch_fmt(float *y, const void *x, const uint8_t *w, int M, int K, 
   return launch_mt<FMT, A16, 4>(y, x, w, M, K, N, sm_count, stream);
 }
 
+// Integer probe of the super-block decode: for every scale group (32 consecutive slots of a
+// super-block: 2 k-rows x 16 columns) S = sum_j q_j and T = sum_j (j + 1) q_j over its slots j in
+// slot order, through the decode routines the matmul uses.  One warp per super-block.
+template <int FMT>
+__global__ void __launch_bounds__(256)
+    tiled_group_sums_kernel(const uint8_t *__restrict__ w, int32_t *__restrict__ s, int32_t *__restrict__ t,
+                            long long n_sb) {
+  const long long sb   = (long long) blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int       lane = threadIdx.x & 31;
+  if (sb >= n_sb) {  // warp-uniform
+    return;
+  }
+  const uint8_t *blk = w + sb * (tile_bytes(FMT) / 4);
+  float2         v[4];
+  if constexpr (FMT == kTileQ8) {
+    // slots 8 * lane .. +7: group lane / 4, first index in the group (8 * lane) % 32
+    decode_byte_pairs(*reinterpret_cast<const uint2 *>(blk + 16 + lane * 8), v);
+    int S = 0, T = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int a = __float2int_rn(v[i].x), b = __float2int_rn(v[i].y), j = ((8 * lane) & 31) + 2 * i;
+      S += a + b;
+      T += (j + 1) * a + (j + 2) * b;
+    }
+#pragma unroll
+    for (int m = 1; m <= 2; m <<= 1) {
+      S += __shfl_xor_sync(0xFFFFFFFFu, S, m);
+      T += __shfl_xor_sync(0xFFFFFFFFu, T, m);
+    }
+    if ((lane & 3) == 0) {
+      s[sb * 8 + (lane >> 2)] = S;
+      t[sb * 8 + (lane >> 2)] = T;
+    }
+  } else {
+    // word `lane` = column `lane`, k-row pairs 0..3: slot 64 * pair + 2 * lane + parity,
+    // group 2 * pair + lane / 16, index in the group (2 * lane) % 32 + parity
+    decode_nibble_word<FMT>(*reinterpret_cast<const uint32_t *>(blk + 16 + lane * 4), v);
+    const int j = (2 * lane) & 31;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int a = __float2int_rn(v[p].x), b = __float2int_rn(v[p].y);
+      int       S = a + b, T = (j + 1) * a + (j + 2) * b;
+#pragma unroll
+      for (int m = 1; m <= 8; m <<= 1) {
+        S += __shfl_xor_sync(0xFFFFFFFFu, S, m);
+        T += __shfl_xor_sync(0xFFFFFFFFu, T, m);
+      }
+      if ((lane & 15) == 0) {
+        s[sb * 8 + 2 * p + (lane >> 4)] = S;
+        t[sb * 8 + 2 * p + (lane >> 4)] = T;
+      }
+    }
+  }
+}
+
 template <int FMT>
 cudaError_t launch_act(float *y, const void *x, const uint8_t *w, int M, int K, int N, bool a16, cudaStream_t stream) {
   return a16 ? launch_fmt<FMT, true>(y, x, w, M, K, N, stream) : launch_fmt<FMT, false>(y, x, w, M, K, N, stream);
@@ -409,6 +476,21 @@ cudaError_t tiled_mul_mat_launch(float *y, const void *x, const uint8_t *w, int 
     case kTileIQ4: return launch_act<kTileIQ4>(y, x, w, M, K, N, a16, stream);
     default: return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t tiled_group_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long long n_super_blocks, int fmt,
+                                    cudaStream_t stream) {
+  if (n_super_blocks <= 0) {
+    return n_super_blocks == 0 ? cudaSuccess : cudaErrorInvalidValue;
+  }
+  const unsigned grid = (unsigned) ((n_super_blocks + 7) / 8);
+  switch (fmt) {
+    case kTileQ4: tiled_group_sums_kernel<kTileQ4><<<grid, 256, 0, stream>>>(w, s, t, n_super_blocks); break;
+    case kTileQ8: tiled_group_sums_kernel<kTileQ8><<<grid, 256, 0, stream>>>(w, s, t, n_super_blocks); break;
+    case kTileIQ4: tiled_group_sums_kernel<kTileIQ4><<<grid, 256, 0, stream>>>(w, s, t, n_super_blocks); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
 }
 
 }  // namespace htp

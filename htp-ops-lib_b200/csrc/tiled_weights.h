@@ -23,4 +23,10 @@ __host__ __device__ constexpr int tile_bytes(int fmt) {
 cudaError_t tiled_mul_mat_launch(float *y, const void *x, const uint8_t *w, int M, int K, int N, int fmt, bool a16,
                                  cudaStream_t stream);
 
+// Integer probe of the super-block decode (formats kTileQ4, kTileQ8, kTileIQ4): per scale group g of
+// every super-block (8 groups of 32 consecutive slots each) s[8 * sb + g] = sum_j q_j and
+// t[8 * sb + g] = sum_j (j + 1) q_j, j the slot's index within its group.
+cudaError_t tiled_group_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long long n_super_blocks, int fmt,
+                                    cudaStream_t stream);
+
 }  // namespace htp

@@ -92,7 +92,10 @@ int htp_b200_mul_mat_static_scratch(void *dst, const void *activation, const voi
  * Integer probe of the block unpack: for each of n_blocks consecutive blocks writes
  * s[b] = sum_i v_i and t[b] = sum_i (i + 1) * v_i (int32), v_i the block's 32 integer values in
  * element order.  No counterpart in the reference (it has no integer path); exists so the
- * unpack the matmul kernels use can be checked bit-exactly.
+ * unpack the matmul kernels use can be checked bit-exactly.  For the permuted super-blocks
+ * (weight_type HTP_B200_WT_PERMUTED | type) a "block" is a scale group - 32 consecutive slots of a
+ * super-block, eight per super-block, element order = slot order; n_blocks must be a multiple of 8
+ * and `weight` 16-byte aligned.
  */
 int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream);
 

@@ -465,6 +465,39 @@ int htp_oracle_tiled_dequantize(const uint8_t *w, float *out, int64_t k, int64_t
   return 0;
 }
 
+/* Integer sums per scale group of the permuted super-blocks (fmt 0x102, 0x108, 0x114): group g of
+ * super-block sb covers its slots t = 32 g .. 32 g + 31; S = sum_j q_j, T = sum_j (j + 1) q_j with
+ * j = t % 32 and q the slot's integer value read exactly as in htp_oracle_tiled_dequantize. */
+int htp_oracle_tiled_group_sums(const uint8_t *w, int32_t *s_out, int32_t *t_out, int64_t n_super_blocks, int fmt) {
+  if (fmt != 0x102 && fmt != 0x108 && fmt != 0x114) {
+    return -1;
+  }
+  const int sbb = tiled_tile_bytes(fmt) / 4;
+  for (int64_t sb = 0; sb < n_super_blocks; ++sb) {
+    const uint8_t *blk = w + sb * sbb;
+    for (int g = 0; g < 8; ++g) {
+      int32_t S = 0, T = 0;
+      for (int j = 0; j < 32; ++j) {
+        const int t = 32 * g + j;
+        int       q;
+        if (fmt == 0x108) {
+          q = (int8_t) blk[16 + t];
+        } else {
+          const int     v = t / 64, sl = t % 64;
+          const uint8_t b   = blk[16 + 2 * sl + (v & 1)];
+          const int     nib = v < 2 ? (b & 0x0F) : (b >> 4);
+          q = fmt == 0x102 ? nib - 8 : kIq4nlValues[nib];
+        }
+        S += q;
+        T += (j + 1) * q;
+      }
+      s_out[sb * 8 + g] = S;
+      t_out[sb * 8 + g] = T;
+    }
+  }
+  return 0;
+}
+
 struct mmd_ctx {
   const float *wd;
   const void  *act;

@@ -61,6 +61,8 @@ def load(path: str | os.PathLike | None = None):
     lib.htp_oracle_mul_mat_f32.argtypes = [vp, vp, i32, vp, i64, i64, i64, i32, i32]
     lib.htp_oracle_tiled_dequantize.restype = i32
     lib.htp_oracle_tiled_dequantize.argtypes = [vp, vp, i64, i64, i32]
+    lib.htp_oracle_tiled_group_sums.restype = i32
+    lib.htp_oracle_tiled_group_sums.argtypes = [vp, vp, vp, i64, i32]
     lib.htp_oracle_mul_mat_dense_f64.restype = i32
     lib.htp_oracle_mul_mat_dense_f64.argtypes = [vp, vp, vp, i32, vp, i64, i64, i64, i32]
     if path is None:
@@ -141,6 +143,17 @@ def tiled_dequantize(w: np.ndarray, k: int, n: int, fmt: int) -> np.ndarray:
     if load().htp_oracle_tiled_dequantize(_ptr(w), _ptr(out), k, n, fmt) != 0:
         raise ValueError("bad arguments")
     return out
+
+
+def tiled_group_sums(w: np.ndarray, fmt: int) -> tuple[np.ndarray, np.ndarray]:
+    """(S, T) per scale group (32 slots, eight per super-block) of a permuted super-block buffer."""
+    sbb = {0x102: 144, 0x108: 272, 0x114: 144}[fmt]
+    n_sb = w.size // sbb
+    s = np.empty(n_sb * 8, dtype=np.int32)
+    t = np.empty(n_sb * 8, dtype=np.int32)
+    if load().htp_oracle_tiled_group_sums(_ptr(w), _ptr(s), _ptr(t), n_sb, fmt) != 0:
+        raise ValueError("bad arguments")
+    return s, t
 
 
 def tiled_mul_mat_f64(act: np.ndarray, w: np.ndarray, n: int, fmt: int, threads: int = 0, want_absdot: bool = False):

@@ -69,6 +69,26 @@ def test_tile_order_matmul_matches_committed_golden_samples(dev):
         assert np.abs(y[:, -16:] - np.array(want["tail"])).max() <= tol * scale
 
 
+@pytest.mark.parametrize("wtype", [Q4, Q8, IQ4])
+def test_permuted_group_sums_bit_exact(dev, oracle, wtype):
+    """Integer sums per scale group through the decode routines the matmul kernel uses, on random bytes
+    (every nibble / byte value in every position): bit-exact against the oracle."""
+    import torch
+    fmt = PERM | wtype
+    sbb = 272 if wtype == Q8 else 144
+    rng = np.random.default_rng(60 + wtype)
+    buf = rng.integers(0, 256, size=1000 * sbb, dtype=np.uint8)
+    tw = torch.from_numpy(buf).cuda()
+    s = torch.empty(8000, dtype=torch.int32, device="cuda")
+    t = torch.empty(8000, dtype=torch.int32, device="cuda")
+    assert dev.lib.htp_b200_block_sums(tw.data_ptr(), s.data_ptr(), t.data_ptr(), 8000, fmt, None) == 0
+    torch.cuda.synchronize()
+    so, to = oracle.tiled_group_sums(buf, fmt)
+    assert (s.cpu().numpy() == so).all() and (t.cpu().numpy() == to).all()
+    assert dev.lib.htp_b200_block_sums(tw.data_ptr(), s.data_ptr(), t.data_ptr(), 12, fmt, None) == -1  # not whole super-blocks
+    assert dev.lib.htp_b200_block_sums(tw.data_ptr(), s.data_ptr(), t.data_ptr(), 8, 1, None) == -1  # fp16 tiles: no integers
+
+
 def test_w16a32_rpc_named_call_on_the_reference_test_shape(dev, oracle, wl):
     """m = 1, k = 1024, n = 1024, inputs uniform in [0, 1) as in src/host/test.c:281-313; the call is the
     one that test makes (htp_ops_mat_mul_permuted_w16a32 on three mapped buffers)."""

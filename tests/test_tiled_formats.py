@@ -146,3 +146,24 @@ def test_golden_tile_order_cases(name):
     for key in ("head", "tail"):
         assert np.allclose(np.array(g[key]), np.array(want[key]), rtol=1e-12, atol=0)
     assert abs(g["abs_sum"] - want["abs_sum"]) <= 1e-10 * want["abs_sum"]
+
+
+@pytest.mark.parametrize("wtype", [Q4, Q8, IQ4])
+def test_permuted_group_sums_match_numpy(wl, oracle, wtype):
+    """S = sum q and T = sum (j + 1) q per scale group (32 consecutive slots), the integer invariant the GPU
+    decode is held to bit for bit: the C loop against a vectorised count on random bytes."""
+    fmt = PERM | wtype
+    sbb = 272 if wtype == Q8 else 144
+    rng = np.random.default_rng(30 + wtype)
+    buf = rng.integers(0, 256, size=24 * sbb, dtype=np.uint8)
+    s, t = oracle.tiled_group_sums(buf, fmt)
+    sb = buf.reshape(-1, sbb)
+    if wtype == Q8:
+        q = sb[:, 16:].copy().view(np.int8).astype(np.int64).reshape(-1, 8, 32)
+    else:
+        qs = sb[:, 16:].reshape(-1, 64, 2)
+        nib = np.stack([qs[:, :, 0] & 15, qs[:, :, 1] & 15, qs[:, :, 0] >> 4, qs[:, :, 1] >> 4], axis=1)  # [sb][pair][slot]
+        q = (nib.astype(np.int64) - 8 if wtype == Q4 else IQ4_TABLE[nib].astype(np.int64)).reshape(-1, 8, 32)
+    assert (s == q.sum(axis=2).reshape(-1)).all()
+    assert (t == (q * np.arange(1, 33)).sum(axis=2).reshape(-1)).all()
+    assert s.dtype == np.int32 and s.size == 24 * 8
