@@ -116,6 +116,44 @@ def rows_of_rank(n: int, rank: int, world: int) -> tuple[int, int]:
     return sharding.row_range(n, rank, world)
 
 
+def seeded_weight_slab(torch, wl, cfg, dev, rows):
+    """Rows [rows[0], rows[1]) of the configuration's SEEDED weight matrix, packed, in device memory:
+    the fp32 values come from the same PCG64 streams as workloads.make_weight (drawn on the host, one
+    8192-row chunk at a time), the packing runs on the device with the same rule as the numpy packer,
+    so the bytes are the ones the committed fixtures were computed from."""
+    import numpy as np
+    op = cfg.ops[0]
+    r0, r1 = rows
+    row_bytes = (op.k // 32) * wl.BLOCK_BYTES[op.wtype]
+    out = torch.empty((r1 - r0) * row_bytes, dtype=torch.uint8, device=dev)
+    pos = 0
+    for c in range(r0 // wl.ROW_CHUNK, (r1 + wl.ROW_CHUNK - 1) // wl.ROW_CHUNK):
+        c0, c1 = c * wl.ROW_CHUNK, min(op.n, (c + 1) * wl.ROW_CHUNK)
+        w = wl._rng(cfg.seed, 0, 0, 0, c).standard_normal((c1 - c0, op.k), dtype=np.float32) * np.float32(0.02)
+        lo, hi = max(r0, c0) - c0, min(r1, c1) - c0
+        q = wl.quantize_torch(torch.from_numpy(w[lo:hi]).to(dev), op.wtype)
+        out[pos:pos + q.numel()] = q
+        pos += q.numel()
+    return out
+
+
+def golden_fixture(name: str, key: str):
+    p = ROOT / "tests" / "golden" / "golden.json"
+    return json.loads(p.read_text())[name][key]["oracle"] if p.exists() else None
+
+
+def matches_fixture(y, g, tol: float) -> bool:
+    """Logits (numpy [m][n]) against the committed oracle samples: sampled token rows (head and tail
+    columns) and the whole-matrix checksum, relative to the oracle's largest magnitude / absolute sum."""
+    import numpy as np
+    head, tail = np.array(g["head"]), np.array(g["tail"])
+    ys = y[g["rows"]]
+    return bool(np.isfinite(y).all()
+                and np.abs(ys[:, :head.shape[1]] - head).max() <= tol * g["max_abs"]
+                and np.abs(ys[:, -tail.shape[1]:] - tail).max() <= tol * g["max_abs"]
+                and abs(float(y.astype(np.float64).sum()) - g["sum"]) <= tol * g["abs_sum"])
+
+
 def time_region(torch, fn, steps: int, stream) -> float:
     """Milliseconds for `steps` calls of fn, CUDA events on `stream`, synchronised on both sides."""
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -163,6 +201,11 @@ def cpu_baseline(wl, cfg_name: str, m: int, seconds: float = 12.0, sample_rows: 
 
 # ------------------------------------------------------------------------------------------------
 
+def workload_name(world: int) -> str:
+    """config.workload of both arms."""
+    return f"cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1, rows sharded over {world} GPU(s)"
+
+
 def run_reference(args):
     """CPU arm: rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -177,8 +220,10 @@ def run_reference(args):
         "impl": "reference", "metric": "decode_GBps", "value": round(b["gbps"], 3), "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": round(b["seconds_per_sample"] * 1e3, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1 (CPU restatement of the "
-                               "reference's dequantise-then-dot; the reference's HVX/HMX code cannot be built here)"},
+        "config": {"workload": workload_name(args.gpus),
+                   "implementation": "CPU restatement of the reference's dequantise-then-dot (fp32, all host threads); "
+                                     "the reference's own HVX/HMX code cannot be built for a host CPU",
+                   "sample": f"first {b['rows']} of 128256 weight rows per step; GB/s does not depend on the row count"},
         "cpu_baseline": {"value": round(b["gbps"], 3), "unit": "GB/s", "cores": b["cores"], "kind": "port",
                          "sample": f"first {b['rows']} of 128256 weight rows per step, {b['iters']} steps, "
                                    f"{b['build']}"},
@@ -226,8 +271,9 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
     steps = 20 if quick else 100
     run_case("cfg0_q4_0_gemv_4096x4096_m1", wl.CONFIGS["cfg0"], 0, 1, steps)
     run_case("cfg1_q8_0_gemv_11008x4096_m1", wl.CONFIGS["cfg1"], 0, 1, steps)
-    run_case("cfg2_q4_0_prefill_14336x4096_m512", wl.CONFIGS["cfg2"], 0, 512, max(3, steps // 10))
-    run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(3, steps // 10))
+    run_case("cfg2_q4_0_prefill_14336x4096_m512", wl.CONFIGS["cfg2"], 0, 512, max(20, steps // 2))
+    run_case("cfg2_shape_q4_0_prefill_14336x4096_m128", wl.CONFIGS["cfg2"], 0, 128, max(20, steps // 2))
+    run_case("cfg4_q8_0_lm_head_m256", wl.CONFIGS["cfg4"], 0, 256, max(10, steps // 4))
     out["rms_norm_f32_4096x32768"] = measure_rms_norm(torch, lib, peaks, stream_ptr, stream, max(5, steps // 5))
     out.update(measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream, max(5, steps // 5)))
     out.update(measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, max(5, steps // 5)))
@@ -249,7 +295,10 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
         return w.reshape(-1)
 
     for name, wtype, a16, m, k, n in (("q4_0_gemv_65536x4096_m1", wl.TYPE_Q4_0, False, 1, 4096, 65536),
+                                      ("q4_0_gemv_65536x4096_m8", wl.TYPE_Q4_0, False, 8, 4096, 65536),
+                                      ("q8_0_gemv_32768x4096_m8", wl.TYPE_Q8_0, False, 8, 4096, 32768),
                                       ("iq4_nl_gemv_65536x4096_m1", wl.TYPE_IQ4_NL, False, 1, 4096, 65536),
+                                      ("iq4_nl_gemv_65536x4096_m8", wl.TYPE_IQ4_NL, False, 8, 4096, 65536),
                                       ("iq4_nl_prefill_14336x4096_m512", wl.TYPE_IQ4_NL, True, 512, 4096, 14336)):
         op = wl.MatMul(name, wtype, a16, k, n)
         copies = 2 if m <= 8 else 1
@@ -422,9 +471,9 @@ def run_ours(args):
     n_loc = r1 - r0
     slab = wl.weight_bytes(op.wtype, op.k, n_loc)
     copies = max(2, -(-L2_BYTES // slab) + 1)
-    w0 = wl.make_weight_torch(cfg, dev, rows=(r0, r1))
+    w0 = seeded_weight_slab(torch, wl, cfg, dev, (r0, r1))
     ws = [w0] + [w0.clone() for _ in range(copies - 1)]
-    x_host = torch.randn((m, op.k), dtype=torch.float32).to(torch.float16).pin_memory()
+    x_host = torch.from_numpy(wl.make_activation(cfg, m)).pin_memory()  # the configuration's seeded tokens
     x = x_host.to(dev)
     logits = torch.empty((m, op.n), device=dev, dtype=torch.float32)  # every rank ends with all of it
     y_loc = logits[:, r0:r1] if world == 1 else torch.empty((m, n_loc), device=dev, dtype=torch.float32)
@@ -451,6 +500,7 @@ def run_ours(args):
     # cross-rank barrier replaces the all-gather.  Used for the timed step when it is available and
     # reproduces the gathered result bit for bit on every rank; otherwise the NCCL all-gather is.
     step, exchange = step_gather, ("none" if world == 1 else "NCCL all-gather of fp32 logits")
+    fused_logits = None  # this rank's copy of the logits the fused exchange assembles
     if world > 1 and not args.no_fused:
         try:
             import ctypes
@@ -469,14 +519,13 @@ def run_ours(args):
                 epoch = [0]
 
                 def step_fused(i):
-                    # the kernel stores this rank's slice into every rank's logits and then raises its flag
-                    # on every GPU; the wait (a tiny kernel on this stream) returns when all ranks' flags of
-                    # this step are here - no all-gather, no separate barrier
+                    # ONE call: the kernel stores this rank's slice into every rank's logits (16-byte peer
+                    # stores) and raises its flag on every GPU; a small wait kernel behind it returns when
+                    # all ranks' flags of this step are here - no all-gather, no separate barrier
                     epoch[0] += 1
-                    assert lib.htp_b200_mul_mat_multi_dst_signal(arr, world, op.n, r0, x.data_ptr(),
-                                                                 ws[i % copies].data_ptr(), m, op.k, n_loc, op.wtype,
-                                                                 pkg.ACT_F16, farr, epoch[0], sp) == 0
-                    assert lib.htp_b200_wait_flags(symf.data_ptr(), world, epoch[0], sp) == 0
+                    assert lib.htp_b200_mul_mat_gather_step(arr, world, op.n, r0, x.data_ptr(),
+                                                            ws[i % copies].data_ptr(), m, op.k, n_loc, op.wtype,
+                                                            pkg.ACT_F16, farr, symf.data_ptr(), epoch[0], sp) == 0
                 sym.zero_()
                 symf.zero_()
                 torch.cuda.synchronize()
@@ -484,6 +533,8 @@ def run_ours(args):
                 step_gather(0)
                 step_fused(0)
                 torch.cuda.synchronize()
+                hdl.barrier()
+                fused_logits = sym
                 same = torch.tensor([1 if bool((sym == logits).all().item()) else 0], device=dev)
                 dist.all_reduce(same, op=dist.ReduceOp.MIN)
                 faster = False
@@ -493,19 +544,35 @@ def run_ours(args):
                         for i in range(3):
                             f(i)
                     barrier()
-                    tt = torch.tensor([time_region(torch, step_fused, 20, stream),
-                                       time_region(torch, step_gather, 20, stream)], device=dev, dtype=torch.float64)
+                    tt = torch.tensor([time_region(torch, step_fused, 50, stream),
+                                       time_region(torch, step_gather, 50, stream)], device=dev, dtype=torch.float64)
                     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                     faster = float(tt[0]) < float(tt[1])
                     if rank == 0:
-                        sys.stderr.write(f"exchange: fused {float(tt[0]) / 20 * 1e3:.1f} us per step, NCCL all-gather "
-                                         f"{float(tt[1]) / 20 * 1e3:.1f} us per step\n")
+                        sys.stderr.write(f"exchange: fused {float(tt[0]) / 50 * 1e3:.1f} us per step, NCCL all-gather "
+                                         f"{float(tt[1]) / 50 * 1e3:.1f} us per step\n")
                 if faster:
-                    step, exchange = step_fused, ("fused: tile completion stores into every rank's logits (peer memory), completion flags "
-                                      "raised by the last CTA, bounded flag wait on every rank")
+                    step, exchange = step_fused, ("fused: tile completion stores into every rank's logits (16-byte peer "
+                                      "stores), completion flags raised by the last CTA, bounded flag wait on every "
+                                      "rank; one library call per step")
         except Exception as e:  # noqa: BLE001 - symmetric memory is optional plumbing
             sys.stderr.write(f"fused exchange unavailable: {type(e).__name__}: {e}\n")
 
+    # Parity of what is about to be timed: the assembled logits of BOTH exchanges on every rank against
+    # the committed oracle samples of config 4 (seeded weights and tokens), gate 1e-3 as for any fp16
+    # activation result.
+    g1 = golden_fixture("cfg4", "m1")
+    parity = {"decode_m1": None}
+    if g1 is not None:
+        step_gather(0)
+        torch.cuda.synchronize()
+        ok = matches_fixture(logits.cpu().numpy(), g1, 1e-3)
+        if fused_logits is not None:
+            ok = ok and matches_fixture(fused_logits.cpu().numpy(), g1, 1e-3)
+        t = torch.tensor([1 if ok else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        parity["decode_m1"] = bool(int(t[0]))
     for i in range(warm):
         step(i)
     barrier()
@@ -569,7 +636,8 @@ def run_ours(args):
                     for f in fw]
 
             def e2e_step(i):
-                assert lib.htp_buf_upload(fx, 0, x_host.data_ptr(), x_host.numel() * 2) == 0
+                # upload is only enqueued (pinned source): the message that follows is ordered behind it
+                assert lib.htp_buf_upload_async(fx, 0, x_host.data_ptr(), x_host.numel() * 2) == 0
                 st = chan.submit(reqs[i % copies])
                 assert st == [0], st
                 if world > 1:
@@ -578,19 +646,26 @@ def run_ours(args):
                 torch.cuda.current_stream().synchronize()
             for i in range(warm):
                 e2e_step(i)
+            e2e_steps = max(steps, 200)
+            per_step = []
             barrier()
             t0 = time.perf_counter()
-            for i in range(steps):
+            for i in range(e2e_steps):
+                t1 = time.perf_counter()
                 e2e_step(i)
+                per_step.append(time.perf_counter() - t1)
             barrier()
-            dt = (time.perf_counter() - t0) / steps
-            t = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dt = (time.perf_counter() - t0) / e2e_steps
+            t = torch.tensor([dt, statistics.median(per_step)], device=dev, dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t[0])
+            dt, med = float(t[0]), float(t[1])
+            e2e_ok = g1 is None or matches_fixture(out_host.numpy(), g1, 1e-3)
             e2e = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "ms_per_step": round(dt * 1e3, 4),
+                   "ms_per_step_median": round(med * 1e3, 4), "steps": e2e_steps,
                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": m * op.n * 4,
-                   "path": "htp_buf_upload -> message channel (1 request) -> "
+                   "downloaded_logits_match_fixture": bool(e2e_ok),
+                   "path": "htp_buf_upload_async (pinned host memory) -> message channel (1 request) -> "
                            + ("NCCL all-gather -> " if world > 1 else "") + "download of the fp32 logits; "
                            "weights stay resident, as the reference's mapped weight buffers do"}
         finally:
@@ -604,8 +679,7 @@ def run_ours(args):
             "metric": "decode_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": steps,
             "warmup": warm, "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16 x int8 -> f32", "data": "synthetic",
-            "config": {"workload": "cfg4 lm_head Q8_0 128256x4096, fp16 activations, M=1, rows sharded over "
-                                   f"{world} GPU(s)", "exchange": exchange,
+            "config": {"workload": workload_name(world), "exchange": exchange,
                        "l2": f"rotating {copies} distinct weight copies per rank "
                              f"({slab * copies / 1e6:.0f} MB > 126 MB L2): every pass reads HBM",
                        "algorithmic_bytes_per_step": total_bytes,
@@ -613,6 +687,9 @@ def run_ours(args):
                        **({"ms_per_step_with_nccl_all_gather": round(gather_ms, 5)} if gather_ms else {})},
             "roofline": {"bound": "hbm", "kernel": "gemv_mma_kernel<Q8_0,f16,M=1>", "achieved": round(achieved, 1),
                          "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4),
+                         # the same kernel inside the long (~0.5 s) step loop, clocks under the power cap
+                         "frac_sustained": (round(total_bytes / (ms_step_long * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+                                            if world == 1 else None),
                          "peak_source": f"{peaks['source']} (copy bandwidth)", "ms_per_launch": round(k_ms, 5),
                          "algorithmic_bytes_per_launch": k_bytes,
                          # the committed capture is of the whole matrix on one GPU; a rank's launch covers its
@@ -620,13 +697,15 @@ def run_ours(args):
                          "traffic": (None if read_traffic("cfg4_m1_q8_0") is None
                                      else int(read_traffic("cfg4_m1_q8_0") * k_bytes / total_bytes))},
             "e2e": e2e, "gpu_launches": int(first_launches), "clocks": clocks,
+            "parity_ok": parity["decode_m1"],
+            "parity": "assembled logits of every rank (NCCL all-gather and fused exchange) against the committed "
+                      "fp64-oracle samples of config 4, gate 1e-3",
         }
     # the sharded prefill case of config 4 (M = 256): each rank multiplies its row shard on the tensor
     # cores, then the [256][N / R] slabs are gathered into [256][N] on every rank
     if world > 1:
         m2, steps2 = 256, max(5, min(20, steps))
-        x2 = torch.randn((m2, op.k), device=dev, dtype=torch.float32, generator=torch.Generator(device=dev)
-                         .manual_seed(4)).to(torch.float16)
+        x2 = torch.from_numpy(wl.make_activation(cfg, m2)).to(dev)  # the configuration's seeded tokens
         y2 = torch.empty((m2, n_loc), device=dev, dtype=torch.float32)
         logits2 = torch.empty((m2, op.n), device=dev, dtype=torch.float32)
 
@@ -672,6 +751,13 @@ def run_ours(args):
                 step3(0)
                 torch.cuda.synchronize()
                 same = bool((sym == logits2).all().item())
+                g256 = golden_fixture("cfg4", "m256")
+                if g256 is not None:
+                    okp = matches_fixture(logits2.cpu().numpy(), g256, 1e-3) and matches_fixture(sym.cpu().numpy(), g256,
+                                                                                                 1e-3)
+                    tp = torch.tensor([1 if okp else 0], device=dev)
+                    dist.all_reduce(tp, op=dist.ReduceOp.MIN)
+                    parity["prefill_m256"] = bool(int(tp[0]))
                 for i in range(3):
                     step3(i)
                 barrier()
@@ -698,6 +784,7 @@ def run_ours(args):
                 "frac_of_tensor_peak_per_gpu": round(wl.flops(op, m2, n_loc) / (float(t[1]) * 1e-3) / 1e12
                                                      / peaks["tflops"], 4),
                 "gathered_bytes_per_step": m2 * op.n * 4, "fused_exchange": fused,
+                "parity_ok": parity.get("prefill_m256"),
                 "note": "whole-job TFLOP/s = 2*256*128256*4096 / max-over-ranks time of GEMM + all-gather"}
         del x2, y2, logits2
     # single-GPU extras and the CPU baseline: rank 0 at N = 1 only

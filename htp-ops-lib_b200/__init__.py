@@ -55,6 +55,8 @@ EXPORTS = {
     "htp_b200_mul_mat_multi_dst": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "htp_b200_mul_mat_multi_dst_signal": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, ctypes.c_uint32,
                                                _vp]),
+    "htp_b200_mul_mat_gather_step": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, ctypes.c_uint32,
+                                          _vp]),
     "htp_b200_wait_flags": (_i, [_vp, _i, ctypes.c_uint32, _vp]),
     "htp_b200_weight_bytes": (_sz, [_i, _i64, _i64]),
     "htp_b200_stream_status": (_i, [_vp]),
@@ -88,6 +90,8 @@ EXPORTS = {
     "htp_buf_free": (_i, [_i]),
     "htp_buf_upload": (_i, [_i, _sz, _vp, _sz]),
     "htp_buf_download": (_i, [_i, _sz, _vp, _sz]),
+    "htp_buf_upload_async": (_i, [_i, _sz, _vp, _sz]),
+    "htp_buf_download_async": (_i, [_i, _sz, _vp, _sz]),
     "htp_buf_ptr": (_vp, [_i]),
     "htp_buf_is_host": (_i, [_i]),
     "htp_buf_size": (_sz, [_i]),

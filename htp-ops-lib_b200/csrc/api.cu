@@ -19,7 +19,7 @@ namespace htp {
 
 int g_opt_pdl           = getenv("HTP_OPS_NO_PDL") ? 0 : 1;  // programmatic dependent launch
 int g_opt_force_generic = 0;
-int g_opt_gemm_min_m     = 64;
+int g_opt_gemm_min_m     = 64;  // fp16 activations with at least this many tokens go to the tensor-core GEMM
 int g_opt_gemv_whole_tiles = getenv("HTP_OPS_NO_WHOLE_TILES") ? 0 : 1;  // small mat-vecs: one whole tile per CTA
 // Cut the GEMM's work into equal K ranges when the tile count is uneven.  Off by default: on the
 // shapes measured (112 to 4008 tiles on 74 CTA pairs) the whole-tile schedule was 1-9 % faster -
@@ -29,7 +29,7 @@ int g_opt_gemm_split     = getenv("HTP_OPS_GEMM_SPLIT") ? 1 : 0;
 // Op indices 2, 3 and 4 of the dispatcher read the reference's permuted super-blocks (1) instead of
 // standard ggml blocks (0).
 int g_opt_permuted_weights = 0;
-int g_opt_gemm_tile_n    = 0;   // tokens per GEMM tile: 0 = by M, else 128 or 256  // fp16 activations with at least this many tokens go to the tensor-core GEMM
+int g_opt_gemm_tile_n    = 0;   // tokens per GEMM tile: 0 = by M, else 128 or 256
 
 namespace {
 std::mutex                                            g_mu;
@@ -88,6 +88,12 @@ StreamScratch *stream_scratch(DeviceCtx *ctx, cudaStream_t stream) {
   s.partials = reinterpret_cast<float *>(base);
   s.counters = reinterpret_cast<unsigned *>(base + pbytes);
   s.err      = reinterpret_cast<int *>(base + pbytes + cbytes);
+  if (cudaHostAlloc(reinterpret_cast<void **>(&s.err_host), 64, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(base);
+    return nullptr;
+  }
+  *s.err_host = 0;
   return &(g_scratch[key] = s);
 }
 
@@ -121,6 +127,7 @@ void release_all_scratch() {
     cudaSetDevice(kv.first.first);
     cudaFree(kv.second.partials);
     cudaFree(kv.second.gemm_part);
+    cudaFreeHost(kv.second.err_host);
   }
   g_scratch.clear();
   if (cur >= 0) {
@@ -166,46 +173,29 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
   if (!sc) {
     return -2;
   }
-  const int bb      = wt == 1 ? 34 : 18;
-  const int kb_all  = k / 32;
-  const int periods = kb_all / 8;
-  const int stage   = kGemvTileRows * gemv_row_pitch(wt);
-  const int budget  = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
-  const int asz     = a16 ? 2 : 4;
+  const int bb     = wt == 1 ? 34 : 18;
+  const int kb_all = k / 32;
+  const int asz    = a16 ? 2 : 4;
 
-  // Tokens per launch.  IQ4_NL has the two-token integer path only.  fp32 activations of more than
-  // four tokens would need two chained MMAs per k-step and 1 KB of activation fragments per block
-  // (K split over several launches): two launches of four tokens read the weights twice (the
-  // second time mostly from L2) but keep K whole and can join a batched launch.
-  const int slice = wt == 2 ? 2 : ((!a16 && m > 4) ? 4 : 8);
+  // Eight tokens per launch (one or two on their own narrower paths); more tokens re-read the weights
+  // once per slice of eight.
+  const int slice = 8;
   for (int m0 = 0; m0 < m; m0 += slice) {
-    const int mm   = (m - m0) < slice ? (m - m0) : slice;
-    const int mpad = mm <= 1 ? 1 : (mm <= 2 ? 2 : (mm <= 4 ? 4 : 8));
-    int       nchunks = 1, chunk_periods = periods, nst = 0;
-    for (;; ++nchunks) {
-      chunk_periods     = (periods + nchunks - 1) / nchunks;
-      const size_t frag = gemv_frag_bytes(wt, a16, mpad, chunk_periods * 8);
-      const long   room = (long) budget - kGemvSmemHeader - (long) frag;
-      nst               = room > 0 ? (int) (room / stage) : 0;
-      if (nst > kGemvMaxStages) {
-        nst = kGemvMaxStages;
-      }
-      if (nst >= 3 || (nst >= 2 && chunk_periods == 1)) {
-        break;
-      }
-      if (chunk_periods == 1) {
-        return -2;  // cannot happen on a device with >= 96 KiB of shared memory
-      }
+    const int mm = (m - m0) < slice ? (m - m0) : slice;
+    GemvPlan  pl;
+    if (!gemv_plan(ctx->max_smem, wt, a16, mm, kb_all, &pl)) {
+      return -2;
     }
-    if (band && nchunks > 1) {
+    if (band && pl.nchunks > 1) {
       return -1;  // K split over accumulating launches: not offered with several destinations
     }
     if (band && band->flags && m > slice) {
       return -1;  // the completion signal belongs to ONE launch
     }
-    for (int c = 0; c * chunk_periods < periods; ++c) {
-      const int p0  = c * chunk_periods;
-      const int pn  = (periods - p0) < chunk_periods ? (periods - p0) : chunk_periods;
+    const int periods = kb_all / 8;
+    for (int c = 0; c < pl.nchunks; ++c) {
+      const int p0  = c * pl.chunk_periods;
+      const int pn  = (periods - p0) < pl.chunk_periods ? (periods - p0) : pl.chunk_periods;
       GemvArgs  a   = {};
       a.y           = dst + (size_t) m0 * (band ? band->ld : n);
       if (band) {
@@ -231,9 +221,9 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       a.N             = n;
       a.kblocks       = pn * 8;
       a.accumulate    = c > 0;
-      a.stages_per_tile = (a.kblocks + gemv_stage_blocks(wt) - 1) / gemv_stage_blocks(wt);
+      a.stages_per_tile = (a.kblocks + pl.stage_blocks - 1) / pl.stage_blocks;
       a.total_items     = (long long) (n / kGemvTileRows) * a.stages_per_tile;
-      const size_t frag = gemv_frag_bytes(wt, a16, mpad, a.kblocks);
+      const size_t frag = gemv_frag_bytes(wt, a16, pl.mpad, a.kblocks);
       // ring depth: never more stages than the busiest CTA has items
       long long grid = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
       if (grid > a.total_items) {
@@ -247,15 +237,15 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
         grid = tiles;
       }
       const long long per_cta = (a.total_items + grid - 1) / grid;
-      a.n_stages              = nst;
+      a.n_stages              = pl.n_stages;
       if (a.n_stages > per_cta) {
         a.n_stages = (int) (per_cta < 2 ? 2 : per_cta);
       }
       a.partials = sc->partials;
       a.counters = sc->counters;
       a.err      = sc->err;
-      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) a.n_stages * stage;
-      if (gemv_mma_launch(a, wt, a16, mpad, (int) grid, smem, stream, pdl) != cudaSuccess) {
+      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) a.n_stages * pl.stage_bytes;
+      if (gemv_mma_launch(a, wt, a16, pl.mpad, (int) grid, smem, stream, pdl) != cudaSuccess) {
         cudaGetLastError();
         return -2;
       }
@@ -335,20 +325,20 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
 
 bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type) {
   const int wt = wt_index(weight_type);
-  if (wt < 0 || m <= 0 || m > (wt == 2 ? 2 : 8) || k <= 0 || n <= 0 || k % 256 != 0 || n % 32 != 0 ||
-      g_opt_force_generic) {
+  if (wt < 0 || m <= 0 || m > 8 || k <= 0 || n <= 0 || k % 256 != 0 || n % 32 != 0 || g_opt_force_generic) {
     return false;
   }
   const bool a16 = act_type == HTP_B200_ACT_F16;
   if (a16 && m >= g_opt_gemm_min_m) {
     return false;
   }
-  const int    mpad = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
-  const size_t frag = gemv_frag_bytes(wt, a16, mpad, k / 32);
-  const long   room = (long) kGemvSmemBudget - kGemvSmemHeader - (long) frag;
-  return room >= 3L * kGemvTileRows * gemv_row_pitch(wt);
+  GemvPlan pl;
+  return gemv_plan(kGemvSmemBudget, wt, a16, m, k / 32, &pl);
 }
 
+// One persistent launch per round: round c carries K range c of every operator that has one (all of
+// them in round 0; only matrices whose activation fragments do not fit one launch after that), and
+// rounds after the first add to the outputs the earlier ones wrote - stream order keeps them apart.
 int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type, int act_type, cudaStream_t st,
                           bool allow_pdl) {
   const int wt = wt_index(weight_type);
@@ -369,64 +359,91 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
   if (!sc) {
     return -2;
   }
-  const bool a16   = act_type == HTP_B200_ACT_F16;
-  const int  mpad  = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
-  const int  bb    = wt == 1 ? 34 : 18;
-  const int  stage = kGemvTileRows * gemv_row_pitch(wt);
-  const int  sb    = gemv_stage_blocks(wt);
+  const bool a16    = act_type == HTP_B200_ACT_F16;
+  const int  bb     = wt == 1 ? 34 : 18;
+  const int  budget = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
+  std::vector<GemvPlan> plans((size_t) n_ops);
+  int                   rounds = 1;
+  for (int i = 0; i < n_ops; ++i) {
+    if (!gemv_plan(budget, wt, a16, m, d[i].k / 32, &plans[i])) {
+      return -2;
+    }
+    rounds = plans[i].nchunks > rounds ? plans[i].nchunks : rounds;
+  }
+  const int mpad  = plans[0].mpad;
+  const int stage = plans[0].stage_bytes;
+  const int sb    = plans[0].stage_blocks;
   static thread_local GemvBatchArgs args;  // ~25 KB of kernel parameters, reused between launches
-  for (int o0 = 0; o0 < n_ops; o0 += kGemvBatchMaxOps) {
-    const int cnt = (n_ops - o0) < kGemvBatchMaxOps ? (n_ops - o0) : kGemvBatchMaxOps;
-    long long items = 0;
-    size_t    frag  = 0;
-    for (int i = 0; i < cnt; ++i) {
-      const MatMulDesc &q  = d[o0 + i];
-      GemvBatchOp      &op = args.ops[i];
-      const int         kb = q.k / 32;
-      if (gemv_weight_map(op.wmap, q.w, (long long) kb * bb, kb, q.n, wt) != cudaSuccess) {
+  for (int round = 0; round < rounds; ++round) {
+    int o0 = 0;
+    while (o0 < n_ops) {
+      // the next (up to) kGemvBatchMaxOps operators that have a K range number `round`
+      int       cnt   = 0;
+      long long items = 0;
+      size_t    frag  = 0;
+      int       i     = o0;
+      for (; i < n_ops && cnt < kGemvBatchMaxOps; ++i) {
+        if (plans[i].nchunks <= round) {
+          continue;
+        }
+        const MatMulDesc &q       = d[i];
+        GemvBatchOp      &op      = args.ops[cnt++];
+        const int         kb_all  = q.k / 32;
+        const int         periods = kb_all / 8;
+        const int         p0      = round * plans[i].chunk_periods;
+        const int         pn = (periods - p0) < plans[i].chunk_periods ? (periods - p0) : plans[i].chunk_periods;
+        const int         kb = pn * 8;
+        if (gemv_weight_map(op.wmap, q.w + (size_t) p0 * 8 * bb, (long long) kb_all * bb, kb, q.n, wt, mpad == 8) !=
+            cudaSuccess) {
+          cudaGetLastError();
+          return -2;
+        }
+        op.y               = q.y;
+        op.x               = q.x;
+        op.item_begin      = items;
+        op.N               = q.n;
+        op.kblocks         = kb;
+        op.x_stride        = q.k;
+        op.x_k_off         = p0 * 256;
+        op.accumulate      = round > 0;
+        op.stages_per_tile = (kb + sb - 1) / sb;
+        items += (long long) (q.n / kGemvTileRows) * op.stages_per_tile;
+        const size_t f = gemv_frag_bytes(wt, a16, mpad, kb);
+        frag           = f > frag ? f : frag;
+      }
+      o0 = i;
+      if (cnt == 0) {
+        break;
+      }
+      args.total_items = items;
+      args.partials    = sc->partials;
+      args.counters    = sc->counters;
+      args.err         = sc->err;
+      args.n_ops       = cnt;
+      args.M           = m;
+      args.frag_bytes  = (int) frag;
+      long long grid   = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
+      if (grid > items) {
+        grid = items;
+      }
+      int nst = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
+      nst     = nst > kGemvMaxStages ? kGemvMaxStages : nst;
+      const long long per_cta = (items + grid - 1) / grid;
+      if (nst > per_cta) {
+        nst = (int) (per_cta < 2 ? 2 : per_cta);
+      }
+      if (nst < 2) {
+        return -2;
+      }
+      args.n_stages     = nst;
+      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
+      if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) !=
+          cudaSuccess) {
         cudaGetLastError();
         return -2;
       }
-      op.y               = q.y;
-      op.x               = q.x;
-      op.item_begin      = items;
-      op.N               = q.n;
-      op.kblocks         = kb;
-      op.x_stride        = q.k;
-      op.stages_per_tile = (kb + sb - 1) / sb;
-      items += (long long) (q.n / kGemvTileRows) * op.stages_per_tile;
-      const size_t f = gemv_frag_bytes(wt, a16, mpad, kb);
-      frag           = f > frag ? f : frag;
+      count_launch();
     }
-    args.total_items = items;
-    args.partials    = sc->partials;
-    args.counters    = sc->counters;
-    args.err         = sc->err;
-    args.n_ops       = cnt;
-    args.M           = m;
-    args.frag_bytes  = (int) frag;
-    long long grid   = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
-    if (grid > items) {
-      grid = items;
-    }
-    const int budget = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
-    int       nst    = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
-    nst              = nst > kGemvMaxStages ? kGemvMaxStages : nst;
-    const long long per_cta = (items + grid - 1) / grid;
-    if (nst > per_cta) {
-      nst = (int) (per_cta < 2 ? 2 : per_cta);
-    }
-    if (nst < 2) {
-      return -2;
-    }
-    args.n_stages     = nst;
-    const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
-    if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) !=
-        cudaSuccess) {
-      cudaGetLastError();
-      return -2;
-    }
-    count_launch();
   }
   return 0;
 }
@@ -517,6 +534,17 @@ int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_
   }
   return mul_mat_multi_dst_impl(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n, weight_type, act_type, flags,
                                 epoch, stream);
+}
+
+int htp_b200_mul_mat_gather_step(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                                 const void *weight, int m, int k, int n, int weight_type, int act_type,
+                                 uint32_t *const *flags, const uint32_t *local_flags, uint32_t epoch, void *stream) {
+  if (!local_flags) {
+    return -1;
+  }
+  const int rc = htp_b200_mul_mat_multi_dst_signal(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n,
+                                                   weight_type, act_type, flags, epoch, stream);
+  return rc != 0 ? rc : htp_b200_wait_flags(local_flags, n_dst, epoch, stream);
 }
 
 int htp_b200_wait_flags(const uint32_t *flags, int n, uint32_t epoch, void *stream) {
@@ -636,18 +664,18 @@ int htp_b200_stream_status(void *stream) {
   if (!ctx) {
     return -2;
   }
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (cudaStreamSynchronize(st) != cudaSuccess) {
-    return -2;
-  }
+  cudaStream_t   st = static_cast<cudaStream_t>(stream);
   StreamScratch *sc = stream_scratch(ctx, st);
   if (!sc) {
     return -2;
   }
-  int code = 0;
-  if (cudaMemcpy(&code, sc->err, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) {
+  // the error word travels to pinned host memory behind the work it reports on: ONE wait, no
+  // blocking copy afterwards
+  if (cudaMemcpyAsync(sc->err_host, sc->err, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+      cudaStreamSynchronize(st) != cudaSuccess) {
     return -2;
   }
+  const int code = *static_cast<volatile int *>(sc->err_host);
   if (code != 0) {
     cudaMemsetAsync(sc->err, 0, 32, st);  // the error word and the launch-completion counter behind it
     // a kernel that gave up may have left arrival counters behind

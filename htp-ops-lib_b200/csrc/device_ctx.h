@@ -11,6 +11,7 @@ struct StreamScratch {
   float    *partials = nullptr;  // [kGemvMaxGrid][2][256]
   unsigned *counters = nullptr;  // [kGemvMaxGrid], zero between launches
   int      *err      = nullptr;  // first kernel error code
+  int      *err_host = nullptr;  // pinned host word the error code is copied to when the stream is waited for
   float    *gemm_part = nullptr;  // split-tile scratch of the prefill GEMM, allocated on its first use
 };
 

@@ -53,23 +53,30 @@ constexpr int kThreads         = kConsumerThreads + 32 + kReduceThreads;
 template <int WT, bool A16, int MPAD>
 struct Cfg {
   static constexpr int  BB       = BlockTraits<WT>::kBytes;
-  // Q4_0 with one or two tokens runs on the INTEGER tensor-core path: nibbles are masked into
-  // unsigned bytes (3 instructions per 8 weights instead of 9 for exact fp16), the activations are
-  // four signed base-128 digits of a 28-bit fixed-point value (column = 4 m + digit), one
-  // m16n8k32 MMA covers a whole block, and the -8 offset of the format comes in through the MMA's
-  // accumulator input.
-  static constexpr bool I8       = ((WT == kQ4 || WT == kIQ4) && MPAD <= 2);
-  static_assert(WT != kIQ4 || I8, "IQ4_NL runs on the integer path only (two tokens per launch)");
-  static constexpr int  CH       = I8 ? 1 : ((!A16 && MPAD == 8) ? 2 : 1);  // chained MMAs per k-step
-  static constexpr int  NC       = I8 ? 4 * MPAD : (A16 ? MPAD : (MPAD == 8 ? 8 : 2 * MPAD));  // MMA columns in use
-  static constexpr bool SPLITCOL = !I8 && (!A16 && MPAD < 8);             // column = 2 m + piece
-  static constexpr int  SB       = gemv_stage_blocks(WT);  // blocks per stage and row
-  static constexpr int  BPW      = SB / kConsumerWarps;    // blocks per consumer warp and stage (even count)
-  static constexpr int  PSTRIDE  = gemv_row_pitch(WT);
+  // Three to eight tokens (MPAD = 8), every weight format: the WIDE integer path.  A token, scaled by
+  // a power of two, is the 23-bit fixed-point integer D2 * 2^16 + D1 * 2^8 + D0 with signed
+  // base-256 digits; MMA number d of a block multiplies the weights by digit d of all eight tokens
+  // (MMA column = token), so the three results of one (row, token) pair sit in the same lane.
+  static constexpr bool WIDE     = MPAD == 8;
+  // Q4_0 / IQ4_NL with one or two tokens run on the INTEGER tensor-core path too: nibbles are
+  // masked into unsigned bytes (3 instructions per 8 weights instead of 9 for exact fp16), the
+  // activations are four signed base-128 digits of a 28-bit fixed-point value (column = 4 m +
+  // digit), one m16n8k32 MMA covers a whole block, and the -8 offset of the format comes in
+  // through the MMA's accumulator input.
+  static constexpr bool I8       = WIDE || ((WT == kQ4 || WT == kIQ4) && MPAD <= 2);
+  static constexpr bool DIGCOL   = I8 && !WIDE;  // MMA column = 4 m + digit
+  static_assert(MPAD == 1 || MPAD == 2 || MPAD == 8, "token paddings built: 1, 2, 8");
+  static constexpr int  NC       = WIDE ? 8 : (I8 ? 4 * MPAD : (A16 ? MPAD : 2 * MPAD));  // MMA columns in use
+  static constexpr bool SPLITCOL = !I8 && !A16;                                         // column = 2 m + piece
+  static constexpr int  SB       = gemv_stage_blocks(WT, WIDE);  // blocks per stage and row
+  static constexpr int  BPW      = SB / kConsumerWarps;          // blocks per consumer warp and stage
+  static_assert(BPW >= 1 && BPW * kConsumerWarps == SB, "a stage splits evenly over the consumer warps");
+  static constexpr int  PSTRIDE  = gemv_row_pitch(WT, WIDE);
   static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
   // uint2 entries per block: two k-steps of fp16 fragments, or one int8 fragment per column and lane
-  // position followed by the columns' accumulator inputs (one int each)
-  static constexpr int  FRAG_U2  = I8 ? NC * 4 + NC / 2 : 2 * CH * NC * 4;
+  // position (per MMA) followed by the columns' accumulator inputs (one int each)
+  static constexpr int  FRAG_U2  = WIDE ? 3 * 32 + 12 : (I8 ? NC * 4 + NC / 2 : 2 * NC * 4);
+  static constexpr int  CIN_OFF  = WIDE ? 3 * 32 : NC * 4;  // where a block's accumulator inputs start
 };
 
 struct Smem {
@@ -89,6 +96,9 @@ struct Smem {
   uint64_t op_bar;  // batched launch: the consumer warps meet here before an operator's activations replace the last one's
   uint8_t  pad2[88];
   float    red[2][kConsumerWarps][256];
+  // finished tile [token][row] of a launch with several destinations: staged here so that the copies
+  // leave as 16-byte stores, 128 contiguous bytes per token and destination
+  float    out_tile[8][kGemvTileRows];
 };
 static_assert(sizeof(Smem) % 128 == 0, "keep the regions after the header 128-byte aligned");
 static_assert(sizeof(Smem) == kGemvSmemHeader, "host-side size computation must match");
@@ -194,7 +204,96 @@ __device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int 
         sd += __shfl_xor_sync(0xffffffffu, sd, 2);
         if (t == 0) {
           // (Q4_0: value = nibble - 8; IQ4_NL: the table values are used as they are)
-          reinterpret_cast<int *>(dst + C::NC * 4)[4 * m + d] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
+          reinterpret_cast<int *>(dst + C::CIN_OFF)[4 * m + d] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
+        }
+      }
+    }
+  }
+}
+
+// Wide integer path (three to eight tokens): token m, scaled by a power of two so that |x| < 1, is
+// the fixed-point integer X = round(x * 2^22) = D2 * 2^16 + D1 * 2^8 + D0 with signed digits (D0, D1
+// in [-128, 127], |D2| <= 65).  Per block: three MMA operand sets, set d = digit d of the eight
+// tokens (column = token), then the 24 accumulator inputs (kMagicBits, less 8 * sum_k D for Q4_0's
+// offset).  The rounding of x, at most 2^-23 of the power of two above the token's largest
+// magnitude per element, is the only inexact step of the path.
+constexpr int kWideShift = 22;
+
+template <int WT, bool A16>
+__device__ void build_x_frags_wide(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
+  using C = Cfg<WT, A16, 8>;
+  if (tid < 8) {
+    sm->tok_amax_bits[tid] = 0;
+  }
+  named_bar_sync(1, kConsumerThreads);
+  const int klen = p.kblocks * 32;
+  auto      xval = [&](int m, int k) -> float {
+    const long long i = (long long) m * p.x_stride + p.x_k_off + k;
+    if constexpr (A16) {
+      return __half2float(static_cast<const __half *>(p.x)[i]);
+    } else {
+      return static_cast<const float *>(p.x)[i];
+    }
+  };
+  for (int m = 0; m < p.M; ++m) {
+    float a = 0.0f;
+    for (int k = tid; k < klen; k += kConsumerThreads) {
+      a = fmaxf(a, fabsf(xval(m, k)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+    }
+    if ((tid & 31) == 0) {
+      atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
+    }
+  }
+  named_bar_sync(1, kConsumerThreads);
+  if (tid < 8) {
+    const int bits = sm->tok_amax_bits[tid];
+    int       sh   = ((bits >> 23) & 0xff) - 127 + 1;  // amax < 2^sh
+    sh             = sh < -100 ? -100 : (sh > 100 ? 100 : sh);
+    sm->tok_scale[tid] = __int_as_float((127 + kWideShift - sh) << 23);  // x -> fixed point
+    sm->tok_inv[tid]   = __int_as_float((127 + sh - kWideShift) << 23);
+  }
+  named_bar_sync(1, kConsumerThreads);
+
+  const int n_units = p.kblocks * 4;  // (block, t): a multiple of 32, so warps stay whole
+  for (int u = tid; u < n_units; u += kConsumerThreads) {
+    const int b = u >> 2, t = u & 3;
+    uint2    *dst = frags + (size_t) b * C::FRAG_U2;
+    for (int m = 0; m < 8; ++m) {
+      // this lane position multiplies block elements 4t .. 4t+3 (register 0) and 16+4t .. (register 1)
+      uint32_t dig[3][2] = {};
+      int      sum[3]    = { 0, 0, 0 };
+      if (m < p.M) {
+        const float sc = sm->tok_scale[m];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            // block element that byte i of A register h (rows g / g + 8) of this lane position holds
+            const int e = WT == kIQ4 ? iq4nl_word_elem(t, h, i) : 16 * h + 4 * t + i;
+            int       r = __float2int_rn(xval(m, b * 32 + e) * sc);
+#pragma unroll
+            for (int d = 0; d < 3; ++d) {
+              const int dv = d < 2 ? ((r + 128) & 255) - 128 : r;
+              r            = (r - dv) >> 8;
+              sum[d] += dv;
+              dig[d][h] |= (uint32_t) (dv & 0xff) << (8 * i);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        dst[(8 * d + m) * 4 + t] = make_uint2(dig[d][0], dig[d][1]);
+        int sd                   = sum[d];
+        sd += __shfl_xor_sync(0xffffffffu, sd, 1);
+        sd += __shfl_xor_sync(0xffffffffu, sd, 2);
+        if (t == 0) {
+          // (Q4_0: value = nibble - 8; Q8_0 and IQ4_NL bytes are the values themselves)
+          reinterpret_cast<int *>(dst + C::CIN_OFF)[8 * d + m] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
         }
       }
     }
@@ -204,6 +303,10 @@ __device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int 
 template <int WT, bool A16, int MPAD>
 __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
   using C = Cfg<WT, A16, MPAD>;
+  if constexpr (C::WIDE) {
+    build_x_frags_wide<WT, A16>(p, sm, frags, tid);
+    return;
+  }
   if constexpr (C::I8) {
     build_x_frags_i8<WT, A16, MPAD>(p, sm, frags, tid);
     return;
@@ -253,7 +356,7 @@ __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid
     const int i01 = mma_frag_elem<WT>(j, t, 0, 1) & 3;
     const int i10 = mma_frag_elem<WT>(j, t, 1, 0) & 3;
     const int i11 = mma_frag_elem<WT>(j, t, 1, 1) & 3;
-    uint2    *dst = frags + (size_t) (b * 2 + j) * C::CH * C::NC * 4;
+    uint2    *dst = frags + (size_t) (b * 2 + j) * C::NC * 4;
     for (int m = 0; m < MPAD; ++m) {
       if constexpr (A16) {
         __half v[4] = { __half(0.f), __half(0.f), __half(0.f), __half(0.f) };
@@ -285,13 +388,8 @@ __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid
         fh.y = h2_as_u32(__halves2half2(hi[i10], hi[i11]));
         fl.x = h2_as_u32(__halves2half2(lo[i00], lo[i01]));
         fl.y = h2_as_u32(__halves2half2(lo[i10], lo[i11]));
-        if constexpr (C::SPLITCOL) {
-          dst[(2 * m) * 4 + t]     = fh;
-          dst[(2 * m + 1) * 4 + t] = fl;
-        } else {
-          dst[m * 4 + t]             = fh;  // chain 0
-          dst[C::NC * 4 + m * 4 + t] = fl;  // chain 1
-        }
+        dst[(2 * m) * 4 + t]     = fh;
+        dst[(2 * m + 1) * 4 + t] = fl;
       }
     }
   }
@@ -300,7 +398,7 @@ __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid
 // ------------------------------------------------------------------ one block x 16 rows
 
 template <int WT, bool A16, int MPAD, bool EVEN>
-__device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf)[2][2], int t, float (&acc)[4]) {
+__device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf)[2], int t, float (&acc)[4]) {
   using C = Cfg<WT, A16, MPAD>;
   // ra: this lane's row g of the 16-row group, at the block's first byte; row g+8 is 8 pitches on
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
@@ -344,12 +442,8 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
   const float db = lds_scale(rb);
 
   float c[4];
-  mma_16816_zero(c, a0, bf[0][0].x, bf[0][0].y);
-  mma_16816(c, a1, bf[1][0].x, bf[1][0].y);
-  if constexpr (C::CH == 2) {
-    mma_16816(c, a0, bf[0][1].x, bf[0][1].y);
-    mma_16816(c, a1, bf[1][1].x, bf[1][1].y);
-  }
+  mma_16816_zero(c, a0, bf[0].x, bf[0].y);
+  mma_16816(c, a1, bf[1].x, bf[1].y);
   acc[0] = fmaf(da, c[0], acc[0]);
   acc[1] = fmaf(da, c[1], acc[1]);
   acc[2] = fmaf(db, c[2], acc[2]);
@@ -409,45 +503,195 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
   acc[3] = fmaf(db, f3, acc[3]);
 }
 
+// Packed pairs of floats (sm_100 has two-lane fp32 add and fma on 64-bit registers).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+// acc += d2 * (bits as floats - 12582912), both lanes: the integer MMA results of one row leave
+// their float bias behind and are scaled by the row's block scale
+__device__ __forceinline__ void scale_add2(uint64_t &acc, int b0, int b1, uint64_t d2, uint64_t neg_magic2) {
+  asm("{\n\t.reg .b64 p;\n\t"
+      "mov.b64 p, {%1, %2};\n\t"
+      "add.rn.f32x2 p, p, %4;\n\t"
+      "fma.rn.f32x2 %0, %3, p, %0;\n\t}"
+      : "+l"(acc)
+      : "r"(b0), "r"(b1), "l"(d2), "l"(neg_magic2));
+}
+
+// Wide integer path: one block x 16 rows x eight tokens = THREE m16n8k32 MMAs on the same weight
+// registers, one per activation digit.  acc[d][0]: row g, tokens 2t and 2t + 1 of digit d; acc[d][1]: row g + 8.
+template <int WT, bool A16, bool EVEN>
+__device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], const uint2 (&cin)[3], int t,
+                                                  uint64_t neg_magic2, uint64_t (&acc)[3][2]) {
+  using C = Cfg<WT, A16, 8>;
+  const uint8_t *rb = ra + 8 * C::PSTRIDE;
+  uint32_t       a0, a1, a2, a3;
+  if constexpr (WT == kQ8) {
+    // lane position t owns quant words t and t + 4 of the block: bytes are the values (signed)
+    if constexpr (EVEN) {  // quants start 2 bytes past a word boundary
+      a0 = __byte_perm(lds32(ra + 4 * t), lds32(ra + 4 * t + 4), 0x5432);
+      a2 = __byte_perm(lds32(ra + 4 * t + 16), lds32(ra + 4 * t + 20), 0x5432);
+      a1 = __byte_perm(lds32(rb + 4 * t), lds32(rb + 4 * t + 4), 0x5432);
+      a3 = __byte_perm(lds32(rb + 4 * t + 16), lds32(rb + 4 * t + 20), 0x5432);
+    } else {
+      a0 = lds32(ra + 2 + 4 * t);
+      a2 = lds32(ra + 2 + 4 * t + 16);
+      a1 = lds32(rb + 2 + 4 * t);
+      a3 = lds32(rb + 2 + 4 * t + 16);
+    }
+  } else {
+    uint32_t qa, qb;
+    if constexpr (EVEN) {
+      qa = __byte_perm(lds32(ra + 4 * t), lds32(ra + 4 * t + 4), 0x5432);
+      qb = __byte_perm(lds32(rb + 4 * t), lds32(rb + 4 * t + 4), 0x5432);
+    } else {
+      qa = lds32(ra + 2 + 4 * t);
+      qb = lds32(rb + 2 + 4 * t);
+    }
+    if constexpr (WT == kIQ4) {
+      iq4nl_unpack_word(qa, a0, a2);
+      iq4nl_unpack_word(qb, a1, a3);
+    } else {
+      a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
+      a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+    }
+  }
+  const float    da  = lds_scale(ra);
+  const float    db  = lds_scale(rb);
+  const uint64_t da2 = pack2(da, da), db2 = pack2(db, db);
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    int r0, r1, r2, r3;
+    if constexpr (WT == kQ4) {
+      asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(cin[d].x), "r"(cin[d].y));
+    } else {
+      asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(cin[d].x), "r"(cin[d].y));
+    }
+    scale_add2(acc[d][0], r0, r1, da2, neg_magic2);
+    scale_add2(acc[d][1], r2, r3, db2, neg_magic2);
+  }
+}
+
+// Per-lane partial sums of the tile in progress: rows g, g + 8 of both 16-row groups x MMA columns
+// 2t, 2t + 1.  The wide path keeps one packed pair per digit, row and group and weighs the digits
+// when the tile is handed over.
+template <class C, bool WIDE = C::WIDE>
+struct TileAcc {
+  float v[2][4];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[rg][i] = 0.f;
+      }
+    }
+  }
+  __device__ __forceinline__ void sums(float (&o)[2][4]) const {
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        o[rg][i] = v[rg][i];
+      }
+    }
+  }
+};
+template <class C>
+struct TileAcc<C, true> {
+  uint64_t v[2][3][2];
+  __device__ __forceinline__ void zero() {
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        v[rg][d][0] = v[rg][d][1] = 0ull;  // the bit pattern of (0.f, 0.f)
+      }
+    }
+  }
+  // digit d weighs 256^d (the common factor 2^-22 is part of the token's output scale)
+  __device__ __forceinline__ void sums(float (&o)[2][4]) const {
+#pragma unroll
+    for (int rg = 0; rg < 2; ++rg) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float a0, a1, b0, b1, c0, c1;
+        unpack2(v[rg][0][r], a0, a1);
+        unpack2(v[rg][1][r], b0, b1);
+        unpack2(v[rg][2][r], c0, c1);
+        o[rg][2 * r]     = fmaf(c0, 65536.f, fmaf(b0, 256.f, a0));
+        o[rg][2 * r + 1] = fmaf(c1, 65536.f, fmaf(b1, 256.f, a1));
+      }
+    }
+  }
+};
+
 // This warp's blocks of one stage, both 16-row groups.  sb: the lane's row g at the warp's first
 // block of the stage; fp: the lane's fragment entry (column g, lane position t) of that block;
-// cp (integer path): the lane's pair of accumulator inputs (columns 2t, 2t + 1) of that block.
+// cp (integer paths): the lane's pair of accumulator inputs (columns 2t, 2t + 1) of that block;
+// par: parity of the warp's first block inside the stage (it decides which blocks start on a word
+// boundary; always 0 when a warp owns an even number of blocks).
 template <int WT, bool A16, int MPAD>
-__device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp, const uint2 *cp, int t,
-                                             float (&acc)[2][4]) {
+__device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp, const uint2 *cp, int t, int par,
+                                             TileAcc<Cfg<WT, A16, MPAD>> &acc) {
   using C = Cfg<WT, A16, MPAD>;
   uint64_t neg_magic2;  // the pair (-kMagic, -kMagic)
   asm("mov.b64 %0, {%1, %1};" : "=l"(neg_magic2) : "f"(-kMagic));
 #pragma unroll
   for (int i = 0; i < C::BPW; ++i) {
-    if constexpr (C::I8) {
+    const bool even = (((C::BPW % 2 == 0) ? 0 : par) + i) % 2 == 0;
+    if constexpr (C::WIDE) {
+      uint2 bf[3], cin[3];
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        bf[d]  = fp[i * C::FRAG_U2 + d * 32];
+        cin[d] = cp[i * C::FRAG_U2 + d * 4];
+      }
+#pragma unroll
+      for (int rg = 0; rg < 2; ++rg) {
+        const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
+        if (even) {
+          block_rows16_wide<WT, A16, true>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+        } else {
+          block_rows16_wide<WT, A16, false>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+        }
+      }
+    } else if constexpr (C::I8) {
       const uint2 bf  = fp[i * C::FRAG_U2];
       const uint2 cin = cp[i * C::FRAG_U2];
 #pragma unroll
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
-        if ((i & 1) == 0) {
-          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, neg_magic2, acc[rg]);
+        if (even) {
+          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
         } else {
-          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, neg_magic2, acc[rg]);
+          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
         }
       }
     } else if constexpr (WT != kIQ4) {
-      uint2 bf[2][2];
+      uint2 bf[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          bf[j][ch] = ch < C::CH ? fp[((i * 2 + j) * C::CH + ch) * C::NC * 4] : make_uint2(0u, 0u);
-        }
+        bf[j] = fp[(i * 2 + j) * C::NC * 4];
       }
 #pragma unroll
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
-        if ((i & 1) == 0) {
-          block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc[rg]);
+        if (even) {
+          block_rows16<WT, A16, MPAD, true>(ra, bf, t, acc.v[rg]);
         } else {
-          block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc[rg]);
+          block_rows16<WT, A16, MPAD, false>(ra, bf, t, acc.v[rg]);
         }
       }
     }
@@ -475,11 +719,14 @@ __device__ __forceinline__ bool mbar_wait_abort(uint64_t *bar, uint32_t parity, 
 // Consumer side of a tile completion, n = how many tiles this CTA has completed before: the warp
 // drops its partial sums into copy n & 1 of the reduction buffer and carries on.  Copy n & 1 was
 // last used by completion n - 2, which the completion warps have read once red_empty says so.
-__device__ __forceinline__ bool publish_tile(Smem *sm, const float (&acc)[2][4], int warp, int lane, unsigned n) {
+template <class C>
+__device__ __forceinline__ bool publish_tile(Smem *sm, const TileAcc<C> &tile_acc, int warp, int lane, unsigned n) {
   const int buf = n & 1;
   if (n >= 2 && !mbar_wait_abort(&sm->red_empty[buf], ((n >> 1) - 1) & 1, &sm->abort_flag)) {
     return false;
   }
+  float acc[2][4];
+  tile_acc.sums(acc);
 #pragma unroll
   for (int rg = 0; rg < 2; ++rg) {
     *reinterpret_cast<float4 *>(&sm->red[buf][warp][rg * 128 + lane * 4]) =
@@ -504,7 +751,7 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
   // which token the lane's results belong to, and whether this lane writes them out
   int  m0, m1;  // tokens of (column 2t, column 2t + 1); equal when the columns are pieces of one token
   bool writer = true;
-  if constexpr (C::I8) {
+  if constexpr (C::DIGCOL) {
     m0 = m1 = t >> 1;
     writer  = (t & 1) == 0;
   } else if constexpr (C::SPLITCOL) {
@@ -572,7 +819,7 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
   }
   // v.x, v.y: row g, columns 2t, 2t + 1;  v.z, v.w: row g + 8, same columns
   float lo0 = v.x, lo1 = v.y, hi0 = v.z, hi1 = v.w;
-  if constexpr (C::I8) {
+  if constexpr (C::DIGCOL) {
     // column 2t + c = 4 m + digit: weigh the digits (2^(7 digit - 27)) and add the four columns
     const float w0 = __int_as_float((127 + 7 * ((t & 1) << 1) - 27) << 23);
     const float w1 = __int_as_float((127 + 7 * (((t & 1) << 1) | 1) - 27) << 23);
@@ -584,24 +831,54 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
     lo0 += lo1;  // hi-piece column + lo-piece column
     hi0 += hi1;
   }
+  const long long ld = p.y_ld > 0 ? p.y_ld : p.N;
+  if (p.n_dst > 1) {
+    // Several destinations (every rank's copy of a row-sharded output): the two completion warps put
+    // the tile together in shared memory, then all 64 threads send it out as 16-byte stores - eight
+    // consecutive lanes cover the 128 bytes one token has in one destination.  (write_out is the same
+    // for all 64 threads.)
+    if (write_out && writer) {
+      auto stage = [&](int m, int r, float val, float inv) {
+        if (m < p.M) {
+          sm->out_tile[m][r] = val * inv;
+        }
+      };
+      stage(m0, rg * 16 + g, lo0, inv0);
+      stage(m0, rg * 16 + g + 8, hi0, inv0);
+      if constexpr (!C::DIGCOL && !C::SPLITCOL) {
+        stage(m1, rg * 16 + g, lo1, inv1);
+        stage(m1, rg * 16 + g + 8, hi1, inv1);
+      }
+    }
+    named_bar_sync(2, kReduceThreads);
+    if (write_out) {
+      const int       per_dst = p.M * (kGemvTileRows / 4);
+      const long long col     = p.y_col0 + tile * kGemvTileRows;
+      for (int i = rg * 32 + lane; i < p.n_dst * per_dst; i += kReduceThreads) {
+        const int    d = i / per_dst, r = i - d * per_dst;
+        const int    m = r >> 3, c = r & 7;
+        const float4 val  = *reinterpret_cast<const float4 *>(&sm->out_tile[m][4 * c]);
+        float       *base = d == 0 ? p.y : p.y_more[d - 1];
+        *reinterpret_cast<float4 *>(base + (long long) m * ld + col + 4 * c) = val;
+      }
+    }
+    named_bar_sync(2, kReduceThreads);  // the next tile may overwrite the staging area
+    return true;
+  }
   if (!write_out || !writer) {
     return true;
   }
   const long long row = tile * kGemvTileRows + rg * 16 + g;
-  const long long ld  = p.y_ld > 0 ? p.y_ld : p.N;
   auto            put = [&](int m, long long r, float val, float inv) {
     if (m < p.M) {
       const long long at = (long long) m * ld + p.y_col0 + r;
       val *= inv;
       p.y[at] = p.accumulate ? (p.y[at] + val) : val;
-      for (int d = 1; d < p.n_dst; ++d) {  // the other copies of the output (other GPUs' memory)
-        p.y_more[d - 1][at] = val;
-      }
     }
   };
   put(m0, row, lo0, inv0);
   put(m0, row + 8, hi0, inv0);
-  if constexpr (!C::I8 && !C::SPLITCOL) {
+  if constexpr (!C::DIGCOL && !C::SPLITCOL) {
     put(m1, row, lo1, inv1);
     put(m1, row + 8, hi1, inv1);
   }
@@ -707,14 +984,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
     named_bar_sync(1, kConsumerThreads);
 
-    float acc[2][4];
-#pragma unroll
-    for (int rg = 0; rg < 2; ++rg) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[rg][i] = 0.f;
-      }
-    }
+    TileAcc<C> acc;
+    acc.zero();
     // item -> (tile, stage) and ring position are tracked incrementally: no divisions in the loop
     long long tile = it0 / S;
     int       st   = (int) (it0 - tile * S);
@@ -728,7 +999,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW) * C::FRAG_U2;
     // (integer path) accumulator inputs of columns 2t, 2t + 1; positions past the columns in use
     // read another pair, their outputs are never stored
-    const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
+    const uint2   *warp_cin  = frags + C::CIN_OFF + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
       if (!mbar_wait_abort(&sm->full[slot], ph, &sm->abort_flag)) {
         record_error(p, kGemvErrConsumerWait);
@@ -741,7 +1012,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
         const uint2   *fp = warp_frag + (size_t) (st * C::SB) * C::FRAG_U2;
         const uint2   *cp = warp_cin + (size_t) (st * C::SB) * C::FRAG_U2;
-        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, acc);
+        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, warp & 1, acc);
       }
       // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
       // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
@@ -763,13 +1034,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = false;
             break;
           }
-#pragma unroll
-          for (int rg = 0; rg < 2; ++rg) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              acc[rg][i] = 0.f;
-            }
-          }
+          acc.zero();
           ++tile;
         }
       }
@@ -816,8 +1081,8 @@ cudaError_t launch_mpad(const GemvArgs &a, const CUtensorMap &wm, int mpad, int 
   switch (mpad) {
     case 1: return launch_one<WT, A16, 1>(a, wm, grid, smem, s, pdl);
     case 2: return launch_one<WT, A16, 2>(a, wm, grid, smem, s, pdl);
-    case 4: return launch_one<WT, A16, 4>(a, wm, grid, smem, s, pdl);
-    default: return launch_one<WT, A16, 8>(a, wm, grid, smem, s, pdl);
+    case 8: return launch_one<WT, A16, 8>(a, wm, grid, smem, s, pdl);
+    default: return cudaErrorInvalidValue;
   }
 }
 
@@ -893,12 +1158,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     GemvArgs p        = {};
     p.y               = b.ops[i].y;
     p.x               = b.ops[i].x;
-    p.x_k_off         = 0;
+    p.x_k_off         = b.ops[i].x_k_off;
     p.x_stride        = b.ops[i].x_stride;
     p.M               = b.M;
     p.N               = b.ops[i].N;
     p.kblocks         = b.ops[i].kblocks;
-    p.accumulate      = 0;
+    p.accumulate      = b.ops[i].accumulate;
     p.stages_per_tile = b.ops[i].stages_per_tile;
     p.item_base       = b.ops[i].item_begin;
     p.total_items     = b.total_items;
@@ -974,14 +1239,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     build_x_frags<WT, A16, MPAD>(p, sm, frags, tid);
     named_bar_sync(1, kConsumerThreads);
 
-    float acc[2][4];
-#pragma unroll
-    for (int rg = 0; rg < 2; ++rg) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc[rg][i] = 0.f;
-      }
-    }
+    TileAcc<C> acc;
+    acc.zero();
     int       S    = p.stages_per_tile;
     long long li   = it0 - p.item_base;
     long long tile = li / S;
@@ -996,7 +1255,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
     const uint2   *warp_frag = frag_lane + (size_t) (warp * C::BPW) * C::FRAG_U2;
     // (integer path) accumulator inputs of columns 2t, 2t + 1; positions past the columns in use
     // read another pair, their outputs are never stored
-    const uint2   *warp_cin  = frags + C::NC * 4 + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
+    const uint2   *warp_cin  = frags + C::CIN_OFF + (t & (C::NC / 2 - 1)) + (size_t) (warp * C::BPW) * C::FRAG_U2;
     for (long long it = it0; it < it1; ++it) {
       if (!mbar_wait_abort(&sm->full[slot], ph, &sm->abort_flag)) {
         atomicCAS(b.err, 0, kGemvErrConsumerWait);
@@ -1009,7 +1268,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
         const uint8_t *sb = warp_base + (size_t) slot * C::STAGE;
         const uint2   *fp = warp_frag + (size_t) (st * C::SB) * C::FRAG_U2;
         const uint2   *cp = warp_cin + (size_t) (st * C::SB) * C::FRAG_U2;
-        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, acc);
+        stage_blocks<WT, A16, MPAD>(sb, fp, cp, t, warp & 1, acc);
       }
       // The stage goes back to the TMA producer here.  An mbarrier arrive does not wait for this
       // thread's outstanding shared-memory loads, and the arithmetic that consumes the last loads
@@ -1031,13 +1290,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
             ok = false;
             break;
           }
-#pragma unroll
-          for (int rg = 0; rg < 2; ++rg) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              acc[rg][i] = 0.f;
-            }
-          }
+          acc.zero();
           if (++tile == tiles_in_op && oi + 1 < b.n_ops) {
             // next operator: its activations and token scales replace the old ones - once the
             // completion warps have taken the last tile of this one (its token scales with it) and
@@ -1108,8 +1361,8 @@ cudaError_t batch_mpad(const GemvBatchArgs &a, int mpad, int grid, size_t smem, 
   switch (mpad) {
     case 1: return batch_one<WT, A16, 1>(a, grid, smem, s, pdl);
     case 2: return batch_one<WT, A16, 2>(a, grid, smem, s, pdl);
-    case 4: return batch_one<WT, A16, 4>(a, grid, smem, s, pdl);
-    default: return batch_one<WT, A16, 8>(a, grid, smem, s, pdl);
+    case 8: return batch_one<WT, A16, 8>(a, grid, smem, s, pdl);
+    default: return cudaErrorInvalidValue;
   }
 }
 
@@ -1149,18 +1402,51 @@ cudaError_t flags_wait_launch(const unsigned *flags, int n, unsigned epoch, int 
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
   size_t b;
-  if ((wt == kQ4 || wt == kIQ4) && mpad <= 2) {  // integer path: 4 digit columns per token + their accumulator inputs
+  if (mpad == 8) {  // wide integer path: three digit sets of 8 columns + 24 accumulator inputs
+    b = (size_t) kblocks * (3 * 32 + 12) * 8;
+  } else if (wt == kQ4 || wt == kIQ4) {  // integer path: 4 digit columns per token + their accumulator inputs
     const int nc = 4 * mpad;
     b            = (size_t) kblocks * (nc * 4 + nc / 2) * 8;
   } else {
-    const int ch = (!a16 && mpad == 8) ? 2 : 1;
-    const int nc = a16 ? mpad : (mpad == 8 ? 8 : 2 * mpad);
-    b            = (size_t) kblocks * 2 * ch * nc * 4 * 8;
+    const int nc = a16 ? mpad : 2 * mpad;
+    b            = (size_t) kblocks * 2 * nc * 4 * 8;
   }
   return (b + 127) & ~(size_t) 127;
 }
 
-cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt) {
+bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *out) {
+  GemvPlan pl;
+  pl.mpad          = gemv_mpad(m);
+  pl.wide          = pl.mpad == 8;
+  pl.stage_blocks  = gemv_stage_blocks(wt, pl.wide);
+  pl.stage_bytes   = kGemvTileRows * gemv_row_pitch(wt, pl.wide);
+  const int periods = kblocks / 8;
+  const int budget  = smem_budget < kGemvSmemBudget ? smem_budget : kGemvSmemBudget;
+  if (m < 1 || m > 8 || kblocks <= 0 || kblocks % 8 != 0) {
+    return false;
+  }
+  for (pl.nchunks = 1;; ++pl.nchunks) {
+    pl.chunk_periods  = (periods + pl.nchunks - 1) / pl.nchunks;
+    const size_t frag = gemv_frag_bytes(wt, a16, pl.mpad, pl.chunk_periods * 8);
+    const long   room = (long) budget - kGemvSmemHeader - (long) frag;
+    pl.n_stages       = room > 0 ? (int) (room / pl.stage_bytes) : 0;
+    if (pl.n_stages > kGemvMaxStages) {
+      pl.n_stages = kGemvMaxStages;
+    }
+    if (pl.n_stages >= gemv_min_stages(pl.mpad) || (pl.n_stages >= 2 && pl.chunk_periods == 1)) {
+      break;
+    }
+    if (pl.chunk_periods == 1) {
+      return false;  // cannot happen on a device with >= 96 KiB of shared memory
+    }
+  }
+  pl.nchunks = (periods + pl.chunk_periods - 1) / pl.chunk_periods;
+  *out       = pl;
+  return true;
+}
+
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt,
+                            bool wide) {
   // Tensor map over a K range of the weight bytes, as 8-byte elements: inner dimension = bytes of
   // the K range per row / 8, outer = n rows, row pitch = w_row_bytes.  Encoding costs about a
   // microsecond of host time, comparable to a small launch, and a decoder re-issues the same few
@@ -1168,7 +1454,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   struct Key {
     const void *base;
     long long   row_bytes;
-    int         kblocks, n, wt, dev;
+    int         kblocks, n, wt, dev;  // wt: format, plus 16 for the wide path's narrower box
     bool operator==(const Key &o) const {
       return base == o.base && row_bytes == o.row_bytes && kblocks == o.kblocks && n == o.n && wt == o.wt &&
              dev == o.dev;
@@ -1186,7 +1472,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
   int                                                  dev = 0;
   cudaGetDevice(&dev);
-  const Key key{ w, w_row_bytes, kblocks, n, wt, dev };
+  const Key key{ w, w_row_bytes, kblocks, n, wt + (wide ? 16 : 0), dev };
   {
     std::lock_guard<std::mutex> lk(cache_mu);
     auto                        it = cache.find(key);
@@ -1203,7 +1489,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   const int        bb         = wt == kQ8 ? 34 : 18;
   const cuuint64_t gdim[2]    = { (cuuint64_t) kblocks * bb / 8, (cuuint64_t) n };
   const cuuint64_t gstride[1] = { (cuuint64_t) w_row_bytes };
-  const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
+  const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt, wide) / 8, (cuuint32_t) kGemvTileRows };
   const cuuint32_t estr[2]    = { 1, 1 };
   if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1224,7 +1510,8 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
 cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                             cudaStream_t stream, bool pdl) {
   CUtensorMap wmap;
-  cudaError_t e = gemv_weight_map(&wmap, args.w + args.w_k_off_bytes, args.w_row_bytes, args.kblocks, args.N, wt);
+  cudaError_t e =
+    gemv_weight_map(&wmap, args.w + args.w_k_off_bytes, args.w_row_bytes, args.kblocks, args.N, wt, mpad == 8);
   if (e != cudaSuccess) {
     return e;
   }
@@ -1232,16 +1519,9 @@ cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, in
     return a16 ? launch_mpad<kQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
                : launch_mpad<kQ4, false>(args, wmap, mpad, grid, smem, stream, pdl);
   }
-  if (wt == kIQ4) {  // integer path only: the caller slices the tokens in pairs
-    if (mpad > 2) {
-      return cudaErrorInvalidValue;
-    }
-    if (mpad == 1) {
-      return a16 ? launch_one<kIQ4, true, 1>(args, wmap, grid, smem, stream, pdl)
-                 : launch_one<kIQ4, false, 1>(args, wmap, grid, smem, stream, pdl);
-    }
-    return a16 ? launch_one<kIQ4, true, 2>(args, wmap, grid, smem, stream, pdl)
-               : launch_one<kIQ4, false, 2>(args, wmap, grid, smem, stream, pdl);
+  if (wt == kIQ4) {
+    return a16 ? launch_mpad<kIQ4, true>(args, wmap, mpad, grid, smem, stream, pdl)
+               : launch_mpad<kIQ4, false>(args, wmap, mpad, grid, smem, stream, pdl);
   }
   return a16 ? launch_mpad<kQ8, true>(args, wmap, mpad, grid, smem, stream, pdl)
              : launch_mpad<kQ8, false>(args, wmap, mpad, grid, smem, stream, pdl);
@@ -1254,15 +1534,8 @@ cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, i
                : batch_mpad<kQ4, false>(args, mpad, grid, smem, stream, pdl);
   }
   if (wt == kIQ4) {
-    if (mpad > 2) {
-      return cudaErrorInvalidValue;
-    }
-    if (mpad == 1) {
-      return a16 ? batch_one<kIQ4, true, 1>(args, grid, smem, stream, pdl)
-                 : batch_one<kIQ4, false, 1>(args, grid, smem, stream, pdl);
-    }
-    return a16 ? batch_one<kIQ4, true, 2>(args, grid, smem, stream, pdl)
-               : batch_one<kIQ4, false, 2>(args, grid, smem, stream, pdl);
+    return a16 ? batch_mpad<kIQ4, true>(args, mpad, grid, smem, stream, pdl)
+               : batch_mpad<kIQ4, false>(args, mpad, grid, smem, stream, pdl);
   }
   return a16 ? batch_mpad<kQ8, true>(args, mpad, grid, smem, stream, pdl)
              : batch_mpad<kQ8, false>(args, mpad, grid, smem, stream, pdl);

@@ -9,7 +9,7 @@ namespace htp {
 
 constexpr int kGemvTileRows    = 32;  // output rows per tile (two 16-row MMA groups)
 constexpr int kGemvMaxStages   = 8;
-constexpr int kGemvSmemHeader  = 33152;   // barriers, per-token scales, cross-warp reduction buffer
+constexpr int kGemvSmemHeader  = 34176;   // barriers, per-token scales, cross-warp reduction buffer
 constexpr int kGemvSmemBudget  = 232448;  // 227 KiB opt-in dynamic shared memory per CTA on sm_100
 constexpr int kGemvMaxGrid     = 1024;    // scratch is sized for this many CTAs
 
@@ -17,15 +17,26 @@ constexpr int kGemvErrProducerWait = 101;
 constexpr int kGemvErrConsumerWait = 102;
 
 // 32-weight blocks per pipeline stage and row: 64 for Q4_0 / IQ4_NL (1152 B), 32 for Q8_0 (1088 B), so a
-// stage of 32 rows is ~36 KB in either format.
-constexpr int gemv_stage_blocks(int wt) {
-  return wt == 1 ? 32 : 64;
+// stage of 32 rows is ~36 KB in either format.  The wide path (three to eight tokens), whose
+// activation fragments take 864 bytes per block, runs on half-size stages.
+constexpr int gemv_stage_blocks(int wt, bool wide = false) {
+  return (wt == 1 ? 32 : 64) / (wide ? 2 : 1);
 }
 
 // Shared-memory pitch of one weight row inside a stage: the stage's bytes plus 16, an odd
 // multiple of 16, so that eight consecutive rows start in eight different 16-byte bank groups.
-constexpr int gemv_row_pitch(int wt) {
-  return wt == 1 ? 1104 /* 32*34 = 1088 -> 69*16 */ : 1168 /* 64*18 = 1152 -> 73*16 */;
+constexpr int gemv_row_pitch(int wt, bool wide = false) {
+  return wide ? (wt == 1 ? 560 /* 16*34 = 544 -> 35*16 */ : 592 /* 32*18 = 576 -> 37*16 */)
+              : (wt == 1 ? 1104 /* 32*34 = 1088 -> 69*16 */ : 1168 /* 64*18 = 1152 -> 73*16 */);
+}
+
+// Tokens per launch are padded to 1, 2 or 8 (8 = the wide integer path).
+constexpr int gemv_mpad(int m) {
+  return m <= 1 ? 1 : (m <= 2 ? 2 : 8);
+}
+// Pipeline stages a launch needs at least: the wide path's stages are half as large.
+constexpr int gemv_min_stages(int mpad) {
+  return mpad == 8 ? 4 : 3;
 }
 
 struct GemvArgs {
@@ -78,6 +89,8 @@ struct alignas(64) GemvBatchOp {
   const void    *x;
   long long      item_begin;  // first item of this operator in the launch's item list
   int            N, kblocks, x_stride, stages_per_tile;
+  int            x_k_off;     // element offset of the operator's K range inside an activation row
+  int            accumulate;  // add to y: a later K range of a matrix whose fragments do not fit one launch
 };
 
 struct GemvBatchArgs {
@@ -90,13 +103,27 @@ struct GemvBatchArgs {
 };
 
 // Fills op.wmap for a weight matrix of n rows and kblocks blocks per row (cached by geometry).
-cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt);
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt,
+                            bool wide);
 
 cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                                   cudaStream_t stream, bool pdl);
 
 // Bytes of shared memory the activation fragments of `kblocks` blocks occupy.
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks);
+
+// How a mat-vec of m (1..8) tokens over kblocks blocks (a multiple of 8) per row runs: token padding,
+// stage geometry, and into how many equal K ranges it is cut so that the activation fragments of
+// one range fit in shared memory beside enough pipeline stages (ranges after the first accumulate
+// into the output, as launches of their own).  False when no split fits.
+struct GemvPlan {
+  int  mpad;
+  bool wide;
+  int  stage_blocks, stage_bytes;
+  int  nchunks, chunk_periods;  // K ranges; blocks of 256 weights per range (the last may be shorter)
+  int  n_stages;                // ring depth the budget allows for one range
+};
+bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *out);
 
 cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                             cudaStream_t stream, bool pdl);

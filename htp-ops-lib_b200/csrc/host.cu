@@ -107,6 +107,10 @@ struct Session {
   // that overlaps one of them must not be prefetched ahead of stream order
   IntervalSet  pending_out;
   PendingBatch batch;
+  // Operator state (the pending batch, pending_out, the stream's error word) is touched by the
+  // channel servicer AND by callers of execute_op_simple / the RPC-named functions; whoever
+  // enqueues or waits holds this lock - the servicer for a whole message, a direct call for itself.
+  std::mutex   op_mu;
   // message channel
   std::thread       servicer;
   std::atomic<bool> stop{ false };
@@ -246,13 +250,9 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   }
   const uintptr_t o0 = (uintptr_t) out, a0 = (uintptr_t) act, w0 = (uintptr_t) w;
   PendingBatch   &b  = g.batch;
-  // eight fp32 tokens go in as two operators of four (see run_gemv in api.cu)
-  const bool split8    = act_type == HTP_B200_ACT_F32 && p.m == 8 && weight_type != 20 &&
-                      htp::mul_mat_batchable(4, p.k, p.n, weight_type, act_type);
-  const int  m_eff     = split8 ? 4 : p.m;
-  const bool batchable = split8 || htp::mul_mat_batchable(p.m, p.k, p.n, weight_type, act_type);
+  const bool batchable = htp::mul_mat_batchable(p.m, p.k, p.n, weight_type, act_type);
   if (!b.ops.empty()) {
-    const bool same_kind = batchable && b.m == m_eff && b.weight_type == weight_type && b.act_type == act_type;
+    const bool same_kind = batchable && b.m == p.m && b.weight_type == weight_type && b.act_type == act_type;
     const bool hazard    = b.writes.overlaps(a0, a0 + act_bytes) || b.writes.overlaps(w0, w0 + w_bytes) ||
                         b.writes.overlaps(o0, o0 + out_bytes) || b.reads.overlaps(o0, o0 + out_bytes);
     if (!same_kind || hazard) {
@@ -268,15 +268,10 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
     return rc;
   }
   if (b.ops.empty()) {
-    b.m = m_eff, b.weight_type = weight_type, b.act_type = act_type;
+    b.m = p.m, b.weight_type = weight_type, b.act_type = act_type;
   }
   b.ops.push_back(htp::MatMulDesc{ reinterpret_cast<float *>(out), act, w, p.k, p.n });
   b.owners.push_back(owner);
-  if (split8) {
-    b.ops.push_back(htp::MatMulDesc{ reinterpret_cast<float *>(out) + (size_t) 4 * p.n,
-                                     reinterpret_cast<const float *>(act) + (size_t) 4 * p.k, w, p.k, p.n });
-    b.owners.push_back(owner);
-  }
   b.writes.add(o0, o0 + out_bytes);
   b.reads.add(a0, a0 + act_bytes);
   b.reads.add(w0, w0 + w_bytes);
@@ -343,7 +338,8 @@ void servicer_loop() {
       continue;
     }
     idle = 0;
-    std::vector<int> enqueued;
+    std::vector<int>            enqueued;
+    std::unique_lock<std::mutex> op_lock(g.op_mu);
     if (message_is_sane(hdr, g.max_msg)) {
       for (int i = 0; i < hdr->n_reqs; ++i) {
         RequestHeader *rh    = message_header_get_request_ptr(hdr, i);
@@ -387,6 +383,7 @@ void servicer_loop() {
         message_header_get_request_ptr(hdr, i)->state = rc;
       }
     }
+    op_lock.unlock();
     store_release64(&hdr->state.d, (uint64_t) v0 | (1ull << 8));
   }
 }
@@ -618,7 +615,8 @@ int execute_op_simple(struct OpComputeRequest *req) {
   if (!req || !set_session_device() || !g.backend) {
     return -1;
   }
-  const int rc = enqueue_op(req, nullptr);
+  std::lock_guard<std::mutex> op_lock(g.op_mu);
+  const int                   rc = enqueue_op(req, nullptr);
   if (rc != 0) {
     return rc;
   }
@@ -700,7 +698,7 @@ int htp_buf_free(int fd) {
   return 0;
 }
 
-static int copy_region(int fd, size_t offset, void *host, size_t size, bool upload) {
+static int copy_region(int fd, size_t offset, void *host, size_t size, bool upload, bool wait = true) {
   Buffer b;
   if (!host || !lookup(fd, &b) || offset > b.size || size > b.size - offset) {
     return -1;
@@ -721,7 +719,7 @@ static int copy_region(int fd, size_t offset, void *host, size_t size, bool uplo
   }
   cudaError_t e = upload ? cudaMemcpyAsync(b.ptr + offset, host, size, cudaMemcpyHostToDevice, g.stream)
                          : cudaMemcpyAsync(host, b.ptr + offset, size, cudaMemcpyDeviceToHost, g.stream);
-  if (e == cudaSuccess) {
+  if (e == cudaSuccess && wait) {
     e = cudaStreamSynchronize(g.stream);
   }
   if (e != cudaSuccess) {
@@ -733,6 +731,14 @@ static int copy_region(int fd, size_t offset, void *host, size_t size, bool uplo
 
 int htp_buf_upload(int fd, size_t offset, const void *src, size_t size) {
   return copy_region(fd, offset, const_cast<void *>(src), size, true);
+}
+
+int htp_buf_upload_async(int fd, size_t offset, const void *src, size_t size) {
+  return copy_region(fd, offset, const_cast<void *>(src), size, true, false);
+}
+
+int htp_buf_download_async(int fd, size_t offset, void *dst, size_t size) {
+  return copy_region(fd, offset, dst, size, false, false);
 }
 
 int htp_buf_download(int fd, size_t offset, void *dst, size_t size) {
@@ -762,6 +768,7 @@ int htp_session_synchronize(void) {
   if (!set_session_device() || !g.backend) {
     return -2;
   }
+  std::lock_guard<std::mutex> op_lock(g.op_mu);
   return wait_stream();
 }
 

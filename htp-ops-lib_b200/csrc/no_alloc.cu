@@ -18,6 +18,7 @@
 //     that first call during set-up, before any stream capture is begun.
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <cstdio>
 #include <mutex>
 
@@ -77,7 +78,7 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
   if (((uintptr_t) dst | (uintptr_t) activation | (uintptr_t) weight) & 127u) {
     return -1;
   }
-  const int wt = weight_type == 2 ? 0 : (weight_type == 8 ? 1 : -1);
+  const int wt = weight_type == 2 ? 0 : (weight_type == 8 ? 1 : (weight_type == 20 ? 2 : -1));  // Q4_0, Q8_0, IQ4_NL
   if (wt < 0 || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
     return -1;
   }
@@ -93,24 +94,22 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
   if (!scratch) {
     return -2;
   }
-  const bool   a16     = act_type == HTP_B200_ACT_F16;
-  const int    mpad    = m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : 8));
-  const int    bb      = wt == 1 ? 34 : 18;
-  const int    kblocks = k / 32;
-  const int    stage   = kGemvTileRows * gemv_row_pitch(wt);
-  const int    budget  = max_smem < kGemvSmemBudget ? max_smem : kGemvSmemBudget;
-  const size_t frag    = gemv_frag_bytes(wt, a16, mpad, kblocks);
-  const long   room    = (long) budget - kGemvSmemHeader - (long) frag;
-  int          nst     = room > 0 ? (int) (room / stage) : 0;
-  if (nst < 2) {
+  const bool a16     = act_type == HTP_B200_ACT_F16;
+  const int  bb      = wt == 1 ? 34 : 18;
+  const int  kblocks = k / 32;
+  // the same plan as htp_b200_mul_mat (token padding, stage geometry, ring depth) - but a K range that
+  // would need accumulating launches is refused here
+  GemvPlan pl;
+  if (!gemv_plan(max_smem, wt, a16, m, kblocks, &pl) || pl.nchunks > 1) {
     fprintf(stderr,
-            "htp_b200_mul_mat_static_scratch: k = %d with m = %d needs %zu bytes of activation fragments, more "
-            "than one launch holds in shared memory; use htp_b200_mul_mat (which splits K)\n", k, m, frag);
+            "htp_b200_mul_mat_static_scratch: k = %d with m = %d needs more activation fragments than one launch "
+            "holds in shared memory; use htp_b200_mul_mat (which splits K)\n", k, m);
     return -3;
   }
-  if (nst > kGemvMaxStages) {
-    nst = kGemvMaxStages;
-  }
+  const int    mpad  = pl.mpad;
+  const int    stage = pl.stage_bytes;
+  const int    nst   = pl.n_stages;
+  const size_t frag  = gemv_frag_bytes(wt, a16, mpad, kblocks);
   GemvArgs a        = {};
   a.y               = static_cast<float *>(dst);
   a.x               = activation;
@@ -123,7 +122,7 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
   a.N               = n;
   a.kblocks         = kblocks;
   a.accumulate      = 0;
-  a.stages_per_tile = (kblocks + gemv_stage_blocks(wt) - 1) / gemv_stage_blocks(wt);
+  a.stages_per_tile = (kblocks + pl.stage_blocks - 1) / pl.stage_blocks;
   a.total_items     = (long long) (n / kGemvTileRows) * a.stages_per_tile;
   long long grid    = sm_count < kStaticMaxGrid ? sm_count : kStaticMaxGrid;
   if (grid > a.total_items) {
@@ -150,5 +149,6 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
     cudaGetLastError();
     return -2;
   }
+  count_launch();
   return 0;
 }

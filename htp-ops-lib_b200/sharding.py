@@ -52,6 +52,10 @@ def all_gather_logits(dist, logits, y_local, m: int, n: int, world: int) -> None
         dist.all_gather(list(tmp.unbind(0)), mine.contiguous())
     else:
         dist.all_gather_into_tensor(tmp, mine.contiguous())
+    if equal:
+        # one strided copy [world][m][per] -> [m][world][per] (the row-major output seen per rank band)
+        logits.view(m, world, per).copy_(tmp.permute(1, 0, 2))
+        return
     for r in range(world):
         r0, r1 = row_range(n, r, world)
         if r1 > r0:

@@ -32,6 +32,14 @@ int htp_buf_free(int fd);
  * region outside the buffer, copy failure). */
 int htp_buf_upload(int fd, size_t offset, const void *src, size_t size);
 int htp_buf_download(int fd, size_t offset, void *dst, size_t size);
+/* The same copies, only ENQUEUED on the session stream: operators submitted afterwards (a message, a
+ * direct call) see an upload's bytes, and a download sees the results of operators submitted before
+ * it, but the call does not wait.  For pinned caller memory (pageable memory makes CUDA stage the
+ * copy and wait anyway).  The caller leaves `src` unchanged, and does not read `dst`, until the
+ * next completed message or htp_session_synchronize.  rpcmem needs no such calls: its bytes are
+ * shared with the DSP (src/host/test.c:30-53). */
+int htp_buf_upload_async(int fd, size_t offset, const void *src, size_t size);
+int htp_buf_download_async(int fd, size_t offset, void *dst, size_t size);
 
 /* Base address: device pointer of a device buffer, host pointer of a host buffer; NULL if unknown. */
 void *htp_buf_ptr(int fd);

@@ -1,7 +1,8 @@
 /*
  * Direct (non-channel) operator calls, same two symbols as the reference's
- * include/host/op_export.h:3-5 (src/host/op_export.c:6-14).  Neither operator is on the quantised
- * matmul path; until they are built they return HTP_AEE_EUNSUPPORTED.
+ * include/host/op_export.h:3-5 (src/host/op_export.c:6-14): synchronous RMSNorm and fp16-weight
+ * matmul on buffer handles, through the session's global handle.  0 on success, an HTP_AEE_* code
+ * otherwise (unknown handle, region outside its buffer, arguments the operator rejects).
  */
 #ifndef HTP_OPS_HOST_OP_EXPORT_H
 #define HTP_OPS_HOST_OP_EXPORT_H

@@ -35,10 +35,13 @@ AEEResult htp_ops_init_backend(remote_handle64 handle);
 AEEResult htp_ops_create_channel(remote_handle64 handle, int32_t fd, uint32_t size);
 /* commu.c:261-263 */
 AEEResult htp_ops_destroy_channel(remote_handle64 handle);
-/* commu.c:266-317; not on the quantised matmul path: HTP_AEE_EUNSUPPORTED */
+/* commu.c:266-317: RMSNorm of ne1 rows of ne0 floats, fd0/offset0 = dst, fd1/offset1 = src; runs and
+ * completes before returning.  HTP_AEE_EFAILED when the session is not ready or the operator rejects
+ * its arguments. */
 AEEResult htp_ops_rms_norm_f32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1, int32_t offset1,
                                int32_t ne0, int32_t ne1);
-/* commu.c:320-385; not on the quantised matmul path: HTP_AEE_EUNSUPPORTED */
+/* commu.c:320-385: output (fd0) = activation (fd1, fp32 [m][k]) x fp16 weights in the reference's tile
+ * order (fd2, as written by src/host/test.c:303-313); synchronous; HTP_AEE_EFAILED as above. */
 AEEResult htp_ops_mat_mul_permuted_w16a32(remote_handle64 handle, int32_t fd0, int32_t offset0, int32_t fd1,
                                           int32_t offset1, int32_t fd2, int32_t offset2, int32_t m, int32_t k,
                                           int32_t n);

@@ -7,6 +7,7 @@
  *   0   success (work is enqueued on `stream`, not necessarily finished),
  *  -1   invalid arguments (the reference's only failure code, src/dsp/ops/mat_mul.c:878-892),
  *  -2   a CUDA runtime call failed,
+ *  -3   (htp_b200_mul_mat_static_scratch only) valid arguments outside that entry point's range,
  *  >0   (htp_b200_stream_status only) a kernel reported a bounded wait that ran out.
  * There is no CPU fallback: without a usable CUDA device every call fails.
  */
@@ -71,13 +72,18 @@ int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activ
 /*
  * The decode mat-vec (m <= 8) for callers that must not allocate device memory once they are
  * running - a server that has handed all of device memory to its own pools, or a decode loop that
- * cannot take the device-wide synchronisation an allocation implies.  Same arguments, checks and
- * results as htp_b200_mul_mat, but the kernel's scratch is a static device array inside the
- * library (about 0.4 MB per GPU, held until the process exits) and the call makes no cudaMalloc,
- * cudaFree or other allocating call.  No counterpart in the reference.
+ * cannot take the device-wide synchronisation an allocation implies.  Same arguments and checks as
+ * htp_b200_mul_mat for the row-major block formats (weight_type 2, 8, 20), the same kernel, launch
+ * plan and results, but the kernel's scratch is a static device array inside the library (about
+ * 0.4 MB per GPU, held until the process exits) and the call makes no cudaMalloc, cudaFree or other
+ * allocating call.  No counterpart in the reference.
  *   - Range: m <= 8, k % 256 == 0, and the activation fragments of the whole k must fit in one
- *     launch's shared memory (always true for k <= 4096; for fp32 activations k = 14336 fits up to
- *     m = 2, for fp16 activations up to m = 4).  Outside it the call prints the reason to stderr and returns -3.
+ *     launch's shared memory (htp_b200_mul_mat cuts a longer k into launches that accumulate; this
+ *     call does not).  That holds for every k <= 4096, and beyond it up to:
+ *       m = 1:      k <= 18944 (Q4_0, IQ4_NL), 23040 (Q8_0, fp32 act.), 46080 (Q8_0, fp16 act.)
+ *       m = 2:      k <=  9472 (Q4_0, IQ4_NL), 11520 (Q8_0, fp32 act.), 23040 (Q8_0, fp16 act.)
+ *       m = 3 .. 8: k <=  4352 (Q4_0, IQ4_NL),  4608 (Q8_0)
+ *     Outside the range the call prints the reason to stderr and returns -3.
  *   - All calls on a device share the one array, which keeps the previous call's contents; what
  *     must start at zero is cleared on `stream` at the start of each call.  Calls that overlap on
  *     the GPU (two streams, two threads) race on it: keep them ordered, e.g. on one stream.
@@ -120,10 +126,25 @@ int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int
  * destination d - a 4-byte word in that destination GPU's memory reserved for THIS rank.  Together
  * with htp_b200_wait_flags on each GPU this replaces the all-gather AND the barrier of a row-sharded
  * decode step: rank r passes flags[d] = &(flag array of the GPU that owns dsts[d])[r].  Epochs must
- * increase from call to call (wrap-around safe).  No counterpart in the reference. */
+ * increase from call to call (wrap-around safe).  The kernel stores each finished 32-row tile to every
+ * destination as 16-byte stores (128 contiguous bytes per token and destination).  The flag says that
+ * THIS rank's band has landed; it does not hold back the next step - see the caller's obligation at
+ * htp_b200_mul_mat_gather_step.  No counterpart in the reference. */
 int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0,
                                       const void *activation, const void *weight, int m, int k, int n, int weight_type,
                                       int act_type, uint32_t *const *flags, uint32_t epoch, void *stream);
+
+/* One decode step of a row-sharded matrix in ONE call: htp_b200_mul_mat_multi_dst_signal, then
+ * htp_b200_wait_flags(local_flags, n_dst, epoch) on the same stream.  local_flags is THIS GPU's flag
+ * array (word r = rank r's flag), i.e. the array the peers' flags[] entries point into.  When the
+ * stream reaches the end of the step, every rank's band of this epoch is in this GPU's copy of the
+ * output.  The caller's obligation: a rank may start step e + 1 - and overwrite its band in the
+ * PEERS' copies - as soon as its own wait of step e has passed, so a consumer that still reads the
+ * output of step e when the next step is issued needs two output buffers used in turn (or its own
+ * cross-rank barrier).  No counterpart in the reference. */
+int htp_b200_mul_mat_gather_step(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
+                                 const void *weight, int m, int k, int n, int weight_type, int act_type,
+                                 uint32_t *const *flags, const uint32_t *local_flags, uint32_t epoch, void *stream);
 
 /* Enqueues on `stream` a bounded wait until flags[r] has reached `epoch` for r = 0 .. n-1 (n <= 32):
  * every rank's band of this step has landed in this GPU's copy.  If a flag does not arrive within

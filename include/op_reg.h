@@ -10,9 +10,13 @@
  *     "A32" ops, but the lm_head / prefill workloads feed fp16 activations);
  *   - HTP_OPS_COUNT therefore grows from 6 to 8; HTP_OPS_REFERENCE_COUNT keeps the old value.
  *
- * Weight layout consumed by indices 2, 3, 6, 7 in this library: standard ggml block_q4_0 /
- * block_q8_0 (quants.h), N rows of K/32 consecutive blocks, the layout walked by the
- * reference's dequantize_common_weight_* routines (src/dsp/ops/mat_mul.c:572-640).
+ * Weight layout consumed by indices 2, 3, 4, 6, 7 in this library: standard ggml block_q4_0 /
+ * block_q8_0 (quants.h; index 4 = the Q4_0 block with the IQ4_NL value table), N rows of K/32
+ * consecutive blocks, the layout walked by the reference's dequantize_common_weight_* routines
+ * (src/dsp/ops/mat_mul.c:572-640); with the library option "permuted_weights" indices 2, 3, 4 read the
+ * reference-private permuted super-blocks instead.  Index 1 reads fp16 weights in the reference's
+ * 32 x 32 tile order (src/host/test.c:303-313).  Index 0 is RMSNorm.  Index 5 (FlashAttention) is
+ * not built: the dispatcher answers -1.
  */
 #ifndef HTP_OPS_OP_REG_H
 #define HTP_OPS_OP_REG_H

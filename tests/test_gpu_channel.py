@@ -138,3 +138,50 @@ def test_chained_ops_in_one_message(dev, oracle, wl):
     assert oracle.error_metrics(h, oracle.mul_mat_f64(x, wa, 512, 2))["max_rel_to_max"] <= 1e-5
     assert oracle.error_metrics(y, ref)["max_rel_to_max"] <= 1e-5
     dev.free(fwa, fwb, fx, fh, fy)
+
+
+def test_direct_calls_while_messages_are_in_flight(dev, oracle, wl):
+    """The reference's host test mixes FastRPC-style direct calls with channel messages in one session
+    (src/host/test.c).  A thread keeps posting messages of several matmuls while this thread issues
+    htp_ops_rpc_rms_norm_f32 and execute_op_simple: the two share the session's operator state, which
+    one lock serialises - every request state is 0 and every result stays right."""
+    import threading
+    lib, pkg = dev.lib, dev.pkg
+    op = pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32
+    shapes = [(1024, 256), (2048, 96), (512, 512), (1024, 64)]
+    cases = [wl.random_case(2100 + i, 2, False, 2, k, n) for i, (k, n) in enumerate(shapes)]
+    fw = [dev.put(wq) for wq, _ in cases]
+    fx = [dev.put(x) for _, x in cases]
+    fy = [dev.buf(2 * n * 4) for _, n in shapes]
+    reqs = [pkg.pack_matmul_request(op, (fy[i], 0), (fx[i], 0), (fw[i], 0), 2, k, n) for i, (k, n) in enumerate(shapes)]
+    src = (np.random.default_rng(5).random((16, 1024), dtype=np.float32) * 40 - 20).astype(np.float32)
+    fsrc, fdst = dev.put(src), dev.buf(src.nbytes)
+    wd, xd = wl.random_case(2200, 8, False, 3, 1024, 160)
+    fwd, fxd, fyd = dev.put(wd), dev.put(xd), dev.buf(3 * 160 * 4)
+    chan = pkg.MessageChannel(4096)
+    bad = []
+
+    def poster():
+        for _ in range(60):
+            st = chan.submit(reqs)
+            if st != [0] * len(reqs):
+                bad.append(st)
+    t = threading.Thread(target=poster)
+    try:
+        t.start()
+        for _ in range(60):
+            assert lib.htp_ops_rpc_rms_norm_f32(fdst, 0, fsrc, 0, 1024, 16) == 0
+            assert dev.execute(pkg.HTP_OPS_MAT_MUL_PERMUTED_W8D16A32, (fyd, 0), (fxd, 0), (fwd, 0), 3, 1024, 160) == 0
+    finally:
+        t.join()
+        chan.close()
+    assert not bad, bad[:2]
+    for i, ((k, n), (wq, x)) in enumerate(zip(shapes, cases)):
+        e = oracle.error_metrics(dev.get(fy[i], (2, n)), oracle.mul_mat_f64(x, wq, n, 2))
+        assert e["max_rel_to_max"] <= 1e-5, e
+    e = oracle.error_metrics(dev.get(fyd, (3, 160)), oracle.mul_mat_f64(xd, wd, 160, 8))
+    assert e["max_rel_to_max"] <= 1e-5, e
+    got = dev.get(fdst, src.shape)
+    ref = src / np.sqrt((src.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
+    assert np.abs(got - ref).max() <= 1e-5
+    dev.free(*fw, *fx, *fy, fsrc, fdst, fwd, fxd, fyd)

@@ -32,7 +32,9 @@ def _run(dev, fn, x, wq, n, wtype):
 def test_static_scratch_entry_point_matches_allocating_one(dev, oracle, wl):
     lib = dev.lib
     # two different shapes back to back: tiles cut by CTA boundaries in both, different formats
-    cases = [(2, False, 1, 4096, 1024), (8, True, 5, 2048, 4000 // 32 * 32)]
+    # (the third and fourth: fp32 tokens on the wide integer path, which both entry points plan alike)
+    cases = [(2, False, 1, 4096, 1024), (8, True, 5, 2048, 4000 // 32 * 32), (2, False, 8, 4096, 1024),
+             (8, False, 7, 2048, 992), (20, False, 3, 1024, 224)]
     for wtype, act_f16, m, k, n in cases:
         wq, x = wl.random_case(500 + m, wtype, act_f16, m, k, n)
         ref = _run(dev, lib.htp_b200_mul_mat, x, wq, n, wtype)
@@ -53,6 +55,19 @@ def test_static_scratch_entry_point_rejects_what_it_cannot_hold(dev, wl):
     assert fn(y, a, w, 9, 256, 32, 2, 0, st) == -3  # m beyond the decode range
     assert fn(y, a, w, 1, 96, 32, 2, 0, st) == -3  # k not a multiple of 256
     assert fn(y, a, w, 8, 14336, 32, 2, 0, st) == -3  # fragments of the whole k do not fit
+    # the limits the header states: one K range only.  Q4_0, fp32: k = 14336 fits at m = 1, not at m = 2;
+    # three to eight tokens: k <= 4352 (Q4_0, IQ4_NL) / 4608 (Q8_0)
+    big = dev.buf(14336 // 32 * 34 * 32)
+    wb = lib.htp_buf_ptr(big)
+    xb = lib.htp_buf_ptr(dev.buf(8 * 14336 * 4))
+    assert fn(y, xb, wb, 1, 14336, 32, 2, 0, st) == 0
+    assert fn(y, xb, wb, 2, 14336, 32, 2, 0, st) == -3
+    assert fn(y, xb, wb, 2, 9472, 32, 2, 0, st) == 0
+    assert fn(y, xb, wb, 8, 4352, 32, 2, 0, st) == 0
+    assert fn(y, xb, wb, 8, 4608, 32, 2, 0, st) == -3
+    assert fn(y, xb, wb, 8, 4608, 32, 8, 0, st) == 0
+    assert fn(y, xb, wb, 8, 4864, 32, 8, 0, st) == -3
+    assert fn(y, xb, wb, 3, 4352, 32, 20, 1, st) == 0
     assert fn(y, a, w, 1, 256, 40, 2, 0, st) == -1  # the ordinary argument checks still apply
     assert fn(None, a, w, 1, 256, 32, 2, 0, st) == -1
     assert fn(y, a, w, 1, 256, 32, 2, 0, st) == 0
