@@ -60,9 +60,9 @@ struct Cfg {
   static constexpr bool WIDE     = MPAD == 8;
   // Q4_0 / IQ4_NL with one or two tokens run on the INTEGER tensor-core path too: nibbles are
   // masked into unsigned bytes (3 instructions per 8 weights instead of 9 for exact fp16), the
-  // activations are four signed base-128 digits of a 28-bit fixed-point value (column = 4 m +
-  // digit), one m16n8k32 MMA covers a whole block, and the -8 offset of the format comes in
-  // through the MMA's accumulator input.
+  // activations are four signed base-256 digits of a 31-bit fixed-point value (column = 4 m +
+  // digit), one m16n8k32 MMA covers a whole block, and the -8 offset of the format comes out with
+  // the float bias of the integer result.
   static constexpr bool I8       = WIDE || ((WT == kQ4 || WT == kIQ4) && MPAD <= 2);
   static constexpr bool DIGCOL   = I8 && !WIDE;  // MMA column = 4 m + digit
   static_assert(MPAD == 1 || MPAD == 2 || MPAD == 8, "token paddings built: 1, 2, 8");
@@ -126,135 +126,100 @@ __device__ __forceinline__ long long item_owner(long long i, long long T, long l
 constexpr int   kMagicBits = 0x4B400000;
 constexpr float kMagic     = 12582912.0f;
 
-// Integer path: token m, scaled by a power of two so that |x| < 1, becomes the fixed-point integer
-// X = round(x * 2^27) = D3 * 2^21 + D2 * 2^14 + D1 * 2^7 + D0 with signed digits in [-64, 64];
-// digit d of token m is MMA column 4 m + d.  Per block and column the accumulator input
-// kMagicBits - 8 * sum_k D turns the MMA result into the float 12582912 + sum_k (q_k - 8) D_k.
-template <int WT, bool A16, int MPAD>
-__device__ void build_x_frags_i8(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
-  using C = Cfg<WT, A16, MPAD>;
-  if (tid < 8) {
-    sm->tok_amax_bits[tid] = 0;
-  }
-  named_bar_sync(1, kConsumerThreads);
-  const int klen = p.kblocks * 32;
-  auto      xval = [&](int m, int k) -> float {
-    const long long i = (long long) m * p.x_stride + p.x_k_off + k;
-    if constexpr (A16) {
-      return __half2float(static_cast<const __half *>(p.x)[i]);
-    } else {
-      return static_cast<const float *>(p.x)[i];
-    }
-  };
-  for (int m = 0; m < p.M; ++m) {
-    float a = 0.0f;
-    for (int k = tid; k < klen; k += kConsumerThreads) {
-      a = fmaxf(a, fabsf(xval(m, k)));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-    }
-    if ((tid & 31) == 0) {
-      atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
-    }
-  }
-  named_bar_sync(1, kConsumerThreads);
-  if (tid < 8) {
-    const int bits = sm->tok_amax_bits[tid];
-    int       sh   = ((bits >> 23) & 0xff) - 127 + 1;  // amax < 2^sh
-    sh             = sh < -100 ? -100 : (sh > 100 ? 100 : sh);
-    sm->tok_scale[tid] = __int_as_float((127 + 27 - sh) << 23);  // x -> fixed point
-    sm->tok_inv[tid]   = __int_as_float((127 + sh) << 23);
-  }
-  named_bar_sync(1, kConsumerThreads);
+// Integer paths.  Token m, scaled by a power of two so that |x| < 1, becomes a fixed-point integer
+// that is split into signed base-256 digits, one MMA column each:
+//   one or two tokens (Q4_0, IQ4_NL):  X = round(x * 2^30) = D3 * 2^24 + D2 * 2^16 + D1 * 2^8 + D0,
+//     column = 4 m + digit;
+//   wide path (three to eight tokens, every format):  X = round(x * 2^22) = D2 * 2^16 + D1 * 2^8 + D0,
+//     MMA number d of a block = digit d of the eight tokens (column = token), so the three results
+//     of one (row, token) pair sit in the same lane.
+// D0 .. are in [-128, 127], the top digit within [-65, 65].  The digits are simply the bytes of
+// (X + 0x8080..) ^ 0x8080..: adding 128 per lower digit makes the lower bytes unsigned digits + 128
+// with the carries where they belong, the xor takes the 128 off again as a signed byte.
+// The MMA starts from the integer kMagicBits in every accumulator, so its int32 result is the bit
+// pattern of the float 12582912 + sum_k q_k D_k exactly; per block and column the fragments carry
+// the float offset -12582912 - 8 * sum_k D (Q4_0: value = nibble - 8) that one packed add removes.
+// The rounding of x - at most 2^-31 (2^-23 on the wide path) of the power of two above the token's
+// largest magnitude per element - is the only inexact step.
+constexpr int kWideShift   = 22;
+constexpr int kNarrowShift = 30;
 
-  const int n_units = p.kblocks * 4;  // (block, t): a multiple of 32, so warps stay whole
-  for (int u = tid; u < n_units; u += kConsumerThreads) {
-    const int b = u >> 2, t = u & 3;
-    uint2    *dst = frags + (size_t) b * C::FRAG_U2;
-    for (int m = 0; m < MPAD; ++m) {
-      // this lane position multiplies block elements 4t .. 4t+3 (register 0) and 16+4t .. (register 1)
-      uint32_t dig[4][2] = {};
-      int      sum[4]    = { 0, 0, 0, 0 };
-      if (m < p.M) {
-        const float sc = sm->tok_scale[m];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // block element that byte i of A register h (rows g / g + 8) of this lane position holds
-            const int e = WT == kIQ4 ? iq4nl_word_elem(t, h, i) : 16 * h + 4 * t + i;
-            int       r = __float2int_rn(xval(m, b * 32 + e) * sc);
-#pragma unroll
-            for (int d = 0; d < 4; ++d) {
-              const int dv = d < 3 ? ((r + 64) & 127) - 64 : r;
-              r            = (r - dv) >> 7;
-              sum[d] += dv;
-              dig[d][h] |= (uint32_t) (dv & 0xff) << (8 * i);
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        dst[(4 * m + d) * 4 + t] = make_uint2(dig[d][0], dig[d][1]);
-        int sd                   = sum[d];
-        sd += __shfl_xor_sync(0xffffffffu, sd, 1);
-        sd += __shfl_xor_sync(0xffffffffu, sd, 2);
-        if (t == 0) {
-          // (Q4_0: value = nibble - 8; IQ4_NL: the table values are used as they are)
-          reinterpret_cast<int *>(dst + C::CIN_OFF)[4 * m + d] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
-        }
-      }
-    }
+// Elements k0 .. k0 + 3 and k0 + 16 .. k0 + 19 of token m as floats (two 16- or 8-byte loads).
+template <bool A16>
+__device__ __forceinline__ void load_x8(const GemvArgs &p, int m, int k0, float (&v)[8]) {
+  const long long i = (long long) m * p.x_stride + p.x_k_off + k0;
+  if constexpr (A16) {
+    const __half *x = static_cast<const __half *>(p.x) + i;
+    const uint2   a = *reinterpret_cast<const uint2 *>(x), b = *reinterpret_cast<const uint2 *>(x + 16);
+    const float2  a0 = __half22float2(u32_as_h2(a.x)), a1 = __half22float2(u32_as_h2(a.y));
+    const float2  b0 = __half22float2(u32_as_h2(b.x)), b1 = __half22float2(u32_as_h2(b.y));
+    v[0] = a0.x, v[1] = a0.y, v[2] = a1.x, v[3] = a1.y, v[4] = b0.x, v[5] = b0.y, v[6] = b1.x, v[7] = b1.y;
+  } else {
+    const float *x = static_cast<const float *>(p.x) + i;
+    const float4 a = *reinterpret_cast<const float4 *>(x), b = *reinterpret_cast<const float4 *>(x + 16);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
   }
 }
 
-// Wide integer path (three to eight tokens): token m, scaled by a power of two so that |x| < 1, is
-// the fixed-point integer X = round(x * 2^22) = D2 * 2^16 + D1 * 2^8 + D0 with signed digits (D0, D1
-// in [-128, 127], |D2| <= 65).  Per block: three MMA operand sets, set d = digit d of the eight
-// tokens (column = token), then the 24 accumulator inputs (kMagicBits, less 8 * sum_k D for Q4_0's
-// offset).  The rounding of x, at most 2^-23 of the power of two above the token's largest
-// magnitude per element, is the only inexact step of the path.
-constexpr int kWideShift = 22;
-
-template <int WT, bool A16>
-__device__ void build_x_frags_wide(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
-  using C = Cfg<WT, A16, 8>;
+// Per-token largest magnitude over the launch's K range -> tok_amax_bits (16-byte loads, every
+// token's loads independent of the others').
+template <bool A16>
+__device__ __forceinline__ void token_amax(const GemvArgs &p, Smem *sm, int tid) {
   if (tid < 8) {
     sm->tok_amax_bits[tid] = 0;
   }
   named_bar_sync(1, kConsumerThreads);
-  const int klen = p.kblocks * 32;
-  auto      xval = [&](int m, int k) -> float {
-    const long long i = (long long) m * p.x_stride + p.x_k_off + k;
-    if constexpr (A16) {
-      return __half2float(static_cast<const __half *>(p.x)[i]);
-    } else {
-      return static_cast<const float *>(p.x)[i];
-    }
-  };
-  for (int m = 0; m < p.M; ++m) {
-    float a = 0.0f;
-    for (int k = tid; k < klen; k += kConsumerThreads) {
-      a = fmaxf(a, fabsf(xval(m, k)));
-    }
+  const int nvec = p.kblocks * 32 / (A16 ? 8 : 4);  // 16-byte pieces per token
+  float     amax[8];
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  for (int m = 0; m < 8; ++m) {
+    amax[m] = 0.f;
+    if (m < p.M) {
+      for (int c = tid; c < nvec; c += kConsumerThreads) {
+        const long long i = (long long) m * p.x_stride + p.x_k_off;
+        if constexpr (A16) {
+          const uint4 q = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(p.x) + i + 8 * c);
+          __half2     h = __hmax2(__habs2(u32_as_h2(q.x)), __habs2(u32_as_h2(q.y)));
+          h             = __hmax2(h, __hmax2(__habs2(u32_as_h2(q.z)), __habs2(u32_as_h2(q.w))));
+          amax[m]       = fmaxf(amax[m], fmaxf(__low2float(h), __high2float(h)));
+        } else {
+          const float4 q = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.x) + i + 4 * c);
+          amax[m] = fmaxf(amax[m], fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w))));
+        }
+      }
     }
-    if ((tid & 31) == 0) {
-      atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
+  }
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    if (m < p.M) {  // (uniform over the block)
+      float a = amax[m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+      }
+      if ((tid & 31) == 0) {
+        atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
+      }
     }
   }
   named_bar_sync(1, kConsumerThreads);
+}
+
+template <int WT, bool A16, int MPAD>
+__device__ void build_x_frags_int(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
+  using C = Cfg<WT, A16, MPAD>;
+  constexpr int      ND    = C::WIDE ? 3 : 4;                       // digits per token
+  constexpr int      SHIFT = C::WIDE ? kWideShift : kNarrowShift;  // fixed-point position
+  constexpr int      NTOK  = C::WIDE ? 8 : MPAD;
+  constexpr uint32_t BIAS  = C::WIDE ? 0x00008080u : 0x00808080u;  // 128 per digit below the top one
+  token_amax<A16>(p, sm, tid);
   if (tid < 8) {
     const int bits = sm->tok_amax_bits[tid];
     int       sh   = ((bits >> 23) & 0xff) - 127 + 1;  // amax < 2^sh
-    sh             = sh < -100 ? -100 : (sh > 100 ? 100 : sh);
-    sm->tok_scale[tid] = __int_as_float((127 + kWideShift - sh) << 23);  // x -> fixed point
-    sm->tok_inv[tid]   = __int_as_float((127 + sh - kWideShift) << 23);
+    sh             = sh < -90 ? -90 : (sh > 90 ? 90 : sh);
+    sm->tok_scale[tid] = __int_as_float((127 + SHIFT - sh) << 23);  // x -> fixed point
+    // wide path: the digit weights 256^d are applied as they are, the common 2^-22 here
+    sm->tok_inv[tid]   = __int_as_float((127 + sh - (C::WIDE ? SHIFT : 0)) << 23);
   }
   named_bar_sync(1, kConsumerThreads);
 
@@ -262,38 +227,58 @@ __device__ void build_x_frags_wide(const GemvArgs &p, Smem *sm, uint2 *frags, in
   for (int u = tid; u < n_units; u += kConsumerThreads) {
     const int b = u >> 2, t = u & 3;
     uint2    *dst = frags + (size_t) b * C::FRAG_U2;
-    for (int m = 0; m < 8; ++m) {
-      // this lane position multiplies block elements 4t .. 4t+3 (register 0) and 16+4t .. (register 1)
-      uint32_t dig[3][2] = {};
-      int      sum[3]    = { 0, 0, 0 };
-      if (m < p.M) {
-        const float sc = sm->tok_scale[m];
+    // this lane position multiplies block elements 4t .. 4t+3 and 16+4t .. 19+4t of every token;
+    // the loads of (up to) four tokens are in flight together
+    constexpr int TG = NTOK < 4 ? NTOK : 4;
+#pragma unroll 1
+    for (int m0 = 0; m0 < NTOK; m0 += TG) {
+      float xv[TG][8];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+      for (int j = 0; j < TG; ++j) {
+        if (m0 + j < p.M) {
+          load_x8<A16>(p, m0 + j, b * 32 + 4 * t, xv[j]);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // block element that byte i of A register h (rows g / g + 8) of this lane position holds
-            const int e = WT == kIQ4 ? iq4nl_word_elem(t, h, i) : 16 * h + 4 * t + i;
-            int       r = __float2int_rn(xval(m, b * 32 + e) * sc);
-#pragma unroll
-            for (int d = 0; d < 3; ++d) {
-              const int dv = d < 2 ? ((r + 128) & 255) - 128 : r;
-              r            = (r - dv) >> 8;
-              sum[d] += dv;
-              dig[d][h] |= (uint32_t) (dv & 0xff) << (8 * i);
-            }
+          for (int i = 0; i < 8; ++i) {
+            xv[j][i] = 0.f;
           }
         }
       }
 #pragma unroll
-      for (int d = 0; d < 3; ++d) {
-        dst[(8 * d + m) * 4 + t] = make_uint2(dig[d][0], dig[d][1]);
-        int sd                   = sum[d];
-        sd += __shfl_xor_sync(0xffffffffu, sd, 1);
-        sd += __shfl_xor_sync(0xffffffffu, sd, 2);
-        if (t == 0) {
-          // (Q4_0: value = nibble - 8; Q8_0 and IQ4_NL bytes are the values themselves)
-          reinterpret_cast<int *>(dst + C::CIN_OFF)[8 * d + m] = kMagicBits - (WT == kQ4 ? 8 * sd : 0);
+      for (int j = 0; j < TG; ++j) {
+        const int   m  = m0 + j;
+        const float sc = sm->tok_scale[m];
+        // y[h][i]: the digits of the element that byte i of A register h (rows g / g + 8) of this
+        // lane position multiplies - block element 16 h + 4 t + i (Q4_0, Q8_0) or
+        // iq4nl_word_elem(t, h, i) = 4 t + 2 h + (i >> 1) + 16 (i & 1) - one digit per byte
+        uint32_t y[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int src = WT == kIQ4 ? 4 * (i & 1) + 2 * h + (i >> 1) : 4 * h + i;
+            y[h][i]       = ((uint32_t) __float2int_rn(xv[j][src] * sc) + BIAS) ^ BIAS;
+          }
+        }
+#pragma unroll
+        for (int d = 0; d < ND; ++d) {
+          // byte d of the four elements of each register, in element order
+          uint32_t w[2];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t lo = __byte_perm(y[h][0], y[h][1], 0x0040 + 0x0011 * d);  // bytes d of elements 0, 1
+            const uint32_t hi = __byte_perm(y[h][2], y[h][3], 0x0040 + 0x0011 * d);  // bytes d of elements 2, 3
+            w[h]              = __byte_perm(lo, hi, 0x5410);
+          }
+          const int col    = C::WIDE ? 8 * d + m : 4 * m + d;
+          dst[col * 4 + t] = make_uint2(w[0], w[1]);
+          int sd           = __dp4a((int) w[0], 0x01010101, __dp4a((int) w[1], 0x01010101, 0));  // sum of the 8 digits
+          sd += __shfl_xor_sync(0xffffffffu, sd, 1);
+          sd += __shfl_xor_sync(0xffffffffu, sd, 2);
+          if (t == 0) {
+            // (Q4_0: value = nibble - 8; Q8_0 and IQ4_NL bytes are the values themselves)
+            reinterpret_cast<float *>(dst + C::CIN_OFF)[col] = -kMagic - (WT == kQ4 ? 8.f * (float) sd : 0.f);
+          }
         }
       }
     }
@@ -303,37 +288,14 @@ __device__ void build_x_frags_wide(const GemvArgs &p, Smem *sm, uint2 *frags, in
 template <int WT, bool A16, int MPAD>
 __device__ void build_x_frags(const GemvArgs &p, Smem *sm, uint2 *frags, int tid) {
   using C = Cfg<WT, A16, MPAD>;
-  if constexpr (C::WIDE) {
-    build_x_frags_wide<WT, A16>(p, sm, frags, tid);
-    return;
-  }
   if constexpr (C::I8) {
-    build_x_frags_i8<WT, A16, MPAD>(p, sm, frags, tid);
+    build_x_frags_int<WT, A16, MPAD>(p, sm, frags, tid);
     return;
   }
   if constexpr (!A16) {
     // per-token power-of-two normalisation: the largest |x| of a token lands in [2^14, 2^15), so
     // fp16(x) neither overflows nor drops into the subnormal range for small-magnitude tokens
-    if (tid < 8) {
-      sm->tok_amax_bits[tid] = 0;
-    }
-    named_bar_sync(1, kConsumerThreads);
-    const float *x    = static_cast<const float *>(p.x);
-    const int    klen = p.kblocks * 32;
-    for (int m = 0; m < p.M; ++m) {
-      float a = 0.0f;
-      for (int k = tid; k < klen; k += kConsumerThreads) {
-        a = fmaxf(a, fabsf(x[(long long) m * p.x_stride + p.x_k_off + k]));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-      }
-      if ((tid & 31) == 0) {
-        atomicMax(&sm->tok_amax_bits[m], __float_as_int(a));
-      }
-    }
-    named_bar_sync(1, kConsumerThreads);
+    token_amax<false>(p, sm, tid);
     if (tid < 8) {
       const int bits = sm->tok_amax_bits[tid];
       const int e    = ((bits >> 23) & 0xff) - 127;  // floor(log2(amax))
@@ -451,10 +413,9 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
 }
 
 // Integer path: one Q4_0 block x 16 rows = ONE m16n8k32 MMA (unsigned nibbles x signed digits,
-// int32 accumulate starting from the column's accumulator input).
+// int32 accumulate starting from kMagicBits).  off2: the float offsets of columns 2t, 2t + 1.
 template <int WT, bool A16, int MPAD, bool EVEN>
-__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint2 cin, int t, uint64_t neg_magic2,
-                                                float (&acc)[4]) {
+__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint64_t off2, int t, float (&acc)[4]) {
   using C = Cfg<WT, A16, MPAD>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
   uint32_t       qa, qb;
@@ -472,21 +433,21 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
     iq4nl_unpack_word(qa, a0, a2);
     iq4nl_unpack_word(qb, a1, a3);
     asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(kMagicBits));
   } else {
     // byte i of the word: low nibble = element 4t + i, high nibble = element 16 + 4t + i
     a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
     a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
     asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(cin.x), "r"(cin.y));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(kMagicBits));
   }
   const float da = lds_scale(ra);
   const float db = lds_scale(rb);
-  // int bits -> float: subtract the bias, two results per instruction (packed fp32 add)
+  // int bits -> float: add the offset, two results per instruction (packed fp32 add)
   float f0, f1, f2, f3;
   asm("{\n\t.reg .b64 p, q;\n\t"
       "mov.b64 p, {%4, %5};\n\t"
@@ -496,7 +457,7 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
       "mov.b64 {%0, %1}, p;\n\t"
       "mov.b64 {%2, %3}, q;\n\t}"
       : "=f"(f0), "=f"(f1), "=f"(f2), "=f"(f3)
-      : "r"(d0), "r"(d1), "r"(d2), "r"(d3), "l"(neg_magic2));
+      : "r"(d0), "r"(d1), "r"(d2), "r"(d3), "l"(off2));
   acc[0] = fmaf(da, f0, acc[0]);
   acc[1] = fmaf(da, f1, acc[1]);
   acc[2] = fmaf(db, f2, acc[2]);
@@ -512,22 +473,22 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-// acc += d2 * (bits as floats - 12582912), both lanes: the integer MMA results of one row leave
-// their float bias behind and are scaled by the row's block scale
-__device__ __forceinline__ void scale_add2(uint64_t &acc, int b0, int b1, uint64_t d2, uint64_t neg_magic2) {
+// acc += d2 * (bits as floats + off2), both lanes: the integer MMA results of one row leave their
+// float bias (and Q4_0's -8 offset) behind and are scaled by the row's block scale
+__device__ __forceinline__ void scale_add2(uint64_t &acc, int b0, int b1, uint64_t d2, uint64_t off2) {
   asm("{\n\t.reg .b64 p;\n\t"
       "mov.b64 p, {%1, %2};\n\t"
       "add.rn.f32x2 p, p, %4;\n\t"
       "fma.rn.f32x2 %0, %3, p, %0;\n\t}"
       : "+l"(acc)
-      : "r"(b0), "r"(b1), "l"(d2), "l"(neg_magic2));
+      : "r"(b0), "r"(b1), "l"(d2), "l"(off2));
 }
 
 // Wide integer path: one block x 16 rows x eight tokens = THREE m16n8k32 MMAs on the same weight
 // registers, one per activation digit.  acc[d][0]: row g, tokens 2t and 2t + 1 of digit d; acc[d][1]: row g + 8.
 template <int WT, bool A16, bool EVEN>
-__device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], const uint2 (&cin)[3], int t,
-                                                  uint64_t neg_magic2, uint64_t (&acc)[3][2]) {
+__device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], const uint64_t (&off2)[3],
+                                                  int t, uint64_t (&acc)[3][2]) {
   using C = Cfg<WT, A16, 8>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
   uint32_t       a0, a1, a2, a3;
@@ -564,22 +525,24 @@ __device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2
   const float    da  = lds_scale(ra);
   const float    db  = lds_scale(rb);
   const uint64_t da2 = pack2(da, da), db2 = pack2(db, db);
+  // the three MMAs first, then their results: nothing waits on an MMA that was only just issued
+  int r[3][4];
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
-    int r0, r1, r2, r3;
     if constexpr (WT == kQ4) {
-      asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(cin[d].x), "r"(cin[d].y));
+      asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+          : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
+          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(kMagicBits));
     } else {
-      asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(cin[d].x), "r"(cin[d].y));
+      asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+          : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
+          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(kMagicBits));
     }
-    scale_add2(acc[d][0], r0, r1, da2, neg_magic2);
-    scale_add2(acc[d][1], r2, r3, db2, neg_magic2);
+  }
+#pragma unroll
+  for (int d = 0; d < 3; ++d) {
+    scale_add2(acc[d][0], r[d][0], r[d][1], da2, off2[d]);
+    scale_add2(acc[d][1], r[d][2], r[d][3], db2, off2[d]);
   }
 }
 
@@ -652,31 +615,32 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
   for (int i = 0; i < C::BPW; ++i) {
     const bool even = (((C::BPW % 2 == 0) ? 0 : par) + i) % 2 == 0;
     if constexpr (C::WIDE) {
-      uint2 bf[3], cin[3];
+      uint2    bf[3];
+      uint64_t off2[3];
 #pragma unroll
       for (int d = 0; d < 3; ++d) {
-        bf[d]  = fp[i * C::FRAG_U2 + d * 32];
-        cin[d] = cp[i * C::FRAG_U2 + d * 4];
+        bf[d]   = fp[i * C::FRAG_U2 + d * 32];
+        off2[d] = WT == kQ4 ? *reinterpret_cast<const uint64_t *>(cp + i * C::FRAG_U2 + d * 4) : neg_magic2;
       }
 #pragma unroll
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if (even) {
-          block_rows16_wide<WT, A16, true>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+          block_rows16_wide<WT, A16, true>(ra, bf, off2, t, acc.v[rg]);
         } else {
-          block_rows16_wide<WT, A16, false>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+          block_rows16_wide<WT, A16, false>(ra, bf, off2, t, acc.v[rg]);
         }
       }
     } else if constexpr (C::I8) {
-      const uint2 bf  = fp[i * C::FRAG_U2];
-      const uint2 cin = cp[i * C::FRAG_U2];
+      const uint2    bf   = fp[i * C::FRAG_U2];
+      const uint64_t off2 = WT == kQ4 ? *reinterpret_cast<const uint64_t *>(cp + i * C::FRAG_U2) : neg_magic2;
 #pragma unroll
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if (even) {
-          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, off2, t, acc.v[rg]);
         } else {
-          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, cin, t, neg_magic2, acc.v[rg]);
+          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, off2, t, acc.v[rg]);
         }
       }
     } else if constexpr (WT != kIQ4) {
@@ -820,9 +784,9 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
   // v.x, v.y: row g, columns 2t, 2t + 1;  v.z, v.w: row g + 8, same columns
   float lo0 = v.x, lo1 = v.y, hi0 = v.z, hi1 = v.w;
   if constexpr (C::DIGCOL) {
-    // column 2t + c = 4 m + digit: weigh the digits (2^(7 digit - 27)) and add the four columns
-    const float w0 = __int_as_float((127 + 7 * ((t & 1) << 1) - 27) << 23);
-    const float w1 = __int_as_float((127 + 7 * (((t & 1) << 1) | 1) - 27) << 23);
+    // column 2t + c = 4 m + digit: weigh the digits (2^(8 digit - 30)) and add the four columns
+    const float w0 = __int_as_float((127 + 8 * ((t & 1) << 1) - kNarrowShift) << 23);
+    const float w1 = __int_as_float((127 + 8 * (((t & 1) << 1) | 1) - kNarrowShift) << 23);
     lo0 = lo0 * w0 + lo1 * w1;
     hi0 = hi0 * w0 + hi1 * w1;
     lo0 += __shfl_xor_sync(0xffffffffu, lo0, 1);
