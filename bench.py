@@ -299,7 +299,9 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
                                       ("q8_0_gemv_32768x4096_m8", wl.TYPE_Q8_0, False, 8, 4096, 32768),
                                       ("iq4_nl_gemv_65536x4096_m1", wl.TYPE_IQ4_NL, False, 1, 4096, 65536),
                                       ("iq4_nl_gemv_65536x4096_m8", wl.TYPE_IQ4_NL, False, 8, 4096, 65536),
-                                      ("iq4_nl_prefill_14336x4096_m512", wl.TYPE_IQ4_NL, True, 512, 4096, 14336)):
+                                      ("iq4_nl_prefill_14336x4096_m512", wl.TYPE_IQ4_NL, True, 512, 4096, 14336),
+                                      ("q4_0_prefill_f32act_14336x4096_m512", wl.TYPE_Q4_0, False, 512, 4096, 14336),
+                                      ("q4_0_prefill_f32act_14336x4096_m32", wl.TYPE_Q4_0, False, 32, 4096, 14336)):
         op = wl.MatMul(name, wtype, a16, k, n)
         copies = 2 if m <= 8 else 1
         ws = [blocks(wtype, k, n) for _ in range(copies)]

@@ -19,7 +19,14 @@ namespace htp {
 
 int g_opt_pdl           = getenv("HTP_OPS_NO_PDL") ? 0 : 1;  // programmatic dependent launch
 int g_opt_force_generic = 0;
-int g_opt_gemm_min_m     = 64;  // fp16 activations with at least this many tokens go to the tensor-core GEMM
+// Matmuls with at least this many tokens go to the tensor-core GEMM.  fp32 activations only from
+// kGemmMinMF32 tokens on: up to there two passes of the decode kernel keep them exact.
+int           g_opt_gemm_min_m = 9;
+constexpr int kGemmMinMF32     = 17;
+// fp32 activations reach the GEMM as fp16 copies (as in the reference, mat_mul.c:89-128).  1 = keep
+// fp32-activation matmuls of any token count on the decode kernel (exact weights, fixed-point
+// activations: 1e-5 instead of 1e-3, at one pass over the weights per eight tokens).
+int g_opt_a32_exact      = 0;
 int g_opt_gemv_whole_tiles = getenv("HTP_OPS_NO_WHOLE_TILES") ? 0 : 1;  // small mat-vecs: one whole tile per CTA
 // Cut the GEMM's work into equal K ranges when the tile count is uneven.  Off by default: on the
 // shapes measured (112 to 4008 tiles on 74 CTA pairs) the whole-tile schedule was 1-9 % faster -
@@ -119,6 +126,31 @@ float *gemm_scratch(DeviceCtx *ctx, StreamScratch *sc) {
   return sc->gemm_part;
 }
 
+// Room for m x k fp16 activations and (after them) m per-token scales on this stream; grown when a
+// larger matmul arrives (the stream is drained first: earlier GEMMs may still read the old area).
+uint8_t *act16_scratch(StreamScratch *sc, cudaStream_t st, int m, int k, float **scales) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  const size_t mpad = ((size_t) m + 255) & ~(size_t) 255;
+  const size_t xb   = (mpad * (size_t) k * 2 + 255) & ~(size_t) 255;
+  const size_t need = xb + mpad * sizeof(float);
+  if (need > sc->act16_bytes) {
+    if (sc->act16) {
+      cudaStreamSynchronize(st);
+      cudaFree(sc->act16);
+      sc->act16 = nullptr, sc->act16_bytes = 0;
+    }
+    const size_t bytes = need + need / 2;
+    void        *base  = nullptr;
+    if (cudaMalloc(&base, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    sc->act16 = static_cast<uint8_t *>(base), sc->act16_bytes = bytes;
+  }
+  *scales = reinterpret_cast<float *>(sc->act16 + xb);
+  return sc->act16;
+}
+
 void release_all_scratch() {
   std::lock_guard<std::mutex> lk(g_mu);
   int                         cur = -1;
@@ -127,6 +159,7 @@ void release_all_scratch() {
     cudaSetDevice(kv.first.first);
     cudaFree(kv.second.partials);
     cudaFree(kv.second.gemm_part);
+    cudaFree(kv.second.act16);
     cudaFreeHost(kv.second.err_host);
   }
   g_scratch.clear();
@@ -301,8 +334,8 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     count_launch();
     return 0;
   }
-  if (a16 && m >= g_opt_gemm_min_m) {
-    // prefill: tensor-core GEMM
+  if (m >= g_opt_gemm_min_m && (a16 || (!g_opt_a32_exact && m >= kGemmMinMF32))) {
+    // prefill: tensor-core GEMM; fp32 activations go in as per-token scaled fp16 copies
     StreamScratch *sc = stream_scratch(ctx, st);
     if (!sc) {
       return -2;
@@ -310,6 +343,16 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     GemmArgs a = {};
     a.y = static_cast<float *>(dst), a.x = activation, a.w = static_cast<const uint8_t *>(weight);
     a.M = m, a.N = n, a.K = k, a.err = sc->err;
+    if (!a16) {
+      float   *scales = nullptr;
+      uint8_t *x16    = act16_scratch(sc, st, m, k, &scales);
+      if (!x16 || act_f32_to_f16_launch(x16, scales, static_cast<const float *>(activation), m, k, st) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
+      }
+      count_launch();
+      a.x = x16, a.tok_scale = scales;
+    }
     a.part = g_opt_gemm_split ? gemm_scratch(ctx, sc) : nullptr;
     if (gemm_tcgen05_launch(a, wt, ctx->sm_count, st) != cudaSuccess) {
       cudaGetLastError();
@@ -329,10 +372,7 @@ bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type) {
     return false;
   }
   const bool a16 = act_type == HTP_B200_ACT_F16;
-  if (a16 && m >= g_opt_gemm_min_m) {
-    return false;
-  }
-  GemvPlan pl;
+  GemvPlan   pl;
   return gemv_plan(kGemvSmemBudget, wt, a16, m, k / 32, &pl);
 }
 
@@ -705,6 +745,8 @@ int htp_b200_set_option(const char *name, int value) {
     slot = &g_opt_gemm_split;
   } else if (!strcmp(name, "permuted_weights")) {
     slot = &g_opt_permuted_weights;
+  } else if (!strcmp(name, "a32_exact")) {
+    slot = &g_opt_a32_exact;
   }
   if (!slot) {
     return -1;

@@ -259,7 +259,57 @@ __global__ void __launch_bounds__(kRmsThreads) rms_norm_f32_kernel(float *__rest
   }
 }
 
+// fp32 activations -> fp16 for the tensor-core GEMM, one CTA per token.  The token is scaled by a
+// power of two that puts its largest magnitude into [2^14, 2^15) - no overflow for large inputs, no
+// loss to subnormals for small ones - and the inverse of that scale is kept per token for the
+// GEMM's epilogue.  (The reference converts its fp32 activations to fp16 as they are,
+// src/dsp/ops/mat_mul.c:89-128.)
+__global__ void __launch_bounds__(256) act_f32_to_f16_kernel(__half *dst, float *inv_scale, const float *src, int k) {
+  __shared__ float red[8];
+  const int        m   = blockIdx.x;
+  const float     *x   = src + (size_t) m * k;
+  __half          *y   = dst + (size_t) m * k;
+  float            a   = 0.f;
+  for (int i = threadIdx.x; i < k / 4; i += 256) {
+    const float4 v = reinterpret_cast<const float4 *>(x)[i];
+    a              = fmaxf(a, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red[threadIdx.x >> 5] = a;
+  }
+  __syncthreads();
+  a = red[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i) {
+    a = fmaxf(a, red[i]);
+  }
+  int sh = ((__float_as_int(a) >> 23) & 0xff) - 127 - 14;  // floor(log2(amax)) - 14
+  sh     = a == 0.f ? 0 : (sh < -100 ? -100 : (sh > 100 ? 100 : sh));
+  const float s = __int_as_float((127 - sh) << 23);
+  if (threadIdx.x == 0) {
+    inv_scale[m] = __int_as_float((127 + sh) << 23);
+  }
+  for (int i = threadIdx.x; i < k / 4; i += 256) {
+    const float4 v = reinterpret_cast<const float4 *>(x)[i];
+    const __half2 lo = __floats2half2_rn(v.x * s, v.y * s), hi = __floats2half2_rn(v.z * s, v.w * s);
+    uint2         o;
+    o.x = *reinterpret_cast<const uint32_t *>(&lo);
+    o.y = *reinterpret_cast<const uint32_t *>(&hi);
+    reinterpret_cast<uint2 *>(y)[i] = o;
+  }
+}
+
 }  // namespace
+
+cudaError_t act_f32_to_f16_launch(void *dst_f16, float *inv_scale, const float *src, int m, int k,
+                                  cudaStream_t stream) {
+  act_f32_to_f16_kernel<<<m, 256, 0, stream>>>(static_cast<__half *>(dst_f16), inv_scale, src, k);
+  return cudaGetLastError();
+}
 
 cudaError_t rms_norm_f32_launch(float *dst, const float *src, int ne0, int ne1, cudaStream_t stream) {
   const bool vec  = (ne0 % 4 == 0) && ne0 <= kRmsRegElems;

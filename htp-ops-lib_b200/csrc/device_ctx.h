@@ -13,6 +13,8 @@ struct StreamScratch {
   int      *err      = nullptr;  // first kernel error code
   int      *err_host = nullptr;  // pinned host word the error code is copied to when the stream is waited for
   float    *gemm_part = nullptr;  // split-tile scratch of the prefill GEMM, allocated on its first use
+  uint8_t  *act16     = nullptr;  // fp16 copies of fp32 activations for the GEMM + their per-token scales
+  size_t    act16_bytes = 0;
 };
 
 struct DeviceCtx {
@@ -55,6 +57,7 @@ extern int      g_opt_gemm_tile_n;
 extern int      g_opt_gemm_split;
 extern int      g_opt_gemv_whole_tiles;
 extern int      g_opt_permuted_weights;
+extern int      g_opt_a32_exact;
 void            count_launch(int n = 1);
 
 }  // namespace htp

@@ -674,6 +674,17 @@ __global__ void __launch_bounds__(kThreads, 1)
             v[i] = __float_as_uint(__uint_as_float(v[i]) + add[i]);
           }
         }
+        if (p.tok_scale && !is_tail) {  // (partial sums travel unscaled)
+          const float4 *ts = reinterpret_cast<const float4 *>(p.tok_scale + m0 + c0);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float4 sc = __ldg(ts + i);
+            v[4 * i]     = __float_as_uint(__uint_as_float(v[4 * i]) * sc.x);
+            v[4 * i + 1] = __float_as_uint(__uint_as_float(v[4 * i + 1]) * sc.y);
+            v[4 * i + 2] = __float_as_uint(__uint_as_float(v[4 * i + 2]) * sc.z);
+            v[4 * i + 3] = __float_as_uint(__uint_as_float(v[4 * i + 3]) * sc.w);
+          }
+        }
         const uint32_t buf = stage0 + (nbuf & 1) * (kOutTok * 128);
         ++nbuf;
         if (lane == 0) {

@@ -33,6 +33,9 @@ struct GemmArgs {
   int            n_dst;
   float         *y_more[kGemmMaxDst - 1];
   long long      y_ld, y_col0;
+  // Optional per-token output scale (fp32 activations arrive as scaled fp16 copies): output row m is
+  // multiplied by tok_scale[m].  Readable up to the next multiple of 256 tokens.  nullptr: none.
+  const float   *tok_scale;
 #ifdef HTP_GEMM_PROF
   int            dbg;      // instrumented builds only: bit mask of waits to skip (timing experiments)
 #endif

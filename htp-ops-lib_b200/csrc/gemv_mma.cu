@@ -925,15 +925,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     if (p.done_counter) {
-      // this CTA's bands are out (both completion warps, fenced above): count it; the last CTA of the
-      // launch tells every destination that this rank is done
+      // this CTA's bands are out (both completion warps, each thread's stores fenced at system scope
+      // above): count the CTA in; the last CTA of the launch tells every destination that this rank is
+      // done.  The counter's acquire-release and the flags' release stores carry the ordering: no
+      // further fence.
       named_bar_sync(2, kReduceThreads);
       if (warp == kReduceWarp0 && lane == 0) {
-        __threadfence_system();
-        const unsigned old = atomicAdd(p.done_counter, 1u);
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.done_counter) : "memory");
         if (old == gridDim.x - 1) {
           *p.done_counter = 0;  // ready for the next launch
-          __threadfence_system();
           for (int d = 0; d < p.n_dst; ++d) {
             asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[d]), "r"(p.epoch) : "memory");
           }

@@ -49,8 +49,13 @@ extern "C" {
  * Replaces hmx_mat_mul_permuted_qk_0_d16a32 (reference include/dsp/ops.h:19-20,
  * src/dsp/ops/mat_mul.c:875-1153) and keeps its argument checks: non-null pointers, non-zero
  * sizes, k % 32 == 0, n % 32 == 0, all three pointers 128-byte aligned; anything else -> -1.
- * Unlike the reference neither activations nor outputs are rounded to fp16.
- * `stream` is a cudaStream_t (NULL = the default stream).
+ * Kernel by token count: m <= 8 one launch of the decode kernel (fp32 activations, m = 9 .. 16: two),
+ * which keeps the weights exact and meets 1e-5 against an fp64 dequantise-then-dot for fp32
+ * activations; from m = 9 (fp16 activations) or m = 17 (fp32 activations) the tensor-core GEMM, whose weights are rounded to fp16 once (value * scale, as the reference's
+ * dequantisation does, mat_mul.c:290, 304) and which takes fp32 activations as fp16 copies, each token
+ * scaled by its own power of two (the reference converts them to fp16 as they are, mat_mul.c:89-128):
+ * 1e-3.  Outputs are never rounded to fp16.  Option "a32_exact" keeps fp32-activation matmuls of any
+ * m on the decode kernel.  `stream` is a cudaStream_t (NULL = the default stream).
  */
 int htp_b200_mul_mat(void *dst, const void *activation, const void *weight, int m, int k, int n, int weight_type,
                      int act_type, void *stream);
@@ -109,7 +114,7 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
  * src/dsp/op_executor.cc:124-126) evaluated in 64 bits.  0 for an unknown type or k % 32 != 0. */
 size_t htp_b200_weight_bytes(int weight_type, int64_t k, int64_t n);
 
-/* Matmul for m <= 8 (decode kernel, either activation type) or for fp16 activations with m >= 64
+/* Matmul for m <= 8 (decode kernel, either activation type) or for fp16 activations with m >= 9
  * (tensor-core kernel), k % 256 == 0, whose result y[m][n] is stored as the column band [dst_col0, dst_col0 + n) of n_dst (1..8) destination matrices
  * of dst_ld floats per token: the fused form of "matmul on my row shard, then all-gather".  A rank of
  * a row-sharded lm_head passes every rank's full logits buffer (its own and the peers' mapped
@@ -162,7 +167,9 @@ int htp_b200_stream_status(void *stream);
 
 /* Tuning / debugging switches: "pdl" (programmatic dependent launch, default 1),
  * "force_generic" (route every matmul to the shape-agnostic kernel, default 0), "gemm_min_m"
- * (fp16-activation matmuls with at least this many tokens use the tensor-core GEMM, default 64),
+ * (matmuls with at least this many tokens use the tensor-core GEMM - fp32 activations from 17 on at
+ * the earliest -, default 9), "a32_exact" (1 = fp32
+ * activations never go through the GEMM's fp16 conversion, default 0),
  * "gemm_tile_n" (tokens per GEMM tile: 0 = automatic, 128 or 256), "gemm_split" (when the GEMM's
  * tiles do not divide evenly among the SMs, cut the work into equal K ranges and finish the split
  * tiles through a scratch area, default 0), "permuted_weights" (op indices 2, 3 and 4 of

@@ -1,6 +1,7 @@
-"""GPU parity of the prefill GEMM (tcgen05 / TMEM): fp16 activations, M >= 64, against the fp64
-oracle.  Gate: max|y - o| / max|o| <= 1e-3 (weights are rounded to fp16 once, as the reference's
-dequantisation does, accumulation is fp32)."""
+"""GPU parity of the prefill GEMM (tcgen05 / TMEM): fp16 activations (M >= 9) or fp32 activations
+converted to fp16 on the way in (M >= 17), against the fp64 oracle.  Gate: max|y - o| / max|o| <= 1e-3
+(weights - and fp32 activations - are rounded to fp16 once, as the reference's dequantisation and
+activation transfer do, src/dsp/ops/mat_mul.c:117, 290, 304; accumulation and output are fp32)."""
 from __future__ import annotations
 
 import numpy as np
@@ -74,11 +75,12 @@ def test_gemm_matches_decode_kernel(dev, wl):
     lib = dev.lib
     wq, x = wl.random_case(77, 8, True, 128, 1024, 256)
     y_gemm = dev.matmul(x, wq, 256, 8)
-    assert lib.htp_b200_set_option(b"gemm_min_m", 1 << 30) == 64
+    old = lib.htp_b200_set_option(b"gemm_min_m", 1 << 30)
+    assert old == 9
     try:
         y_gemv = dev.matmul(x, wq, 256, 8)
     finally:
-        lib.htp_b200_set_option(b"gemm_min_m", 64)
+        lib.htp_b200_set_option(b"gemm_min_m", old)
     assert np.abs(y_gemm - y_gemv).max() <= 1e-3 * np.abs(y_gemv).max()
 
 
@@ -111,6 +113,47 @@ def test_gemm_multi_destination_band(dev, oracle, wl, wtype):
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0 + 16, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, ld - 32, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
     assert lib.htp_b200_mul_mat_multi_dst(ptrs, 9, ld, col0, tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 1, st) == -1
-    # between the decode kernel's range (m <= 8) and the tensor-core kernel's (m >= 64)
-    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), 32, k, n, wtype, 1, st) == -1
+    # fp32 activations beyond the decode kernel's range (m <= 8)
+    assert lib.htp_b200_mul_mat_multi_dst(ptrs, 3, ld, col0, tx.data_ptr(), tw.data_ptr(), 12, k, n, wtype, 0, st) == -1
     assert lib.htp_b200_launch_count() == before
+
+
+@pytest.mark.parametrize("wtype", [2, 8, 20])
+@pytest.mark.parametrize("m,k,n", [(17, 256, 64), (32, 1024, 480), (64, 2048, 1024), (512, 4096, 2240), (100, 14336, 96)])
+def test_gemm_fp32_activations(dev, oracle, wl, wtype, m, k, n):
+    """The reference's own A32 ops (indices 2, 3, 4) at prefill sizes: ONE conversion launch (fp32 ->
+    per-token scaled fp16) and ONE GEMM launch, never token slices through the decode kernel."""
+    import torch
+    wq, x = wl.random_case(990, wtype, False, m, k, n)
+    x[0] *= 3.0e5  # beyond the fp16 range: the per-token power-of-two scale must absorb it
+    x[1] *= 1.0e-6
+    tw, tx = torch.from_numpy(wq).cuda(), torch.from_numpy(x).cuda()
+    ty = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    before = dev.lib.htp_b200_launch_count()
+    assert dev.lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 0, st) == 0
+    torch.cuda.synchronize()
+    assert dev.lib.htp_b200_stream_status(st) == 0
+    assert dev.lib.htp_b200_launch_count() == before + 2
+    y = ty.cpu().numpy()
+    ref = oracle.mul_mat_f64(x, wq, n, wtype)
+    assert np.isfinite(y).all()
+    for r in range(m):  # per token: the tokens differ by eleven orders of magnitude
+        assert np.abs(y[r] - ref[r]).max() <= 1e-3 * np.abs(ref[r]).max(), r
+    # the exact path stays available: decode kernel in slices of eight tokens, gate 1e-5
+    old = dev.lib.htp_b200_set_option(b"a32_exact", 1)
+    try:
+        assert dev.lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, wtype, 0, st) == 0
+        torch.cuda.synchronize()
+    finally:
+        dev.lib.htp_b200_set_option(b"a32_exact", old)
+    y = ty.cpu().numpy()
+    for r in range(m):
+        assert np.abs(y[r] - ref[r]).max() <= 1e-5 * np.abs(ref[r]).max(), r
+
+
+@pytest.mark.parametrize("m", [9, 16, 24, 48, 63])
+def test_gemm_fp16_between_decode_and_full_tiles(dev, oracle, wl, m):
+    """9 .. 63 tokens: one GEMM launch on a padded 128-token tile (cheaper than one pass over the
+    weights per eight tokens)."""
+    run(dev, oracle, wl, 2, m, 1024, 992, seed=m)
