@@ -345,25 +345,32 @@ def measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, st
     two rotating copies each.  Algorithmic bytes = weight buffer + activation + output."""
     dev = torch.device("cuda", torch.cuda.current_device())
     out = {}
-    for name, fmt, k, n in (("w16a32_tiled_gemv_32768x4096_m1", wl.WT_F16_TILED, 4096, 32768),
-                            ("permuted_q4_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q4_0, 4096, 65536),
-                            ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 4096, 65536)):
+    for name, fmt, m, k, n in (("w16a32_tiled_gemv_32768x4096_m1", wl.WT_F16_TILED, 1, 4096, 32768),
+                               ("w16a32_tiled_prefill_f32act_14336x4096_m512", wl.WT_F16_TILED, 512, 4096, 14336),
+                               ("permuted_q4_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q4_0, 1, 4096, 65536),
+                               ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 1, 4096, 65536)):
         nbytes = wl.weight_bytes(fmt, k, n)
         assert nbytes == lib.htp_b200_weight_bytes(fmt, k, n)
-        ws = [tile_order_device_weights(torch, wl, fmt, k, n, dev) for _ in range(2)]
-        x = torch.randn((1, k), device=dev, dtype=torch.float32)
-        y = torch.empty((1, n), device=dev, dtype=torch.float32)
+        copies = 2 if m == 1 else 1
+        ws = [tile_order_device_weights(torch, wl, fmt, k, n, dev) for _ in range(copies)]
+        x = torch.randn((m, k), device=dev, dtype=torch.float32)
+        y = torch.empty((m, n), device=dev, dtype=torch.float32)
 
         def step(i):
-            assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % 2].data_ptr(), 1, k, n, fmt, pkg.ACT_F32,
+            assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, k, n, fmt, pkg.ACT_F32,
                                         stream_ptr) == 0
         for i in range(3):
             step(i)
         ms = time_region(torch, step, steps, stream) / steps
         assert lib.htp_b200_stream_status(stream_ptr) == 0
-        gb = (nbytes + 4 * k + 4 * n) / (ms * 1e-3) / 1e9
-        out[name] = {"ms": round(ms, 5), "m": 1, "k": k, "n": n, "weight_copies": 2, "GBps": round(gb, 1),
-                     "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4)}
+        r = {"ms": round(ms, 5), "m": m, "k": k, "n": n, "weight_copies": copies}
+        if m == 1:
+            gb = (nbytes + 4 * k + 4 * n) / (ms * 1e-3) / 1e9
+            r.update(GBps=round(gb, 1), frac_of_hbm_peak=round(gb / peaks["hbm_gbs"], 4))
+        else:
+            tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+            r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
+        out[name] = r
         del ws
     return out
 

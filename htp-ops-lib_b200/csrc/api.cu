@@ -316,6 +316,33 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     return -2;
   }
   const bool a16 = act_type == HTP_B200_ACT_F16;
+  if (tfmt == kTileF16 && k % 128 == 0 && m >= g_opt_gemm_min_m && (a16 || (!g_opt_a32_exact && m >= kGemmMinMF32))) {
+    // fp16 weights in the reference's tile order, many tokens: the tensor-core GEMM reads the tiles
+    // as they lie (its "unpack" is a copy); fp32 activations go in as per-token scaled fp16 copies
+    StreamScratch *sc = stream_scratch(ctx, st);
+    if (!sc) {
+      return -2;
+    }
+    GemmArgs a = {};
+    a.y = static_cast<float *>(dst), a.x = activation, a.w = static_cast<const uint8_t *>(weight);
+    a.M = m, a.N = n, a.K = k, a.err = sc->err;
+    if (!a16) {
+      float   *scales = nullptr;
+      uint8_t *x16    = act16_scratch(sc, st, m, k, &scales);
+      if (!x16 || act_f32_to_f16_launch(x16, scales, static_cast<const float *>(activation), m, k, st) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
+      }
+      count_launch();
+      a.x = x16, a.tok_scale = scales;
+    }
+    if (gemm_tcgen05_launch(a, kGemmWtF16Tiled, ctx->sm_count, st) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    count_launch();
+    return 0;
+  }
   if (tfmt >= 0) {
     // weights in the reference's tile order: streamed in place by the tile-order kernel
     if (tiled_mul_mat_launch(static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n,

@@ -59,8 +59,7 @@ namespace {
 
 constexpr int kBW        = 128;  // weight rows per tile (UMMA M, the TMEM lanes)
 constexpr int kBK        = 64;   // K per pipeline step: one 128-byte swizzled row of fp16
-constexpr int kKPerRaw   = 256;  // weights per row in one raw stage (a 16-byte aligned period)
-constexpr int kQ         = kKPerRaw / kBK;  // K steps per raw stage
+constexpr int kF16T      = 3;    // weight "format" of this file only: fp16 values in the reference's 32 x 32 tile order
 constexpr int kNAT       = 8;    // A tiles (32 TMEM columns each) in the tensor-memory ring
 constexpr int kThreads   = 512;
 constexpr int kEpiWarp0  = 4;
@@ -71,11 +70,25 @@ constexpr int kOutTok    = 16;      // tokens per output store (one TMA box of 3
 constexpr int kSmemLimit = 232448;  // opt-in dynamic shared memory per CTA
 constexpr uint32_t kFlagWaitCap = 1u << 22;  // polls of the other contributor's flag (about a second)
 
+}  // namespace
+template <>
+struct BlockTraits<3> {  // kF16T: 32 fp16 weights of a row
+  static constexpr int kBytes = 64;
+};
+namespace {
+
 template <int WT, int BT, bool TWO>
 struct GCfg {
+  static constexpr bool TILED    = WT == kF16T;
+  // A raw stage = the bytes of RAWK weights per row, fetched and unpacked as one unit: 256 weights of
+  // the block formats (a 16-byte aligned period of 8 blocks), 128 of the fp16 tile order (four 2 KB
+  // tiles per 32 rows).
+  static constexpr int RAWK      = TILED ? 128 : 256;
+  static constexpr int Q         = RAWK / kBK;  // K steps per raw stage
+  static constexpr int NG        = kNAT / Q;    // raw stages the ring of K steps holds
   static constexpr int BB        = BlockTraits<WT>::kBytes;
-  static constexpr int RB        = 8 * BB;   // raw bytes per row and raw stage: 144 / 272
-  static constexpr int RW        = RB / 16;  // 16-byte words per row: 9 / 17
+  static constexpr int RB        = (RAWK / 32) * BB;  // raw bytes per row and raw stage: 144 / 272 / 256
+  static constexpr int RW        = RB / 16;           // 16-byte words per row: 9 / 17 / 16
   static constexpr int XROWS     = TWO ? BT / 2 : BT;  // activation rows this CTA loads per K step
   static constexpr int X_BYTES   = XROWS * 128;
   static constexpr int RAW_BYTES = kBW * RB;
@@ -332,6 +345,7 @@ struct Ring {
 // (quant bytes biased to 0..255; the scale halfwords are un-biased again where they are used).
 template <int WT>
 __device__ __forceinline__ void dequant_two_blocks(const uint32_t *raw, int q, uint4 (&out)[8]) {
+  static_assert(WT == kQ4 || WT == kQ8 || WT == kIQ4, "block formats only");
   // block b of the raw stage starts at byte b * BB; its scale is the first halfword
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -455,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int t_tiles = (p.M + BT - 1) / BT;                // token tiles
   const int w_tiles = (p.N + ROWS_TILE - 1) / ROWS_TILE;  // weight-row tiles
   const int tiles   = t_tiles * w_tiles;
-  const int k_raws  = p.K / kKPerRaw;
+  const int k_raws  = p.K / C::RAWK;
   const int worker  = TWO ? (int) (blockIdx.x >> 1) : (int) blockIdx.x;  // CTA, or CTA pair
   const int workers = TWO ? (int) (gridDim.x >> 1) : (int) gridDim.x;
   const int row_off = (int) rank * kBW;        // this CTA's weight rows inside the tile
@@ -511,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         segment(li, t, rs0, rs1);
         li += rs1 - rs0;
         const int m0 = (t % t_tiles) * BT + tok_off;
-        for (int kb = rs0 * kQ; kb < rs1 * kQ; ++kb) {
+        for (int kb = rs0 * C::Q; kb < rs1 * C::Q; ++kb) {
           ok = wait_or_abort(&bar->empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
           if (!ok) {
             break;
@@ -554,10 +568,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc_fence_after();
         for (int rs = rs0; rs < rs1 && ok; ++rs, ++gs) {
-          const int g = gs & 1, gph = (gs >> 1) & 1;
+          const int sg = (int) (gs % C::NG), gph = (int) (gs / C::NG) & 1;  // ring position of the raw stage
 #pragma unroll
-          for (int q = 0; q < kQ; ++q) {
-            const int slot = g * kQ + q;
+          for (int q = 0; q < C::Q; ++q) {
+            const int slot = sg * C::Q + q;
             ok = wait_or_abort(&bar->full[slot], gph, abort_flag, p.err, kGemmErrMma);
             ok = __all_sync(0xffffffffu, ok);
             PROF_ADD(2);
@@ -786,7 +800,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     // (A tiled TMA copy of 128 such short rows was the bottleneck of an earlier version: the copy
     // engine's cost is per row, about the same for 144 bytes as for a kilobyte.)
     const int      g     = (warp - kDeqWarp0) >> 2;
-    const int      r     = (warp & 3) * 32 + lane;
     const uint32_t tlane = tmem_base + kTmemA + ((uint32_t) ((warp & 3) * 32) << 16);
     const uint32_t warp_smem = smem_u32(sRaw + g * RAW_PITCH + (warp & 3) * 32 * C::RB);
     const uint32_t slot_smem = warp_smem + lane * C::RB;  // this thread's row
@@ -805,16 +818,28 @@ __global__ void __launch_bounds__(kThreads, 1)
         return;  // N is a multiple of 32: the warp's rows are all inside or all outside the matrix;
                  // rows outside are computed on whatever the slice holds and never stored
       }
-      const uint8_t *src = p.w + (row0 + row_first) * row_bytes + (long long) rs * C::RB + 16 * pc_first;
-      int            pc  = pc_first;
-      uint32_t       dst = warp_smem + 16 * lane;
+      if constexpr (C::TILED) {
+        // the warp's 32 rows are ONE column tile of the reference's tile order, and the RAWK / 32
+        // k-tiles of a raw stage are consecutive 2 KB tiles: one contiguous run, copied as it lies
+        const uint8_t *src = p.w + ((row0 >> 5) * (long long) (p.K / 32) + (long long) rs * (C::RAWK / 32)) * 2048 + 16 * lane;
+        uint32_t       dst = warp_smem + 16 * lane;
 #pragma unroll
-      for (int i = 0; i < C::RW; ++i) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-        const bool wrap = pc + kB >= C::RW;
-        pc += wrap ? kB - C::RW : kB;
-        src += wrap ? (kA + 1) * row_bytes + 16 * (kB - C::RW) : kA * row_bytes + 16 * kB;
-        dst += 512;
+        for (int i = 0; i < C::RW; ++i) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          src += 512, dst += 512;
+        }
+      } else {
+        const uint8_t *src = p.w + (row0 + row_first) * row_bytes + (long long) rs * C::RB + 16 * pc_first;
+        int            pc  = pc_first;
+        uint32_t       dst = warp_smem + 16 * lane;
+#pragma unroll
+        for (int i = 0; i < C::RW; ++i) {
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          const bool wrap = pc + kB >= C::RW;
+          pc += wrap ? kB - C::RW : kB;
+          src += wrap ? (kA + 1) * row_bytes + 16 * (kB - C::RW) : kA * row_bytes + 16 * kB;
+          dst += 512;
+        }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -828,7 +853,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     PROF_T0();
     for (int li = g; li < n_stages; li += 2) {
       const unsigned gs  = (unsigned) li;  // running stage index
-      const int      gph = (gs >> 1) & 1;
+      const int      sg = (int) (gs % C::NG), gph = (int) (gs / C::NG) & 1;  // ring position of the raw stage
       asm volatile("cp.async.wait_group 0;" ::: "memory");
       // every lane's pieces of the stage have landed; the warp also leaves TOGETHER here once a
       // lane has given up a wait
@@ -836,24 +861,49 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       PROF_ADD(0);
-      uint32_t raw[C::RW * 4 + 1];
+      // the thread's row of the raw stage, out of the slice into registers
+      constexpr int RAW_WORDS = C::TILED ? C::RAWK / 2 : C::RW * 4;
+      uint32_t      raw[RAW_WORDS + 1];
+      if constexpr (C::TILED) {
+        // tile order: the k-pair (2 kp, 2 kp + 1) of column n of a tile is the 32-bit word kp * 32 + n;
+        // a lane's words are the fp16 pairs of its row in K order - what the tensor memory wants
 #pragma unroll
-      for (int i = 0; i < C::RW; ++i) {
-        asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
-                     : "r"(slot_smem + 16 * i)
-                     : "memory");
-      }
-      if constexpr (WT == kQ8) {
+        for (int i = 0; i < RAW_WORDS; ++i) {
+          asm volatile("ld.volatile.shared.u32 %0, [%1];"
+                       : "=r"(raw[i])
+                       : "r"(warp_smem + (i >> 4) * 2048 + (i & 15) * 128 + lane * 4)
+                       : "memory");
+        }
+      } else {
 #pragma unroll
-        for (int i = 0; i < C::RW * 4; ++i) {
-          raw[i] ^= 0x80808080u;  // quant bytes biased to 0..255, once per word
+        for (int i = 0; i < C::RW; ++i) {
+          asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(raw[4 * i]), "=r"(raw[4 * i + 1]), "=r"(raw[4 * i + 2]), "=r"(raw[4 * i + 3])
+                       : "r"(slot_smem + 16 * i)
+                       : "memory");
+        }
+        if constexpr (WT == kQ8) {
+#pragma unroll
+          for (int i = 0; i < C::RW * 4; ++i) {
+            raw[i] ^= 0x80808080u;  // quant bytes biased to 0..255, once per word
+          }
         }
       }
-      raw[C::RW * 4] = 0;  // the word past the end is only ever the unused half of a byte_perm
+      raw[RAW_WORDS] = 0;  // the word past the end is only ever the unused half of a byte_perm
       // the fp16 values of a K step are computed before waiting for their TMEM slot
       uint4 out[8];
-      dequant_two_blocks<WT>(raw, 0, out);
+      auto  k_step = [&](int q) {
+        if constexpr (C::TILED) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            out[c] = make_uint4(raw[32 * q + 4 * c], raw[32 * q + 4 * c + 1], raw[32 * q + 4 * c + 2],
+                                raw[32 * q + 4 * c + 3]);
+          }
+        } else {
+          dequant_two_blocks<WT>(raw, q, out);
+        }
+      };
+      k_step(0);
       // Next stage of this group into the same slice.
       // The loads above are volatile (they stay where they are written) and the copies below go
       // down the same in-order load/store pipe behind them, writing shared memory only after a
@@ -864,19 +914,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       PROF_ADD(1);
 #pragma unroll
-      for (int q = 0; q < kQ; ++q) {
-        const int slot = g * kQ + q;
+      for (int q = 0; q < C::Q; ++q) {
+        const int slot = sg * C::Q + q;
         ok = ok && wait_or_abort(&bar->empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
         PROF_ADD(2);
         ok = __all_sync(0xffffffffu, ok);  // a warp stores to tensor memory as a whole or not at all
         if (ok) {
           tc_fence_after();
           tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
-#ifdef HTP_GEMM_DEFER_ST
-          if (q + 1 < kQ) {
-            dequant_two_blocks<WT>(raw, q + 1, out);  // overlaps the store
-          }
-#endif
           tmem_st_wait();
           tc_fence_before();
           PROF_ADD(3);
@@ -889,11 +934,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-#ifndef HTP_GEMM_DEFER_ST
-        if (q + 1 < kQ) {
-          dequant_two_blocks<WT>(raw, q + 1, out);
+        if (q + 1 < C::Q) {
+          k_step(q + 1);
         }
-#endif
         PROF_ADD(4);
       }
     }
@@ -1056,6 +1099,9 @@ cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, c
   }
   if (wt == kIQ4) {
     return one ? launch<kIQ4, 128, false>(args, sm_count, stream) : launch<kIQ4, 256, true>(args, sm_count, stream);
+  }
+  if (wt == kGemmWtF16Tiled) {
+    return one ? launch<kF16T, 128, false>(args, sm_count, stream) : launch<kF16T, 256, true>(args, sm_count, stream);
   }
   return one ? launch<kQ8, 128, false>(args, sm_count, stream) : launch<kQ8, 256, true>(args, sm_count, stream);
 }

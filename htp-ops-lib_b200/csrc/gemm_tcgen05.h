@@ -14,11 +14,16 @@ constexpr int kGemmErrFixup    = 205;  // the other contributor of a split tile 
 
 constexpr int kGemmMaxDst = 8;
 
+// `wt` of gemm_tcgen05_launch beyond the block formats (0 Q4_0, 1 Q8_0, 2 IQ4_NL): fp16 weights in the
+// reference's 32 x 32 tile order (tile (n/32, k/32) at tile number (n/32) * (K/32) + k/32, element
+// (k, n) of a tile at halfword (k & ~1) * 32 + 2 n + (k & 1)); K a multiple of 128.
+constexpr int kGemmWtF16Tiled = 3;
+
 struct GemmArgs {
   float         *y;  // [M][N] fp32 (destination 0)
   const void    *x;  // [M][K] fp16
-  const uint8_t *w;  // N rows of K/32 blocks
-  int            M, N, K;  // K a multiple of 256, N a multiple of 32
+  const uint8_t *w;  // N rows of K/32 blocks, or fp16 tiles
+  int            M, N, K;  // K a multiple of 256 (fp16 tiles: 128), N a multiple of 32
   int           *err;      // first error code, 0 when none
   // Scratch for tiles whose K range is split between two workers (gemm_scratch_bytes() bytes at
   // `part`, 256-byte aligned, zero before the first launch; the flags are zero again after every

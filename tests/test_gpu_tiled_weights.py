@@ -36,9 +36,17 @@ def _raw(dev, x, wq, n, fmt):
     rc = dev.lib.htp_b200_mul_mat(ty.data_ptr(), tx.data_ptr(), tw.data_ptr(), m, k, n, fmt,
                                   1 if x.dtype == np.float16 else 0, st)
     assert rc == 0
-    assert dev.lib.htp_b200_launch_count() == before + 1
+    # one launch; fp32 activations on their way to the tensor-core GEMM take a conversion launch first
+    assert dev.lib.htp_b200_launch_count() == before + (2 if _gemm_path(fmt, x) and x.dtype == np.float32 else 1)
     assert dev.lib.htp_b200_stream_status(st) == 0
     return ty.cpu().numpy()
+
+
+def _gemm_path(fmt, x) -> bool:
+    """fp16 tiles with many tokens run on the tensor-core GEMM (fp16 activations from 9 tokens, fp32 from
+    17, k % 128 == 0): activations rounded to fp16, gate 1e-3."""
+    m, k = x.shape
+    return fmt == 1 and k % 128 == 0 and m >= (9 if x.dtype == np.float16 else 17)
 
 
 @pytest.mark.parametrize("act_f16", [False, True])
@@ -47,7 +55,29 @@ def _raw(dev, x, wq, n, fmt):
 def test_tile_order_matmul_matches_oracle(dev, oracle, wl, fmt, act_f16, m, k, n):
     wq, x = wl.tiled_random_case(50, fmt, act_f16, m, k, n)
     assert wq.size == dev.lib.htp_b200_weight_bytes(fmt, k, n)
-    _check(oracle, _raw(dev, x, wq, n, fmt), x, wq, n, fmt, 1e-3 if act_f16 else 1e-5)
+    _check(oracle, _raw(dev, x, wq, n, fmt), x, wq, n, fmt, 1e-3 if act_f16 or _gemm_path(fmt, x) else 1e-5)
+
+
+@pytest.mark.parametrize("act_f16", [False, True])
+@pytest.mark.parametrize("m,k,n", [(17, 128, 32), (64, 1024, 1024), (200, 2048, 480), (512, 4096, 2240), (300, 1152, 19360 // 32 * 32)])
+def test_fp16_tiles_many_tokens_on_the_tensor_cores(dev, oracle, wl, act_f16, m, k, n):
+    """The reference's W16A32 op takes any m (src/dsp/ops/mat_mul.c:758-855): many tokens over fp16 tiles
+    run as ONE tensor-core GEMM launch that reads the tiles as they lie - full and ragged tiles in M and
+    N, one and many K steps, K a multiple of 128 but not of 256, more tiles than one wave."""
+    wq, x = wl.tiled_random_case(60 + m, 1, act_f16, m, k, n)
+    if not act_f16:
+        x[0] *= 1.0e5  # beyond the fp16 range: absorbed by the per-token scale
+    y = _raw(dev, x, wq, n, 1)
+    ref = oracle.tiled_mul_mat_f64(x, wq, n, 1)
+    assert np.isfinite(y).all()
+    for r in range(m):
+        assert np.abs(y[r] - ref[r]).max() <= 1e-3 * np.abs(ref[r]).max(), r
+    # through the op registry (index 1) as well: same bytes
+    if not act_f16:
+        fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
+        assert dev.execute(dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W16A32, (fy, 0), (fx, 0), (fw, 0), m, k, n) == 0
+        assert (dev.get(fy, (m, n)) == y).all()
+        dev.free(fw, fx, fy)
 
 
 def test_tile_order_matmul_matches_committed_golden_samples(dev):
