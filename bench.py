@@ -166,6 +166,36 @@ def time_region(torch, fn, steps: int, stream) -> float:
     return e0.elapsed_time(e1)
 
 
+def graph_time(torch, lib, launch, n_in_graph: int, replays: int):
+    """Milliseconds per launch when `n_in_graph` launches (launch(i, stream_ptr), i = 0 ..) are captured
+    into ONE CUDA graph and the graph is replayed `replays` times: the host cost of issuing each
+    operator is paid at capture time, not per launch.  None when the capture fails."""
+    side = torch.cuda.Stream()
+    try:
+        with torch.cuda.stream(side):
+            for i in range(2):  # first use of the stream: scratch allocation, attribute set-up - not capturable
+                launch(i, side.cuda_stream)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(n_in_graph):
+                launch(i, side.cuda_stream)
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        assert lib.htp_b200_stream_status(side.cuda_stream) == 0
+        return e0.elapsed_time(e1) / (replays * n_in_graph)
+    except Exception as e:  # noqa: BLE001 - reported as absent, the stream-launch number stands
+        sys.stderr.write(f"graph capture failed: {type(e).__name__}: {e}\n")
+        return None
+
+
 def cpu_baseline(wl, cfg_name: str, m: int, seconds: float = 12.0, sample_rows: int = 8192):
     """The CPU restatement (fp32, threaded) timed on a bounded row sample of the workload."""
     import numpy as np
@@ -250,10 +280,13 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
         y = torch.empty((m, op.n), device=dev, dtype=torch.float32)
         act_t = pkg.ACT_F16 if op.act_f16 else pkg.ACT_F32
 
-        def step(i):
+        def launch(i, sp_):
             rc = lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, op.k, op.n, op.wtype,
-                                      act_t, stream_ptr)
+                                      act_t, sp_)
             assert rc == 0
+
+        def step(i):
+            launch(i, stream_ptr)
         for i in range(3):
             step(i)
         ms = time_region(torch, step, steps, stream) / steps
@@ -262,6 +295,13 @@ def measure_single_gpu_configs(torch, pkg, lib, wl, peaks, stream_ptr, quick: bo
         if m <= 8:
             gb = wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9
             r.update(GBps=round(gb, 1), frac_of_hbm_peak=round(gb / peaks["hbm_gbs"], 4))
+            # a small mat-vec is bound by the HOST's launch rate (about 5 us per call from Python): the
+            # same launches replayed from a CUDA graph show what the device does
+            msg = graph_time(torch, lib, launch, max(copies, 8), max(5, steps // 4))
+            if msg is not None:
+                gbg = wl.algorithmic_bytes(op, m) / (msg * 1e-3) / 1e9
+                r.update(ms_graph=round(msg, 5), GBps_graph=round(gbg, 1),
+                         frac_of_hbm_peak_graph=round(gbg / peaks["hbm_gbs"], 4))
         else:
             tf = wl.flops(op, m) / (ms * 1e-3) / 1e12
             r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
@@ -308,9 +348,12 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
         x = torch.randn((m, k), device=dev, dtype=torch.float16 if a16 else torch.float32)
         y = torch.empty((m, n), device=dev, dtype=torch.float32)
 
-        def step(i):
+        def launch(i, sp_):
             assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, k, n, wtype,
-                                        pkg.ACT_F16 if a16 else pkg.ACT_F32, stream_ptr) == 0
+                                        pkg.ACT_F16 if a16 else pkg.ACT_F32, sp_) == 0
+
+        def step(i):
+            launch(i, stream_ptr)
         for i in range(3):
             step(i)
         ms = time_region(torch, step, steps, stream) / steps
@@ -319,6 +362,11 @@ def measure_large_decode_and_iq4(torch, pkg, lib, wl, peaks, stream_ptr, stream,
         if m <= 8:
             gb = wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9
             r.update(GBps=round(gb, 1), frac_of_hbm_peak=round(gb / peaks["hbm_gbs"], 4))
+            msg = graph_time(torch, lib, launch, 8, max(5, steps // 2))
+            if msg is not None:
+                gbg = wl.algorithmic_bytes(op, m) / (msg * 1e-3) / 1e9
+                r.update(ms_graph=round(msg, 5), GBps_graph=round(gbg, 1),
+                         frac_of_hbm_peak_graph=round(gbg / peaks["hbm_gbs"], 4))
         else:
             tf = wl.flops(op, m) / (ms * 1e-3) / 1e12
             r.update(TFLOPs=round(tf, 2), frac_of_tensor_peak=round(tf / peaks["tflops"], 4))
@@ -855,12 +903,20 @@ def run_case(args):
         step(i)
     enqueue_us = (time.perf_counter() - t0) / args.steps * 1e6  # host time to issue one op
     torch.cuda.synchronize()
+
+    def launch(i, sp_):
+        assert lib.htp_b200_mul_mat(y.data_ptr(), x.data_ptr(), ws[i % copies].data_ptr(), m, k, n, wtype,
+                                    pkg.ACT_F16 if a16 else pkg.ACT_F32, sp_) == 0
+    ms_graph = graph_time(torch, lib, launch, max(copies, 8), max(3, args.steps // 4)) if args.graph else None
     peaks = read_peaks()
     r = {"case": args.case, "ms": round(ms, 5), "host_enqueue_us": round(enqueue_us, 2), "weight_copies": copies,
          "GBps": round(wl.algorithmic_bytes(op, m) / (ms * 1e-3) / 1e9, 1),
          "TFLOPs": round(wl.flops(op, m) / (ms * 1e-3) / 1e12, 2)}
     r["frac_hbm"] = round(r["GBps"] / peaks["hbm_gbs"], 4)
     r["frac_tensor"] = round(r["TFLOPs"] / peaks["tflops"], 4)
+    if ms_graph is not None:
+        r["ms_graph"] = round(ms_graph, 5)
+        r["frac_hbm_graph"] = round(wl.algorithmic_bytes(op, m) / (ms_graph * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
     print(json.dumps(r), flush=True)
 
 
@@ -876,6 +932,7 @@ def main():
     ap.add_argument("--no-fused", action="store_true",
                     help="N > 1: assemble the logits with an NCCL all-gather instead of the kernel's own peer stores")
     ap.add_argument("--case", default=None, help="wtype,act,m,k,n: time one shape only (profiling aid)")
+    ap.add_argument("--graph", action="store_true", help="--case: also time the launches replayed from a CUDA graph")
     args = ap.parse_args()
     if args.case:
         run_case(args)

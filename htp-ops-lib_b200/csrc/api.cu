@@ -460,8 +460,7 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
         const int         p0      = round * plans[i].chunk_periods;
         const int         pn = (periods - p0) < plans[i].chunk_periods ? (periods - p0) : plans[i].chunk_periods;
         const int         kb = pn * 8;
-        if (gemv_weight_map(op.wmap, q.w + (size_t) p0 * 8 * bb, (long long) kb_all * bb, kb, q.n, wt, mpad == 8) !=
-            cudaSuccess) {
+        if (gemv_weight_map(op.wmap, q.w + (size_t) p0 * 8 * bb, (long long) kb_all * bb, kb, q.n, wt) != cudaSuccess) {
           cudaGetLastError();
           return -2;
         }

@@ -68,10 +68,10 @@ struct Cfg {
   static_assert(MPAD == 1 || MPAD == 2 || MPAD == 8, "token paddings built: 1, 2, 8");
   static constexpr int  NC       = WIDE ? 8 : (I8 ? 4 * MPAD : (A16 ? MPAD : 2 * MPAD));  // MMA columns in use
   static constexpr bool SPLITCOL = !I8 && !A16;                                         // column = 2 m + piece
-  static constexpr int  SB       = gemv_stage_blocks(WT, WIDE);  // blocks per stage and row
+  static constexpr int  SB       = gemv_stage_blocks(WT);  // blocks per stage and row
   static constexpr int  BPW      = SB / kConsumerWarps;          // blocks per consumer warp and stage
   static_assert(BPW >= 1 && BPW * kConsumerWarps == SB, "a stage splits evenly over the consumer warps");
-  static constexpr int  PSTRIDE  = gemv_row_pitch(WT, WIDE);
+  static constexpr int  PSTRIDE  = gemv_row_pitch(WT);
   static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
   // uint2 entries per block: two k-steps of fp16 fragments, or one int8 fragment per column and lane
   // position (per MMA) followed by the columns' accumulator inputs (one int each)
@@ -415,7 +415,8 @@ __device__ __forceinline__ void block_rows16(const uint8_t *ra, const uint2 (&bf
 // Integer path: one Q4_0 block x 16 rows = ONE m16n8k32 MMA (unsigned nibbles x signed digits,
 // int32 accumulate starting from kMagicBits).  off2: the float offsets of columns 2t, 2t + 1.
 template <int WT, bool A16, int MPAD, bool EVEN>
-__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint64_t off2, int t, float (&acc)[4]) {
+__device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uint64_t off2, const int (&mg)[4], int t,
+                                                float (&acc)[4]) {
   using C = Cfg<WT, A16, MPAD>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
   uint32_t       qa, qb;
@@ -433,17 +434,17 @@ __device__ __forceinline__ void block_rows16_i8(const uint8_t *ra, uint2 bf, uin
     iq4nl_unpack_word(qa, a0, a2);
     iq4nl_unpack_word(qb, a1, a3);
     asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(kMagicBits));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]), "r"(mg[3]));
   } else {
     // byte i of the word: low nibble = element 4t + i, high nibble = element 16 + 4t + i
     a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
     a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
     asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
       : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(kMagicBits));
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf.x), "r"(bf.y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]), "r"(mg[3]));
   }
   const float da = lds_scale(ra);
   const float db = lds_scale(rb);
@@ -488,7 +489,7 @@ __device__ __forceinline__ void scale_add2(uint64_t &acc, int b0, int b1, uint64
 // registers, one per activation digit.  acc[d][0]: row g, tokens 2t and 2t + 1 of digit d; acc[d][1]: row g + 8.
 template <int WT, bool A16, bool EVEN>
 __device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], const uint64_t (&off2)[3],
-                                                  int t, uint64_t (&acc)[3][2]) {
+                                                  const int (&mg)[4], int t, uint64_t (&acc)[3][2]) {
   using C = Cfg<WT, A16, 8>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
   uint32_t       a0, a1, a2, a3;
@@ -530,13 +531,15 @@ __device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
     if constexpr (WT == kQ4) {
-      asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
           : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
-          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(kMagicBits));
+          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]),
+            "r"(mg[3]));
     } else {
-      asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
           : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
-          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(kMagicBits));
+          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]),
+            "r"(mg[3]));
     }
   }
 #pragma unroll
@@ -611,6 +614,12 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
   using C = Cfg<WT, A16, MPAD>;
   uint64_t neg_magic2;  // the pair (-kMagic, -kMagic)
   asm("mov.b64 %0, {%1, %1};" : "=l"(neg_magic2) : "f"(-kMagic));
+  // the accumulator input of every integer MMA: four registers of their own, so that the compiler
+  // keeps ONE register quad for all of them instead of assembling it before each MMA
+  int mg[4];
+  asm volatile("mov.b32 %0, %4;\n\tmov.b32 %1, %4;\n\tmov.b32 %2, %4;\n\tmov.b32 %3, %4;"
+               : "=r"(mg[0]), "=r"(mg[1]), "=r"(mg[2]), "=r"(mg[3])
+               : "r"(kMagicBits));
 #pragma unroll
   for (int i = 0; i < C::BPW; ++i) {
     const bool even = (((C::BPW % 2 == 0) ? 0 : par) + i) % 2 == 0;
@@ -626,9 +635,9 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if (even) {
-          block_rows16_wide<WT, A16, true>(ra, bf, off2, t, acc.v[rg]);
+          block_rows16_wide<WT, A16, true>(ra, bf, off2, mg, t, acc.v[rg]);
         } else {
-          block_rows16_wide<WT, A16, false>(ra, bf, off2, t, acc.v[rg]);
+          block_rows16_wide<WT, A16, false>(ra, bf, off2, mg, t, acc.v[rg]);
         }
       }
     } else if constexpr (C::I8) {
@@ -638,9 +647,9 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if (even) {
-          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, off2, t, acc.v[rg]);
+          block_rows16_i8<WT, A16, MPAD, true>(ra, bf, off2, mg, t, acc.v[rg]);
         } else {
-          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, off2, t, acc.v[rg]);
+          block_rows16_i8<WT, A16, MPAD, false>(ra, bf, off2, mg, t, acc.v[rg]);
         }
       }
     } else if constexpr (WT != kIQ4) {
@@ -665,16 +674,21 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
 // ------------------------------------------------------------------ tile completion
 
 // Bounded wait that also gives up when another role of the CTA has raised the abort flag.
+// A failed try_wait comes back within tens of cycles, so a waiting warp would otherwise spin at full
+// speed and take issue slots from the warps that have work: after a few polls it sleeps between them
+// (NS nanoseconds: short for the consumers, whose data is usually a moment away, longer for the tile
+// completion warps, which have a tile every few microseconds).
+template <int NS = 32>
 __device__ __forceinline__ bool mbar_wait_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
   for (uint32_t i = 0; i < kWaitCap; ++i) {
     if (mbar_try_wait(bar, parity)) {
       return true;
     }
-    if (i > 64) {
-      if (*abort_flag) {
+    if (i >= 4) {
+      if (i > 64 && *abort_flag) {
         return false;
       }
-      __nanosleep(64);
+      __nanosleep(NS);
     }
   }
   return false;
@@ -723,7 +737,7 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
   } else {
     m0 = 2 * t, m1 = 2 * t + 1;
   }
-  const bool arrived = mbar_wait_abort(&sm->red_full[buf], (n >> 1) & 1, &sm->abort_flag);
+  const bool arrived = mbar_wait_abort<256>(&sm->red_full[buf], (n >> 1) & 1, &sm->abort_flag);
   // (both completion warps leave together: the barriers further down need all 64 threads)
   if (!named_bar_and(2, kReduceThreads, arrived)) {
     record_error(p, kGemvErrConsumerWait);
@@ -1382,9 +1396,8 @@ size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
 bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *out) {
   GemvPlan pl;
   pl.mpad          = gemv_mpad(m);
-  pl.wide          = pl.mpad == 8;
-  pl.stage_blocks  = gemv_stage_blocks(wt, pl.wide);
-  pl.stage_bytes   = kGemvTileRows * gemv_row_pitch(wt, pl.wide);
+  pl.stage_blocks  = gemv_stage_blocks(wt);
+  pl.stage_bytes   = kGemvTileRows * gemv_row_pitch(wt);
   const int periods = kblocks / 8;
   const int budget  = smem_budget < kGemvSmemBudget ? smem_budget : kGemvSmemBudget;
   if (m < 1 || m > 8 || kblocks <= 0 || kblocks % 8 != 0) {
@@ -1410,8 +1423,7 @@ bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *
   return true;
 }
 
-cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt,
-                            bool wide) {
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt) {
   // Tensor map over a K range of the weight bytes, as 8-byte elements: inner dimension = bytes of
   // the K range per row / 8, outer = n rows, row pitch = w_row_bytes.  Encoding costs about a
   // microsecond of host time, comparable to a small launch, and a decoder re-issues the same few
@@ -1419,7 +1431,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   struct Key {
     const void *base;
     long long   row_bytes;
-    int         kblocks, n, wt, dev;  // wt: format, plus 16 for the wide path's narrower box
+    int         kblocks, n, wt, dev;
     bool operator==(const Key &o) const {
       return base == o.base && row_bytes == o.row_bytes && kblocks == o.kblocks && n == o.n && wt == o.wt &&
              dev == o.dev;
@@ -1437,7 +1449,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   static std::unordered_map<Key, CUtensorMap, KeyHash> cache;
   int                                                  dev = 0;
   cudaGetDevice(&dev);
-  const Key key{ w, w_row_bytes, kblocks, n, wt + (wide ? 16 : 0), dev };
+  const Key key{ w, w_row_bytes, kblocks, n, wt, dev };
   {
     std::lock_guard<std::mutex> lk(cache_mu);
     auto                        it = cache.find(key);
@@ -1454,7 +1466,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
   const int        bb         = wt == kQ8 ? 34 : 18;
   const cuuint64_t gdim[2]    = { (cuuint64_t) kblocks * bb / 8, (cuuint64_t) n };
   const cuuint64_t gstride[1] = { (cuuint64_t) w_row_bytes };
-  const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt, wide) / 8, (cuuint32_t) kGemvTileRows };
+  const cuuint32_t box[2]     = { (cuuint32_t) gemv_row_pitch(wt) / 8, (cuuint32_t) kGemvTileRows };
   const cuuint32_t estr[2]    = { 1, 1 };
   if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(w), gdim, gstride, box, estr,
           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1475,8 +1487,7 @@ cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_by
 cudaError_t gemv_mma_launch(const GemvArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                             cudaStream_t stream, bool pdl) {
   CUtensorMap wmap;
-  cudaError_t e =
-    gemv_weight_map(&wmap, args.w + args.w_k_off_bytes, args.w_row_bytes, args.kblocks, args.N, wt, mpad == 8);
+  cudaError_t e = gemv_weight_map(&wmap, args.w + args.w_k_off_bytes, args.w_row_bytes, args.kblocks, args.N, wt);
   if (e != cudaSuccess) {
     return e;
   }

@@ -17,26 +17,26 @@ constexpr int kGemvErrProducerWait = 101;
 constexpr int kGemvErrConsumerWait = 102;
 
 // 32-weight blocks per pipeline stage and row: 64 for Q4_0 / IQ4_NL (1152 B), 32 for Q8_0 (1088 B), so a
-// stage of 32 rows is ~36 KB in either format.  The wide path (three to eight tokens), whose
-// activation fragments take 864 bytes per block, runs on half-size stages.
-constexpr int gemv_stage_blocks(int wt, bool wide = false) {
-  return (wt == 1 ? 32 : 64) / (wide ? 2 : 1);
+// stage of 32 rows is ~36 KB in either format.
+constexpr int gemv_stage_blocks(int wt) {
+  return wt == 1 ? 32 : 64;
 }
 
 // Shared-memory pitch of one weight row inside a stage: the stage's bytes plus 16, an odd
 // multiple of 16, so that eight consecutive rows start in eight different 16-byte bank groups.
-constexpr int gemv_row_pitch(int wt, bool wide = false) {
-  return wide ? (wt == 1 ? 560 /* 16*34 = 544 -> 35*16 */ : 592 /* 32*18 = 576 -> 37*16 */)
-              : (wt == 1 ? 1104 /* 32*34 = 1088 -> 69*16 */ : 1168 /* 64*18 = 1152 -> 73*16 */);
+constexpr int gemv_row_pitch(int wt) {
+  return wt == 1 ? 1104 /* 32*34 = 1088 -> 69*16 */ : 1168 /* 64*18 = 1152 -> 73*16 */;
 }
 
 // Tokens per launch are padded to 1, 2 or 8 (8 = the wide integer path).
 constexpr int gemv_mpad(int m) {
   return m <= 1 ? 1 : (m <= 2 ? 2 : 8);
 }
-// Pipeline stages a launch needs at least: the wide path's stages are half as large.
+// Pipeline stages a launch needs at least.  The wide path (8), whose activation fragments take 864
+// bytes per block, runs K = 4096 on a two-stage ring: measured faster than more, smaller stages (the
+// hand-over per stage is what costs) and than cutting K into launches that accumulate.
 constexpr int gemv_min_stages(int mpad) {
-  return mpad == 8 ? 4 : 3;
+  return mpad == 8 ? 2 : 3;
 }
 
 struct GemvArgs {
@@ -103,8 +103,7 @@ struct GemvBatchArgs {
 };
 
 // Fills op.wmap for a weight matrix of n rows and kblocks blocks per row (cached by geometry).
-cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt,
-                            bool wide);
+cudaError_t gemv_weight_map(void *wmap_out, const uint8_t *w, long long w_row_bytes, int kblocks, int n, int wt);
 
 cudaError_t gemv_mma_batch_launch(const GemvBatchArgs &args, int wt, bool a16, int mpad, int grid, size_t smem,
                                   cudaStream_t stream, bool pdl);
@@ -118,7 +117,6 @@ size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks);
 // into the output, as launches of their own).  False when no split fits.
 struct GemvPlan {
   int  mpad;
-  bool wide;
   int  stage_blocks, stage_bytes;
   int  nchunks, chunk_periods;  // K ranges; blocks of 256 weights per range (the last may be shorter)
   int  n_stages;                // ring depth the budget allows for one range

@@ -51,8 +51,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) {
       return true;
     }
-    if (i > 64) {
-      __nanosleep(64);
+    if (i >= 4) {
+      __nanosleep(128);  // a failed try_wait returns at once: do not spin at full speed
     }
   }
   return false;
