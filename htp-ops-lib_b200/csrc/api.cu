@@ -151,6 +151,26 @@ uint8_t *act16_scratch(StreamScratch *sc, cudaStream_t st, int m, int k, float *
   return sc->act16;
 }
 
+// Room for the K-range slabs of one batch on this stream, grown when a larger batch arrives.
+float *kslab_scratch(StreamScratch *sc, cudaStream_t st, size_t need) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (need > sc->kslab_bytes) {
+    if (sc->kslab) {
+      cudaStreamSynchronize(st);
+      cudaFree(sc->kslab);
+      sc->kslab = nullptr, sc->kslab_bytes = 0;
+    }
+    const size_t bytes = need + need / 2;
+    void        *base  = nullptr;
+    if (cudaMalloc(&base, bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    sc->kslab = static_cast<uint8_t *>(base), sc->kslab_bytes = bytes;
+  }
+  return reinterpret_cast<float *>(sc->kslab);
+}
+
 void release_all_scratch() {
   std::lock_guard<std::mutex> lk(g_mu);
   int                         cur = -1;
@@ -160,6 +180,7 @@ void release_all_scratch() {
     cudaFree(kv.second.partials);
     cudaFree(kv.second.gemm_part);
     cudaFree(kv.second.act16);
+    cudaFree(kv.second.kslab);
     cudaFreeHost(kv.second.err_host);
   }
   g_scratch.clear();
@@ -403,9 +424,10 @@ bool mul_mat_batchable(int m, int k, int n, int weight_type, int act_type) {
   return gemv_plan(kGemvSmemBudget, wt, a16, m, k / 32, &pl);
 }
 
-// One persistent launch per round: round c carries K range c of every operator that has one (all of
-// them in round 0; only matrices whose activation fragments do not fit one launch after that), and
-// rounds after the first add to the outputs the earlier ones wrote - stream order keeps them apart.
+// Operators are laid end to end in persistent launches of up to kGemvBatchMaxOps entries.  An operator
+// whose activation fragments do not fit one launch is entered once per K range; each range writes a
+// slab of its own in stream scratch, and one small kernel afterwards adds the slabs into the output in
+// range order (deterministic, no atomics, no launches that wait for each other's outputs).
 int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type, int act_type, cudaStream_t st,
                           bool allow_pdl) {
   const int wt = wt_index(weight_type);
@@ -430,86 +452,119 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
   const int  bb     = wt == 1 ? 34 : 18;
   const int  budget = ctx->max_smem < kGemvSmemBudget ? ctx->max_smem : kGemvSmemBudget;
   std::vector<GemvPlan> plans((size_t) n_ops);
-  int                   rounds = 1;
+  size_t                slab_floats = 0;
   for (int i = 0; i < n_ops; ++i) {
     if (!gemv_plan(budget, wt, a16, m, d[i].k / 32, &plans[i])) {
       return -2;
     }
-    rounds = plans[i].nchunks > rounds ? plans[i].nchunks : rounds;
+    if (plans[i].nchunks > 1) {
+      slab_floats += (size_t) plans[i].nchunks * m * d[i].n;
+    }
+  }
+  float *slabs = nullptr;
+  if (slab_floats && !(slabs = kslab_scratch(sc, st, slab_floats * sizeof(float)))) {
+    return -2;
   }
   const int mpad  = plans[0].mpad;
   const int stage = plans[0].stage_bytes;
   const int sb    = plans[0].stage_blocks;
   static thread_local GemvBatchArgs args;  // ~25 KB of kernel parameters, reused between launches
-  for (int round = 0; round < rounds; ++round) {
-    int o0 = 0;
-    while (o0 < n_ops) {
-      // the next (up to) kGemvBatchMaxOps operators that have a K range number `round`
-      int       cnt   = 0;
-      long long items = 0;
-      size_t    frag  = 0;
-      int       i     = o0;
-      for (; i < n_ops && cnt < kGemvBatchMaxOps; ++i) {
-        if (plans[i].nchunks <= round) {
-          continue;
-        }
-        const MatMulDesc &q       = d[i];
-        GemvBatchOp      &op      = args.ops[cnt++];
-        const int         kb_all  = q.k / 32;
-        const int         periods = kb_all / 8;
-        const int         p0      = round * plans[i].chunk_periods;
-        const int         pn = (periods - p0) < plans[i].chunk_periods ? (periods - p0) : plans[i].chunk_periods;
-        const int         kb = pn * 8;
-        if (gemv_weight_map(op.wmap, q.w + (size_t) p0 * 8 * bb, (long long) kb_all * bb, kb, q.n, wt) != cudaSuccess) {
-          cudaGetLastError();
-          return -2;
-        }
-        op.y               = q.y;
-        op.x               = q.x;
-        op.item_begin      = items;
-        op.N               = q.n;
-        op.kblocks         = kb;
-        op.x_stride        = q.k;
-        op.x_k_off         = p0 * 256;
-        op.accumulate      = round > 0;
-        op.stages_per_tile = (kb + sb - 1) / sb;
-        items += (long long) (q.n / kGemvTileRows) * op.stages_per_tile;
-        const size_t f = gemv_frag_bytes(wt, a16, mpad, kb);
-        frag           = f > frag ? f : frag;
-      }
-      o0 = i;
-      if (cnt == 0) {
-        break;
-      }
-      args.total_items = items;
-      args.partials    = sc->partials;
-      args.counters    = sc->counters;
-      args.err         = sc->err;
-      args.n_ops       = cnt;
-      args.M           = m;
-      args.frag_bytes  = (int) frag;
-      long long grid   = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
-      if (grid > items) {
-        grid = items;
-      }
-      int nst = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
-      nst     = nst > kGemvMaxStages ? kGemvMaxStages : nst;
-      const long long per_cta = (items + grid - 1) / grid;
-      if (nst > per_cta) {
-        nst = (int) (per_cta < 2 ? 2 : per_cta);
-      }
-      if (nst < 2) {
+  static thread_local KSumArgs      sums;
+  sums.n_ops = 0;
+  auto flush_sums = [&]() -> bool {
+    if (sums.n_ops == 0) {
+      return true;
+    }
+    if (k_range_sum_launch(sums, st) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    count_launch();
+    sums.n_ops = 0;
+    return true;
+  };
+  int       cnt   = 0;
+  long long items = 0;
+  size_t    frag  = 0;
+  auto launch_entries = [&]() -> bool {
+    if (cnt == 0) {
+      return true;
+    }
+    args.total_items = items;
+    args.partials    = sc->partials;
+    args.counters    = sc->counters;
+    args.err         = sc->err;
+    args.n_ops       = cnt;
+    args.M           = m;
+    args.frag_bytes  = (int) frag;
+    long long grid   = ctx->sm_count < kGemvMaxGrid ? ctx->sm_count : kGemvMaxGrid;
+    if (grid > items) {
+      grid = items;
+    }
+    int nst = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
+    nst     = nst > kGemvMaxStages ? kGemvMaxStages : nst;
+    const long long per_cta = (items + grid - 1) / grid;
+    if (nst > per_cta) {
+      nst = (int) (per_cta < 2 ? 2 : per_cta);
+    }
+    if (nst < 2) {
+      return false;
+    }
+    args.n_stages     = nst;
+    const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
+    if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    count_launch();
+    cnt = 0, items = 0, frag = 0;
+    return true;
+  };
+  size_t slab_at = 0;
+  for (int i = 0; i < n_ops; ++i) {
+    const MatMulDesc &q       = d[i];
+    const int         kb_all  = q.k / 32;
+    const int         periods = kb_all / 8;
+    const int         nch     = plans[i].nchunks;
+    float            *slab    = nch > 1 ? slabs + slab_at : nullptr;
+    for (int c = 0; c < nch; ++c) {
+      if (cnt == kGemvBatchMaxOps && !launch_entries()) {
         return -2;
       }
-      args.n_stages     = nst;
-      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
-      if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) !=
-          cudaSuccess) {
+      GemvBatchOp &op = args.ops[cnt++];
+      const int    p0 = c * plans[i].chunk_periods;
+      const int    pn = (periods - p0) < plans[i].chunk_periods ? (periods - p0) : plans[i].chunk_periods;
+      const int    kb = pn * 8;
+      if (gemv_weight_map(op.wmap, q.w + (size_t) p0 * 8 * bb, (long long) kb_all * bb, kb, q.n, wt) != cudaSuccess) {
         cudaGetLastError();
         return -2;
       }
-      count_launch();
+      op.y               = slab ? slab + (size_t) c * m * q.n : q.y;
+      op.x               = q.x;
+      op.item_begin      = items;
+      op.N               = q.n;
+      op.kblocks         = kb;
+      op.x_stride        = q.k;
+      op.x_k_off         = p0 * 256;
+      op.accumulate      = 0;
+      op.stages_per_tile = (kb + sb - 1) / sb;
+      items += (long long) (q.n / kGemvTileRows) * op.stages_per_tile;
+      const size_t f = gemv_frag_bytes(wt, a16, mpad, kb);
+      frag           = f > frag ? f : frag;
     }
+    if (slab) {
+      slab_at += (size_t) nch * m * q.n;
+      if (sums.n_ops == kKSumMaxOps) {
+        // the sums read what the entries collected so far write: issue those first
+        if (!launch_entries() || !flush_sums()) {
+          return -2;
+        }
+      }
+      sums.ops[sums.n_ops++] = KSumOp{ q.y, slab, (long long) m * q.n, nch };
+    }
+  }
+  if (!launch_entries() || !flush_sums()) {
+    return -2;
   }
   return 0;
 }

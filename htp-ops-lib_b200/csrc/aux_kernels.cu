@@ -303,7 +303,31 @@ __global__ void __launch_bounds__(256) act_f32_to_f16_kernel(__half *dst, float 
   }
 }
 
+// y[i] = part[0][i] + part[1][i] + ... (fixed order) for up to kKSumMaxOps outputs at once: the K
+// ranges of a batched mat-vec whose activation fragments do not fit one launch each write their own
+// slab, this adds them.  blockIdx.y = output, blockIdx.x strides over its elements.
+__global__ void __launch_bounds__(256) k_range_sum_kernel(const __grid_constant__ KSumArgs a) {
+  const KSumOp &op = a.ops[blockIdx.y];
+  for (long long i = (long long) blockIdx.x * 256 + threadIdx.x; i < op.count; i += (long long) gridDim.x * 256) {
+    float v = op.part[i];
+    for (int c = 1; c < op.n_parts; ++c) {
+      v += op.part[(long long) c * op.count + i];
+    }
+    op.y[i] = v;
+  }
+}
+
 }  // namespace
+
+cudaError_t k_range_sum_launch(const KSumArgs &args, cudaStream_t stream) {
+  long long most = 0;
+  for (int i = 0; i < args.n_ops; ++i) {
+    most = args.ops[i].count > most ? args.ops[i].count : most;
+  }
+  const int bx = (int) ((most + 2047) / 2048 < 1 ? 1 : ((most + 2047) / 2048 > 64 ? 64 : (most + 2047) / 2048));
+  k_range_sum_kernel<<<dim3(bx, args.n_ops), 256, 0, stream>>>(args);
+  return cudaGetLastError();
+}
 
 cudaError_t act_f32_to_f16_launch(void *dst_f16, float *inv_scale, const float *src, int m, int k,
                                   cudaStream_t stream) {

@@ -19,6 +19,20 @@ cudaError_t block_sums_launch(const uint8_t *w, int32_t *s, int32_t *t, long lon
 // [2^14, 2^15)); inv_scale[token] undoes the scale on the outputs.  k % 4 == 0, rows 16-byte aligned.
 cudaError_t act_f32_to_f16_launch(void *dst_f16, float *inv_scale, const float *src, int m, int k, cudaStream_t stream);
 
+// Sums of K-range slabs: y[i] = sum over c < n_parts of part[c * count + i], i < count, in that order.
+constexpr int kKSumMaxOps = 64;
+struct KSumOp {
+  float       *y;
+  const float *part;
+  long long    count;
+  int          n_parts;
+};
+struct KSumArgs {
+  KSumOp ops[kKSumMaxOps];
+  int    n_ops;
+};
+cudaError_t k_range_sum_launch(const KSumArgs &args, cudaStream_t stream);
+
 cudaError_t rms_norm_f32_launch(float *dst, const float *src, int ne0, int ne1, cudaStream_t stream);
 
 }  // namespace htp

@@ -15,6 +15,8 @@ struct StreamScratch {
   float    *gemm_part = nullptr;  // split-tile scratch of the prefill GEMM, allocated on its first use
   uint8_t  *act16     = nullptr;  // fp16 copies of fp32 activations for the GEMM + their per-token scales
   size_t    act16_bytes = 0;
+  uint8_t  *kslab      = nullptr;  // partial outputs of the K ranges of batched mat-vecs, summed afterwards
+  size_t    kslab_bytes = 0;
 };
 
 struct DeviceCtx {

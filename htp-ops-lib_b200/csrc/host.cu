@@ -162,6 +162,8 @@ uint8_t *resolve(const RpcmemBufAddr &a, size_t bytes) {
   return b.ptr + off;
 }
 
+constexpr int kFlushOps = 64;  // operators collected before a batch is issued without waiting for more
+
 // Issues the collected batch (if any).  Returns 0 or the launch error.
 int flush_batch() {
   PendingBatch &b = g.batch;
@@ -277,6 +279,12 @@ int enqueue_op(const OpComputeRequest *req, RequestHeader *owner) {
   b.reads.add(w0, w0 + w_bytes);
   b.weights_hazard = b.weights_hazard || weights_hazard;
   g.pending_out.add(o0, o0 + out_bytes);
+  // A long message (a decoder's 224 requests) is issued in pieces: the GPU starts on the first
+  // kFlushOps operators while the host is still reading the rest (about half a microsecond per
+  // request), instead of idling until the whole message has been parsed.
+  if ((int) b.ops.size() >= kFlushOps) {
+    flush_batch();  // a launch failure lands in the owners' request states
+  }
   return 0;
 }
 
