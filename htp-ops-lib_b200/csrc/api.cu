@@ -298,7 +298,7 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       a.partials = sc->partials;
       a.counters = sc->counters;
       a.err      = sc->err;
-      const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) a.n_stages * pl.stage_bytes;
+      const size_t smem = (size_t) gemv_header_bytes(pl.mpad) + frag + (size_t) a.n_stages * pl.stage_bytes;
       if (gemv_mma_launch(a, wt, a16, pl.mpad, (int) grid, smem, stream, pdl) != cudaSuccess) {
         cudaGetLastError();
         return -2;
@@ -501,7 +501,7 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
     if (grid > items) {
       grid = items;
     }
-    int nst = (int) (((long) budget - kGemvSmemHeader - (long) frag) / stage);
+    int nst = (int) (((long) budget - gemv_header_bytes(mpad) - (long) frag) / stage);
     nst     = nst > kGemvMaxStages ? kGemvMaxStages : nst;
     const long long per_cta = (items + grid - 1) / grid;
     if (nst > per_cta) {
@@ -511,7 +511,7 @@ int mul_mat_batch_checked(const MatMulDesc *d, int n_ops, int m, int weight_type
       return false;
     }
     args.n_stages     = nst;
-    const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) nst * stage;
+    const size_t smem = (size_t) gemv_header_bytes(mpad) + frag + (size_t) nst * stage;
     if (gemv_mma_batch_launch(args, wt, a16, mpad, (int) grid, smem, st, allow_pdl && g_opt_pdl != 0) != cudaSuccess) {
       cudaGetLastError();
       return false;

@@ -75,8 +75,14 @@ struct Cfg {
   static constexpr int  STAGE    = kGemvTileRows * PSTRIDE;
   // uint2 entries per block: two k-steps of fp16 fragments, or one int8 fragment per column and lane
   // position (per MMA) followed by the columns' accumulator inputs (one int each)
-  static constexpr int  FRAG_U2  = WIDE ? 3 * 32 + 12 : (I8 ? NC * 4 + NC / 2 : 2 * NC * 4);
-  static constexpr int  CIN_OFF  = WIDE ? 3 * 32 : NC * 4;  // where a block's accumulator inputs start
+  // (the wide path needs no offsets: its Q4_0 nibbles go in as signed bytes 16 (q - 8))
+  static constexpr int  FRAG_U2  = WIDE ? 3 * 32 : (I8 ? NC * 4 + NC / 2 : 2 * NC * 4);
+  static constexpr int  CIN_OFF  = NC * 4;  // where a block's offsets start (one or two tokens)
+  // Copies of the cross-warp reduction buffer: two, so that a tile is handed over while the one before
+  // is still being added up; the wide path gives the second copy's 16 KB to the pipeline (a third
+  // stage at K = 4096) - its tiles are far enough apart.
+  static constexpr int  RED_BUFS = WIDE ? 1 : 2;
+  static constexpr int  HEADER   = gemv_header_bytes(MPAD);
 };
 
 struct Smem {
@@ -95,13 +101,15 @@ struct Smem {
   uint64_t red_empty[2];
   uint64_t op_bar;  // batched launch: the consumer warps meet here before an operator's activations replace the last one's
   uint8_t  pad2[88];
-  float    red[2][kConsumerWarps][256];
   // finished tile [token][row] of a launch with several destinations: staged here so that the copies
   // leave as 16-byte stores, 128 contiguous bytes per token and destination
   float    out_tile[8][kGemvTileRows];
+  // (last: a path that uses one copy only starts its fragments where the second copy would be)
+  float    red[2][kConsumerWarps][256];
 };
 static_assert(sizeof(Smem) % 128 == 0, "keep the regions after the header 128-byte aligned");
-static_assert(sizeof(Smem) == kGemvSmemHeader, "host-side size computation must match");
+static_assert(sizeof(Smem) == gemv_header_bytes(1) && sizeof(Smem) - sizeof(float) * kConsumerWarps * 256 == gemv_header_bytes(8),
+              "host-side size computation must match");
 
 __device__ __forceinline__ void record_error(const GemvArgs &p, int code) {
   atomicCAS(p.err, 0, code);
@@ -218,8 +226,9 @@ __device__ void build_x_frags_int(const GemvArgs &p, Smem *sm, uint2 *frags, int
     int       sh   = ((bits >> 23) & 0xff) - 127 + 1;  // amax < 2^sh
     sh             = sh < -90 ? -90 : (sh > 90 ? 90 : sh);
     sm->tok_scale[tid] = __int_as_float((127 + SHIFT - sh) << 23);  // x -> fixed point
-    // wide path: the digit weights 256^d are applied as they are, the common 2^-22 here
-    sm->tok_inv[tid]   = __int_as_float((127 + sh - (C::WIDE ? SHIFT : 0)) << 23);
+    // wide path: the digit weights 256^d are applied as they are, the common 2^-22 here - and 2^-4
+    // for Q4_0, whose nibbles go into the MMA as 16 (q - 8)
+    sm->tok_inv[tid]   = __int_as_float((127 + sh - (C::WIDE ? SHIFT + (WT == kQ4 ? 4 : 0) : 0)) << 23);
   }
   named_bar_sync(1, kConsumerThreads);
 
@@ -272,12 +281,14 @@ __device__ void build_x_frags_int(const GemvArgs &p, Smem *sm, uint2 *frags, int
           }
           const int col    = C::WIDE ? 8 * d + m : 4 * m + d;
           dst[col * 4 + t] = make_uint2(w[0], w[1]);
-          int sd           = __dp4a((int) w[0], 0x01010101, __dp4a((int) w[1], 0x01010101, 0));  // sum of the 8 digits
-          sd += __shfl_xor_sync(0xffffffffu, sd, 1);
-          sd += __shfl_xor_sync(0xffffffffu, sd, 2);
-          if (t == 0) {
-            // (Q4_0: value = nibble - 8; Q8_0 and IQ4_NL bytes are the values themselves)
-            reinterpret_cast<float *>(dst + C::CIN_OFF)[col] = -kMagic - (WT == kQ4 ? 8.f * (float) sd : 0.f);
+          if constexpr (!C::WIDE) {
+            int sd = __dp4a((int) w[0], 0x01010101, __dp4a((int) w[1], 0x01010101, 0));  // sum of the 8 digits
+            sd += __shfl_xor_sync(0xffffffffu, sd, 1);
+            sd += __shfl_xor_sync(0xffffffffu, sd, 2);
+            if (t == 0) {
+              // (Q4_0: value = nibble - 8; IQ4_NL bytes are the values themselves)
+              reinterpret_cast<float *>(dst + C::CIN_OFF)[col] = -kMagic - (WT == kQ4 ? 8.f * (float) sd : 0.f);
+            }
           }
         }
       }
@@ -488,7 +499,7 @@ __device__ __forceinline__ void scale_add2(uint64_t &acc, int b0, int b1, uint64
 // Wide integer path: one block x 16 rows x eight tokens = THREE m16n8k32 MMAs on the same weight
 // registers, one per activation digit.  acc[d][0]: row g, tokens 2t and 2t + 1 of digit d; acc[d][1]: row g + 8.
 template <int WT, bool A16, bool EVEN>
-__device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], const uint64_t (&off2)[3],
+__device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2 (&bf)[3], uint64_t neg_magic2,
                                                   const int (&mg)[4], int t, uint64_t (&acc)[3][2]) {
   using C = Cfg<WT, A16, 8>;
   const uint8_t *rb = ra + 8 * C::PSTRIDE;
@@ -519,8 +530,11 @@ __device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2
       iq4nl_unpack_word(qa, a0, a2);
       iq4nl_unpack_word(qb, a1, a3);
     } else {
-      a0 = qa & 0x0F0F0F0Fu, a2 = (qa >> 4) & 0x0F0F0F0Fu;
-      a1 = qb & 0x0F0F0F0Fu, a3 = (qb >> 4) & 0x0F0F0F0Fu;
+      // q - 8 is the nibble q ^ 8 read as a signed 4-bit number: in the high half of a byte that is the
+      // signed byte 16 (q - 8) - no offset to take out afterwards (the 16 leaves with the output scale)
+      const uint32_t ta = qa ^ 0x88888888u, tb = qb ^ 0x88888888u;
+      a0 = (ta << 4) & 0xF0F0F0F0u, a2 = ta & 0xF0F0F0F0u;
+      a1 = (tb << 4) & 0xF0F0F0F0u, a3 = tb & 0xF0F0F0F0u;
     }
   }
   const float    da  = lds_scale(ra);
@@ -530,22 +544,14 @@ __device__ __forceinline__ void block_rows16_wide(const uint8_t *ra, const uint2
   int r[3][4];
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
-    if constexpr (WT == kQ4) {
-      asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-          : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
-          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]),
-            "r"(mg[3]));
-    } else {
-      asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-          : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
-          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]),
-            "r"(mg[3]));
-    }
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(r[d][0]), "=r"(r[d][1]), "=r"(r[d][2]), "=r"(r[d][3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(bf[d].x), "r"(bf[d].y), "r"(mg[0]), "r"(mg[1]), "r"(mg[2]), "r"(mg[3]));
   }
 #pragma unroll
   for (int d = 0; d < 3; ++d) {
-    scale_add2(acc[d][0], r[d][0], r[d][1], da2, off2[d]);
-    scale_add2(acc[d][1], r[d][2], r[d][3], db2, off2[d]);
+    scale_add2(acc[d][0], r[d][0], r[d][1], da2, neg_magic2);
+    scale_add2(acc[d][1], r[d][2], r[d][3], db2, neg_magic2);
   }
 }
 
@@ -624,20 +630,18 @@ __device__ __forceinline__ void stage_blocks(const uint8_t *sb, const uint2 *fp,
   for (int i = 0; i < C::BPW; ++i) {
     const bool even = (((C::BPW % 2 == 0) ? 0 : par) + i) % 2 == 0;
     if constexpr (C::WIDE) {
-      uint2    bf[3];
-      uint64_t off2[3];
+      uint2 bf[3];
 #pragma unroll
       for (int d = 0; d < 3; ++d) {
-        bf[d]   = fp[i * C::FRAG_U2 + d * 32];
-        off2[d] = WT == kQ4 ? *reinterpret_cast<const uint64_t *>(cp + i * C::FRAG_U2 + d * 4) : neg_magic2;
+        bf[d] = fp[i * C::FRAG_U2 + d * 32];
       }
 #pragma unroll
       for (int rg = 0; rg < 2; ++rg) {
         const uint8_t *ra = sb + rg * 16 * C::PSTRIDE + i * C::BB;
         if (even) {
-          block_rows16_wide<WT, A16, true>(ra, bf, off2, mg, t, acc.v[rg]);
+          block_rows16_wide<WT, A16, true>(ra, bf, neg_magic2, mg, t, acc.v[rg]);
         } else {
-          block_rows16_wide<WT, A16, false>(ra, bf, off2, mg, t, acc.v[rg]);
+          block_rows16_wide<WT, A16, false>(ra, bf, neg_magic2, mg, t, acc.v[rg]);
         }
       }
     } else if constexpr (C::I8) {
@@ -699,8 +703,9 @@ __device__ __forceinline__ bool mbar_wait_abort(uint64_t *bar, uint32_t parity, 
 // last used by completion n - 2, which the completion warps have read once red_empty says so.
 template <class C>
 __device__ __forceinline__ bool publish_tile(Smem *sm, const TileAcc<C> &tile_acc, int warp, int lane, unsigned n) {
-  const int buf = n & 1;
-  if (n >= 2 && !mbar_wait_abort(&sm->red_empty[buf], ((n >> 1) - 1) & 1, &sm->abort_flag)) {
+  constexpr unsigned NB  = C::RED_BUFS;
+  const int          buf = (int) (n % NB);
+  if (n >= NB && !mbar_wait_abort(&sm->red_empty[buf], ((n / NB) - 1) & 1, &sm->abort_flag)) {
     return false;
   }
   float acc[2][4];
@@ -724,7 +729,8 @@ template <int WT, bool A16, int MPAD>
 __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long long it0, long long it1, int S, int rg,
                               int lane, unsigned n) {
   using C = Cfg<WT, A16, MPAD>;
-  const int buf = n & 1;
+  constexpr unsigned NB  = C::RED_BUFS;
+  const int          buf = (int) (n % NB);
   const int g = lane >> 2, t = lane & 3;
   // which token the lane's results belong to, and whether this lane writes them out
   int  m0, m1;  // tokens of (column 2t, column 2t + 1); equal when the columns are pieces of one token
@@ -737,7 +743,7 @@ __device__ bool complete_tile(const GemvArgs &p, Smem *sm, long long tile, long 
   } else {
     m0 = 2 * t, m1 = 2 * t + 1;
   }
-  const bool arrived = mbar_wait_abort<256>(&sm->red_full[buf], (n >> 1) & 1, &sm->abort_flag);
+  const bool arrived = mbar_wait_abort<256>(&sm->red_full[buf], (n / NB) & 1, &sm->abort_flag);
   // (both completion warps leave together: the barriers further down need all 64 threads)
   if (!named_bar_and(2, kReduceThreads, arrived)) {
     record_error(p, kGemvErrConsumerWait);
@@ -871,8 +877,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   using C = Cfg<WT, A16, MPAD>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem    *sm     = reinterpret_cast<Smem *>(smem_raw);
-  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + sizeof(Smem));
-  uint8_t *stages = smem_raw + sizeof(Smem) + (((size_t) p.kblocks * C::FRAG_U2 * 8 + 127) & ~(size_t) 127);
+  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + C::HEADER);
+  uint8_t *stages = smem_raw + C::HEADER + (((size_t) p.kblocks * C::FRAG_U2 * 8 + 127) & ~(size_t) 127);
 
   const int       warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int       S   = p.stages_per_tile;
@@ -1103,8 +1109,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
   using C = Cfg<WT, A16, MPAD>;
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Smem    *sm     = reinterpret_cast<Smem *>(smem_raw);
-  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + sizeof(Smem));
-  uint8_t *stages = smem_raw + sizeof(Smem) + b.frag_bytes;
+  uint2   *frags  = reinterpret_cast<uint2 *>(smem_raw + C::HEADER);
+  uint8_t *stages = smem_raw + C::HEADER + b.frag_bytes;
 
   const int       warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int       NST = b.n_stages;
@@ -1276,7 +1282,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_batch_kernel(const __gri
             // every consumer warp has stopped reading the fragments (the barriers below)
             // (an mbarrier, not bar.sync: a warp that has given up a wait never gets here, and the
             // others must not wait for it for ever)
-            bool go = mbar_wait_abort(&sm->red_empty[(n_done - 1) & 1], ((n_done - 1) >> 1) & 1, &sm->abort_flag);
+            bool go = mbar_wait_abort(&sm->red_empty[(n_done - 1) % C::RED_BUFS], ((n_done - 1) / C::RED_BUFS) & 1,
+                                      &sm->abort_flag);
             if (go) {
               __syncwarp();
               if (lane == 0) {
@@ -1381,8 +1388,8 @@ cudaError_t flags_wait_launch(const unsigned *flags, int n, unsigned epoch, int 
 
 size_t gemv_frag_bytes(int wt, bool a16, int mpad, int kblocks) {
   size_t b;
-  if (mpad == 8) {  // wide integer path: three digit sets of 8 columns + 24 accumulator inputs
-    b = (size_t) kblocks * (3 * 32 + 12) * 8;
+  if (mpad == 8) {  // wide integer path: three digit sets of 8 columns
+    b = (size_t) kblocks * (3 * 32) * 8;
   } else if (wt == kQ4 || wt == kIQ4) {  // integer path: 4 digit columns per token + their accumulator inputs
     const int nc = 4 * mpad;
     b            = (size_t) kblocks * (nc * 4 + nc / 2) * 8;
@@ -1406,7 +1413,7 @@ bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *
   for (pl.nchunks = 1;; ++pl.nchunks) {
     pl.chunk_periods  = (periods + pl.nchunks - 1) / pl.nchunks;
     const size_t frag = gemv_frag_bytes(wt, a16, pl.mpad, pl.chunk_periods * 8);
-    const long   room = (long) budget - kGemvSmemHeader - (long) frag;
+    const long   room = (long) budget - gemv_header_bytes(pl.mpad) - (long) frag;
     pl.n_stages       = room > 0 ? (int) (room / pl.stage_bytes) : 0;
     if (pl.n_stages > kGemvMaxStages) {
       pl.n_stages = kGemvMaxStages;

@@ -9,7 +9,11 @@ namespace htp {
 
 constexpr int kGemvTileRows    = 32;  // output rows per tile (two 16-row MMA groups)
 constexpr int kGemvMaxStages   = 8;
-constexpr int kGemvSmemHeader  = 34176;   // barriers, per-token scales, cross-warp reduction buffer
+// Fixed part of the kernel's shared memory: barriers, per-token scales, the output staging tile and
+// two copies (one on the wide path, token padding 8) of the 16 KB cross-warp reduction buffer.
+constexpr int gemv_header_bytes(int mpad) {
+  return mpad == 8 ? 17792 : 34176;
+}
 constexpr int kGemvSmemBudget  = 232448;  // 227 KiB opt-in dynamic shared memory per CTA on sm_100
 constexpr int kGemvMaxGrid     = 1024;    // scratch is sized for this many CTAs
 

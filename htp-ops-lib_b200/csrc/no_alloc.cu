@@ -143,7 +143,7 @@ extern "C" int htp_b200_mul_mat_static_scratch(void *dst, const void *activation
     cudaGetLastError();
     return -2;
   }
-  const size_t smem = (size_t) kGemvSmemHeader + frag + (size_t) a.n_stages * stage;
+  const size_t smem = (size_t) gemv_header_bytes(mpad) + frag + (size_t) a.n_stages * stage;
   // plain stream order (no programmatic dependent launch): the memset above must be complete
   if (gemv_mma_launch(a, wt, a16, mpad, (int) grid, smem, st, false) != cudaSuccess) {
     cudaGetLastError();

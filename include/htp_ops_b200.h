@@ -87,7 +87,7 @@ int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activ
  *     call does not).  That holds for every k <= 4096, and beyond it up to:
  *       m = 1:      k <= 18944 (Q4_0, IQ4_NL), 23040 (Q8_0, fp32 act.), 46080 (Q8_0, fp16 act.)
  *       m = 2:      k <=  9472 (Q4_0, IQ4_NL), 11520 (Q8_0, fp32 act.), 23040 (Q8_0, fp16 act.)
- *       m = 3 .. 8: k <=  4352 (Q4_0, IQ4_NL),  4608 (Q8_0)
+ *       m = 3 .. 8: k <=  5632 (Q4_0, IQ4_NL),  5888 (Q8_0)
  *     Outside the range the call prints the reason to stderr and returns -3.
  *   - All calls on a device share the one array, which keeps the previous call's contents; what
  *     must start at zero is cleared on `stream` at the start of each call.  Calls that overlap on

@@ -45,9 +45,10 @@ def raw(dev, x, wq, n, wtype):
     return ty.cpu().numpy()
 
 
-# K = 4352 / 4608: the largest K whose fragments fit one launch (Q4_0 / Q8_0); 4864, 14336: K ranges
-# that accumulate; 2048 x 4000: tiles cut by CTA range boundaries; 256 x 32: a single, partial stage
-SHAPES = [(256, 32), (2048, 4000 // 32 * 32), (4096, 1024), (4352, 64), (4608, 96), (4864, 64), (14336, 96)]
+# K = 5632 / 5888: the largest K whose fragments fit one launch (Q4_0 / Q8_0); 6144, 14336: K ranges
+# that accumulate; 2048 x 4000: tiles cut by CTA range boundaries; 256 x 32: a single, partial stage;
+# 4352: a two-stage ring; 4096: three stages
+SHAPES = [(256, 32), (2048, 4000 // 32 * 32), (4096, 1024), (4352, 64), (5632, 96), (5888, 64), (6144, 64), (14336, 96)]
 
 
 @pytest.mark.parametrize("wtype", [2, 8, 20])

@@ -56,18 +56,18 @@ def test_static_scratch_entry_point_rejects_what_it_cannot_hold(dev, wl):
     assert fn(y, a, w, 1, 96, 32, 2, 0, st) == -3  # k not a multiple of 256
     assert fn(y, a, w, 8, 14336, 32, 2, 0, st) == -3  # fragments of the whole k do not fit
     # the limits the header states: one K range only.  Q4_0, fp32: k = 14336 fits at m = 1, not at m = 2;
-    # three to eight tokens: k <= 4352 (Q4_0, IQ4_NL) / 4608 (Q8_0)
+    # three to eight tokens: k <= 5632 (Q4_0, IQ4_NL) / 5888 (Q8_0)
     big = dev.buf(14336 // 32 * 34 * 32)
     wb = lib.htp_buf_ptr(big)
     xb = lib.htp_buf_ptr(dev.buf(8 * 14336 * 4))
     assert fn(y, xb, wb, 1, 14336, 32, 2, 0, st) == 0
     assert fn(y, xb, wb, 2, 14336, 32, 2, 0, st) == -3
     assert fn(y, xb, wb, 2, 9472, 32, 2, 0, st) == 0
-    assert fn(y, xb, wb, 8, 4352, 32, 2, 0, st) == 0
-    assert fn(y, xb, wb, 8, 4608, 32, 2, 0, st) == -3
-    assert fn(y, xb, wb, 8, 4608, 32, 8, 0, st) == 0
-    assert fn(y, xb, wb, 8, 4864, 32, 8, 0, st) == -3
-    assert fn(y, xb, wb, 3, 4352, 32, 20, 1, st) == 0
+    assert fn(y, xb, wb, 8, 5632, 32, 2, 0, st) == 0
+    assert fn(y, xb, wb, 8, 5888, 32, 2, 0, st) == -3
+    assert fn(y, xb, wb, 8, 5888, 32, 8, 0, st) == 0
+    assert fn(y, xb, wb, 8, 6144, 32, 8, 0, st) == -3
+    assert fn(y, xb, wb, 3, 5632, 32, 20, 1, st) == 0
     assert fn(y, a, w, 1, 256, 40, 2, 0, st) == -1  # the ordinary argument checks still apply
     assert fn(None, a, w, 1, 256, 32, 2, 0, st) == -1
     assert fn(y, a, w, 1, 256, 32, 2, 0, st) == 0
