@@ -241,7 +241,18 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
       return -2;
     }
     if (band && pl.nchunks > 1) {
-      return -1;  // K split over accumulating launches: not offered with several destinations
+      return -1;  // K cut into ranges: not offered with several destinations
+    }
+    if (pl.nchunks > 1) {
+      // the ranges run as entries of ONE persistent launch, each into a slab of its own, and a small
+      // kernel adds the slabs (the batched form, with one operator)
+      const MatMulDesc one = { dst + (size_t) m0 * n, static_cast<const uint8_t *>(act) + (size_t) m0 * k * asz, w, k, n };
+      const int        rc  = mul_mat_batch_checked(&one, 1, mm, wt == 0 ? 2 : (wt == 1 ? 8 : 20),
+                                                   a16 ? HTP_B200_ACT_F16 : HTP_B200_ACT_F32, stream, pdl);
+      if (rc != 0) {
+        return rc;
+      }
+      continue;
     }
     if (band && band->flags && m > slice) {
       return -1;  // the completion signal belongs to ONE launch

@@ -1410,20 +1410,33 @@ bool gemv_plan(int smem_budget, int wt, bool a16, int m, int kblocks, GemvPlan *
   if (m < 1 || m > 8 || kblocks <= 0 || kblocks % 8 != 0) {
     return false;
   }
-  for (pl.nchunks = 1;; ++pl.nchunks) {
-    pl.chunk_periods  = (periods + pl.nchunks - 1) / pl.nchunks;
-    const size_t frag = gemv_frag_bytes(wt, a16, pl.mpad, pl.chunk_periods * 8);
+  auto stages_for = [&](int chunk_periods) {
+    const size_t frag = gemv_frag_bytes(wt, a16, pl.mpad, chunk_periods * 8);
     const long   room = (long) budget - gemv_header_bytes(pl.mpad) - (long) frag;
-    pl.n_stages       = room > 0 ? (int) (room / pl.stage_bytes) : 0;
-    if (pl.n_stages > kGemvMaxStages) {
-      pl.n_stages = kGemvMaxStages;
+    const int    nst  = room > 0 ? (int) (room / pl.stage_bytes) : 0;
+    return nst > kGemvMaxStages ? kGemvMaxStages : nst;
+  };
+  const int need = gemv_min_stages(pl.mpad);
+  pl.chunk_periods = periods;
+  pl.n_stages      = stages_for(periods);
+  if (pl.n_stages < need) {
+    // K does not fit one launch: ranges of whole pipeline stages (a partly filled stage costs the
+    // consumers as much as a full one), the longest that leave room for the ring
+    const int spb = pl.stage_blocks / 8;  // blocks of 256 weights per stage
+    int       cp  = (periods - 1) / spb * spb;
+    for (; cp >= spb; cp -= spb) {
+      if (stages_for(cp) >= need) {
+        break;
+      }
     }
-    if (pl.n_stages >= gemv_min_stages(pl.mpad) || (pl.n_stages >= 2 && pl.chunk_periods == 1)) {
-      break;
+    if (cp < spb) {
+      cp = 1;  // (not reached with 227 KB of shared memory: one stage of K always fits)
+      if (stages_for(cp) < 2) {
+        return false;
+      }
     }
-    if (pl.chunk_periods == 1) {
-      return false;  // cannot happen on a device with >= 96 KiB of shared memory
-    }
+    pl.chunk_periods = cp;
+    pl.n_stages      = stages_for(cp);
   }
   pl.nchunks = (periods + pl.chunk_periods - 1) / pl.chunk_periods;
   *out       = pl;
