@@ -51,6 +51,7 @@ EXPORTS = {
     "htp_b200_mul_mat_batch": (_i, [_i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "htp_b200_mul_mat_static_scratch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "htp_b200_block_sums": (_i, [_vp, _vp, _vp, _i64, _i, _vp]),
+    "htp_b200_decode_plan": (_i, [_i, _i, _i, _i, ctypes.POINTER(_i), ctypes.POINTER(_i), ctypes.POINTER(_i)]),
     "htp_b200_rms_norm_f32": (_i, [_vp, _vp, _i, _i, _vp]),
     "htp_b200_mul_mat_multi_dst": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "htp_b200_mul_mat_multi_dst_signal": (_i, [_vp, _i, _i64, _i64, _vp, _vp, _i, _i, _i, _i, _i, _vp, ctypes.c_uint32,

@@ -606,6 +606,27 @@ int htp_b200_mul_mat_batch(int n_ops, void *const *dst, const void *const *activ
   return mul_mat_batch_checked(d.data(), n_ops, m, weight_type, act_type, static_cast<cudaStream_t>(stream), true);
 }
 
+int htp_b200_decode_plan(int m, int k, int weight_type, int act_type, int *k_ranges, int *range_k, int *stages) {
+  const int wt = wt_index(weight_type);
+  if (wt < 0 || m < 1 || m > 8 || k <= 0 || k % 256 != 0 || (act_type != HTP_B200_ACT_F32 && act_type != HTP_B200_ACT_F16)) {
+    return -1;
+  }
+  GemvPlan pl;
+  if (!gemv_plan(kGemvSmemBudget, wt, act_type == HTP_B200_ACT_F16, m, k / 32, &pl)) {
+    return -1;
+  }
+  if (k_ranges) {
+    *k_ranges = pl.nchunks;
+  }
+  if (range_k) {
+    *range_k = pl.chunk_periods * 256;
+  }
+  if (stages) {
+    *stages = pl.n_stages;
+  }
+  return 0;
+}
+
 int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_blocks, int weight_type, void *stream) {
   const int wt   = wt_index(weight_type);
   const int tfmt = tile_fmt_index(weight_type);

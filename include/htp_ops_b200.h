@@ -100,6 +100,18 @@ int htp_b200_mul_mat_static_scratch(void *dst, const void *activation, const voi
                                     int weight_type, int act_type, void *stream);
 
 /*
+ * How the decode kernel would run m (1..8) tokens over k (a multiple of 256) weights per row of a block
+ * format on a device with 227 KB of shared memory per CTA: into how many K ranges the row is cut
+ * (*k_ranges; 1 = the activation fragments of the whole k fit one launch, which is what
+ * htp_b200_mul_mat_static_scratch requires), the weights per range (*range_k, whole pipeline stages; the
+ * last range may be shorter) and the depth of the shared-memory ring (*stages).  Pure host arithmetic:
+ * needs no GPU, launches nothing.  Any of the three pointers may be NULL.  -1 for arguments the decode
+ * kernel does not take.  No counterpart in the reference (its chunk sizes are found by find_chunk_size,
+ * src/dsp/ops/mat_mul.c:72-86, for a scratchpad of a different shape).
+ */
+int htp_b200_decode_plan(int m, int k, int weight_type, int act_type, int *k_ranges, int *range_k, int *stages);
+
+/*
  * Integer probe of the block unpack: for each of n_blocks consecutive blocks writes
  * s[b] = sum_i v_i and t[b] = sum_i (i + 1) * v_i (int32), v_i the block's 32 integer values in
  * element order.  No counterpart in the reference (it has no integer path); exists so the
