@@ -441,7 +441,7 @@ def measure_rms_norm(torch, lib, peaks, stream_ptr, stream, steps):
             "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4)}
 
 
-def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
+def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool, layers: int = 32, ms_list=None):
     """Config 3: 32 layers x 7 Q4_0 matmuls issued in order through the message channel (one message
     of 224 requests per pass); 3.9 GB of weights per pass, so every pass streams from HBM."""
     cfg = wl.CONFIGS["cfg3"]
@@ -451,7 +451,6 @@ def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
         return {"cfg3": {"error": "open_dsp_session failed"}}
     lib.init_htp_backend()
     try:
-        layers = 32
         # one distinct weight set per layer (generated once per matrix kind, then perturbed per layer
         # by copying: the bytes differ in address, which is what matters for HBM traffic)
         base = [wl.make_weight_torch(cfg, dev, i, 0) for i in range(len(cfg.ops))]
@@ -460,7 +459,7 @@ def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
         total_w = sum(w.numel() for lw in weights for w in lw)
         chan = pkg.MessageChannel(16384)
         try:
-            for m in cfg.ms:
+            for m in (ms_list or cfg.ms):
                 # independent N(0,1) activations per matrix kind, one output buffer per (layer, matrix):
                 # no request reads or overwrites what another one writes
                 xs = [torch.randn((m, op.k), device=dev, dtype=torch.float32) for op in cfg.ops]
@@ -500,6 +499,7 @@ def measure_decoder_stack(torch, pkg, lib, wl, peaks, quick: bool):
                     "frac_of_hbm_peak": round(gb / peaks["hbm_gbs"], 4),
                     "ms_per_pass_on_device": round(ms_dev, 4),
                     "frac_of_hbm_peak_on_device": round(algo / (ms_dev * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                    "layers": layers,
                     "kernel_launches_per_pass": (lib.htp_b200_launch_count() - launches0) // (n_pass + 2),
                     "timed": "ms_per_pass: host wall clock around message-channel round trips (224 requests per "
                              "message, composed once); on_device: CUDA events on the session stream around a message"}
@@ -946,8 +946,18 @@ def main():
                     help="N > 1: assemble the logits with an NCCL all-gather instead of the kernel's own peer stores")
     ap.add_argument("--case", default=None, help="wtype,act,m,k,n: time one shape only (profiling aid)")
     ap.add_argument("--graph", action="store_true", help="--case: also time the launches replayed from a CUDA graph")
+    ap.add_argument("--stack", default=None, help="m[,layers]: time config 3's decoder stack only, through the message "
+                                                  "channel, with that many tokens and layers (profiling aid)")
     args = ap.parse_args()
-    if args.case:
+    if args.stack:
+        import torch
+        pkg = entry.load_package()
+        from htp_ops_lib_b200 import workloads as wl
+        parts = [int(v) for v in args.stack.split(",")]
+        torch.cuda.set_device(0)
+        print(json.dumps(measure_decoder_stack(torch, pkg, pkg.load(), wl, read_peaks(), True,
+                                               layers=parts[1] if len(parts) > 1 else 32, ms_list=[parts[0]])), flush=True)
+    elif args.case:
         run_case(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -219,6 +219,7 @@ struct OutBand {
   float *const *more;  // n_dst - 1 further destinations
   unsigned *const *flags = nullptr;  // optional completion flags, one per destination
   unsigned     epoch     = 0;
+  const unsigned *wait_flags = nullptr;  // optional: this GPU's flag array, waited for inside the launch
 };
 
 int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int m, int k, int n, int wt, bool a16,
@@ -274,6 +275,8 @@ int run_gemv(DeviceCtx *ctx, float *dst, const void *act, const uint8_t *w, int 
           for (int d = 0; d < band->n_dst; ++d) {
             a.sig_flags[d] = band->flags[d];
           }
+          a.wait_flags = band->wait_flags;
+          a.n_wait     = band->n_dst;
         }
       }
       a.x           = static_cast<const uint8_t *>(act) + (size_t) m0 * k * asz;
@@ -666,7 +669,8 @@ int htp_b200_block_sums(const void *weight, int32_t *s, int32_t *t, int64_t n_bl
 
 static int mul_mat_multi_dst_impl(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                   const void *weight, int m, int k, int n, int weight_type, int act_type,
-                                  unsigned *const *flags, unsigned epoch, void *stream);
+                                  unsigned *const *flags, unsigned epoch, void *stream,
+                                  const unsigned *wait_flags = nullptr);
 
 int htp_b200_mul_mat_multi_dst(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                const void *weight, int m, int k, int n, int weight_type, int act_type, void *stream) {
@@ -692,12 +696,17 @@ int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_
 int htp_b200_mul_mat_gather_step(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                  const void *weight, int m, int k, int n, int weight_type, int act_type,
                                  uint32_t *const *flags, const uint32_t *local_flags, uint32_t epoch, void *stream) {
-  if (!local_flags) {
+  if (!flags || !local_flags || m > 8 || (reinterpret_cast<uintptr_t>(local_flags) & 3u)) {
     return -1;
   }
-  const int rc = htp_b200_mul_mat_multi_dst_signal(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n,
-                                                   weight_type, act_type, flags, epoch, stream);
-  return rc != 0 ? rc : htp_b200_wait_flags(local_flags, n_dst, epoch, stream);
+  for (int d = 0; d < n_dst && d < kGemmMaxDst; ++d) {
+    if (!flags[d] || (reinterpret_cast<uintptr_t>(flags[d]) & 3u)) {
+      return -1;
+    }
+  }
+  // one launch: the mat-vec signals, and its last CTA waits for the peers' flags
+  return mul_mat_multi_dst_impl(dsts, n_dst, dst_ld, dst_col0, activation, weight, m, k, n, weight_type, act_type, flags,
+                                epoch, stream, local_flags);
 }
 
 int htp_b200_wait_flags(const uint32_t *flags, int n, uint32_t epoch, void *stream) {
@@ -720,7 +729,7 @@ int htp_b200_wait_flags(const uint32_t *flags, int n, uint32_t epoch, void *stre
 
 static int mul_mat_multi_dst_impl(void *const *dsts, int n_dst, int64_t dst_ld, int64_t dst_col0, const void *activation,
                                   const void *weight, int m, int k, int n, int weight_type, int act_type,
-                                  unsigned *const *flags, unsigned epoch, void *stream) {
+                                  unsigned *const *flags, unsigned epoch, void *stream, const unsigned *wait_flags) {
   if (!dsts || n_dst < 1 || n_dst > kGemmMaxDst || !activation || !weight || m <= 0 || n <= 0 || k <= 0) {
     return -1;
   }
@@ -759,8 +768,9 @@ static int mul_mat_multi_dst_impl(void *const *dsts, int n_dst, int64_t dst_ld, 
       more[d - 1] = static_cast<float *>(dsts[d]);
     }
     OutBand band = { n_dst, dst_ld, dst_col0, more };
-    band.flags   = flags;
-    band.epoch   = epoch;
+    band.flags      = flags;
+    band.epoch      = epoch;
+    band.wait_flags = wait_flags;
     return run_gemv(ctx, static_cast<float *>(dsts[0]), activation, static_cast<const uint8_t *>(weight), m, k, n, wt,
                     a16, st, g_opt_pdl != 0, &band);
   }

@@ -950,13 +950,37 @@ __global__ void __launch_bounds__(kThreads, 1)
       // done.  The counter's acquire-release and the flags' release stores carry the ordering: no
       // further fence.
       named_bar_sync(2, kReduceThreads);
-      if (warp == kReduceWarp0 && lane == 0) {
-        unsigned old;
-        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.done_counter) : "memory");
-        if (old == gridDim.x - 1) {
-          *p.done_counter = 0;  // ready for the next launch
-          for (int d = 0; d < p.n_dst; ++d) {
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[d]), "r"(p.epoch) : "memory");
+      if (warp == kReduceWarp0) {
+        unsigned last = 0;
+        if (lane == 0) {
+          unsigned old;
+          asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.done_counter) : "memory");
+          if (old == gridDim.x - 1) {
+            *p.done_counter = 0;  // ready for the next launch
+            for (int d = 0; d < p.n_dst; ++d) {
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[d]), "r"(p.epoch) : "memory");
+            }
+            last = 1;
+          }
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        // Optionally the launch also WAITS (bounded, about a second) until every rank's flag of this epoch
+        // is in this GPU's flag array: the kernel's end is then the end of the step on this GPU - every
+        // rank's band has landed here - without a separate wait kernel and its kernel boundary.  The
+        // last CTA waits; lane r watches rank r.  (Kernels of DIFFERENT GPUs wait for each other here;
+        // each rank's launch depends only on its own earlier steps, so no cycle can form.)
+        if (last && p.wait_flags && lane < p.n_wait) {
+          bool seen = false;
+          for (uint32_t i = 0; i < (1u << 23) && !seen; ++i) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p.wait_flags + lane) : "memory");
+            seen = (int) (v - p.epoch) >= 0;
+            if (!seen) {
+              __nanosleep(100);
+            }
+          }
+          if (!seen) {
+            atomicCAS(p.err, 0, kGemvErrFlagWait);
           }
         }
       }

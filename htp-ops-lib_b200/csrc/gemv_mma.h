@@ -19,6 +19,7 @@ constexpr int kGemvMaxGrid     = 1024;    // scratch is sized for this many CTAs
 
 constexpr int kGemvErrProducerWait = 101;
 constexpr int kGemvErrConsumerWait = 102;
+constexpr int kGemvErrFlagWait     = 103;  // a peer's completion flag never arrived
 
 // 32-weight blocks per pipeline stage and row: 64 for Q4_0 / IQ4_NL (1152 B), 32 for Q8_0 (1088 B), so a
 // stage of 32 rows is ~36 KB in either format.
@@ -74,9 +75,12 @@ struct GemvArgs {
   unsigned      *done_counter;
   unsigned      *sig_flags[8];
   unsigned       epoch;
+  // Optional: after signalling, the last CTA waits (bounded) until wait_flags[r] has reached `epoch`
+  // for r = 0 .. n_wait - 1 - this GPU's flag array, written by the peers' launches of the same step.
+  const unsigned *wait_flags;
+  int             n_wait;
 };
 
-constexpr int kGemvErrFlagWait = 103;  // htp_b200_wait_flags: a peer's completion flag never arrived
 
 // Waits (bounded) on `stream` until flags[r] has reached `epoch` for r = 0 .. n - 1; records
 // kGemvErrFlagWait in *err when that does not happen.

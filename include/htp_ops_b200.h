@@ -151,11 +151,13 @@ int htp_b200_mul_mat_multi_dst_signal(void *const *dsts, int n_dst, int64_t dst_
                                       const void *activation, const void *weight, int m, int k, int n, int weight_type,
                                       int act_type, uint32_t *const *flags, uint32_t epoch, void *stream);
 
-/* One decode step of a row-sharded matrix in ONE call: htp_b200_mul_mat_multi_dst_signal, then
- * htp_b200_wait_flags(local_flags, n_dst, epoch) on the same stream.  local_flags is THIS GPU's flag
+/* One decode step of a row-sharded matrix in ONE call and ONE launch: htp_b200_mul_mat_multi_dst_signal
+ * whose last CTA, after raising this rank's flags, waits (bounded to about a second, then error 103)
+ * until local_flags[r] has reached `epoch` for r = 0 .. n_dst - 1.  local_flags is THIS GPU's flag
  * array (word r = rank r's flag), i.e. the array the peers' flags[] entries point into.  When the
- * stream reaches the end of the step, every rank's band of this epoch is in this GPU's copy of the
- * output.  The caller's obligation: a rank may start step e + 1 - and overwrite its band in the
+ * stream reaches the end of the launch, every rank's band of this epoch is in this GPU's copy of the
+ * output.  Every rank must issue the same sequence of steps (a rank's launch depends only on its own
+ * earlier steps, so the ranks cannot wait for each other in a circle).  The caller's obligation: a rank may start step e + 1 - and overwrite its band in the
  * PEERS' copies - as soon as its own wait of step e has passed, so a consumer that still reads the
  * output of step e when the next step is issued needs two output buffers used in turn (or its own
  * cross-rank barrier).  No counterpart in the reference. */
