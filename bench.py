@@ -390,13 +390,17 @@ def tile_order_device_weights(torch, wl, fmt: int, k: int, n: int, dev):
 def measure_tile_order_decode(torch, pkg, lib, wl, peaks, stream_ptr, stream, steps):
     """One-token mat-vecs over weights in the reference's tile order, read in place: the fp16 tiles of the
     W16A32 op (32768 x 4096, 268 MB) and the permuted Q4_0 / Q8_0 super-blocks (65536 x 4096, 151 / 285 MB),
-    two rotating copies each.  Algorithmic bytes = weight buffer + activation + output."""
+    two rotating copies each.  Algorithmic bytes = weight buffer + activation + output.  The 512-token
+    lines are config 2's shape on the same formats (fp32 activations, as the reference's ops take them):
+    conversion launch + tensor-core GEMM, flops = 2 m n k."""
     dev = torch.device("cuda", torch.cuda.current_device())
     out = {}
     for name, fmt, m, k, n in (("w16a32_tiled_gemv_32768x4096_m1", wl.WT_F16_TILED, 1, 4096, 32768),
                                ("w16a32_tiled_prefill_f32act_14336x4096_m512", wl.WT_F16_TILED, 512, 4096, 14336),
                                ("permuted_q4_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q4_0, 1, 4096, 65536),
-                               ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 1, 4096, 65536)):
+                               ("permuted_q8_0_gemv_65536x4096_m1", wl.WT_PERMUTED | wl.TYPE_Q8_0, 1, 4096, 65536),
+                               ("permuted_q4_0_prefill_f32act_14336x4096_m512", wl.WT_PERMUTED | wl.TYPE_Q4_0, 512, 4096, 14336),
+                               ("permuted_q8_0_prefill_f32act_14336x4096_m512", wl.WT_PERMUTED | wl.TYPE_Q8_0, 512, 4096, 14336)):
         nbytes = wl.weight_bytes(fmt, k, n)
         assert nbytes == lib.htp_b200_weight_bytes(fmt, k, n)
         copies = 2 if m == 1 else 1

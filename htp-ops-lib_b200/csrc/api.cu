@@ -378,6 +378,35 @@ int mul_mat_checked(void *dst, const void *activation, const void *weight, int m
     count_launch();
     return 0;
   }
+  if (tfmt > kTileF16 && k % 128 == 0 && m >= g_opt_gemm_min_m && (a16 || (!g_opt_a32_exact && m >= kGemmMinMF32))) {
+    // the reference's permuted super-blocks, many tokens: the same GEMM, its unpack reading the
+    // super-blocks as they lie (value * scale rounded to fp16 once, as the reference does,
+    // src/dsp/ops/mat_mul.c:396-405, 490-506)
+    StreamScratch *sc = stream_scratch(ctx, st);
+    if (!sc) {
+      return -2;
+    }
+    GemmArgs a = {};
+    a.y = static_cast<float *>(dst), a.x = activation, a.w = static_cast<const uint8_t *>(weight);
+    a.M = m, a.N = n, a.K = k, a.err = sc->err;
+    if (!a16) {
+      float   *scales = nullptr;
+      uint8_t *x16    = act16_scratch(sc, st, m, k, &scales);
+      if (!x16 || act_f32_to_f16_launch(x16, scales, static_cast<const float *>(activation), m, k, st) != cudaSuccess) {
+        cudaGetLastError();
+        return -2;
+      }
+      count_launch();
+      a.x = x16, a.tok_scale = scales;
+    }
+    const int gwt = tfmt == kTileQ4 ? kGemmWtPermQ4 : (tfmt == kTileQ8 ? kGemmWtPermQ8 : kGemmWtPermIQ4);
+    if (gemm_tcgen05_launch(a, gwt, ctx->sm_count, st) != cudaSuccess) {
+      cudaGetLastError();
+      return -2;
+    }
+    count_launch();
+    return 0;
+  }
   if (tfmt >= 0) {
     // weights in the reference's tile order: streamed in place by the tile-order kernel
     if (tiled_mul_mat_launch(static_cast<float *>(dst), activation, static_cast<const uint8_t *>(weight), m, k, n,

@@ -38,6 +38,11 @@
 //               of its 32 rows itself (coalesced cp.async, one stage ahead); thread = one weight
 //               row: 9 / 17 conflict-free 16-byte loads to registers, then per K step 64 weights to
 //               fp16 (value * scale, rounded once) stored as 32 TMEM columns of its lane
+// Weight formats: the row-major 32-weight blocks (Q4_0, Q8_0, IQ4_NL) and, read in place, the
+// reference's 32 x 32 tile order - fp16 tiles (its W16A32 op) and the permuted super-blocks its
+// quantised ops consume (include/dsp/quants.h:16-31, src/dsp/ops/mat_mul.c:308-510): there a warp's
+// 32 rows are one column tile, a raw stage is 128 of K = four contiguous tiles, and the unpack is a
+// copy (fp16) or one 16-byte chunk per super-block (eight k-rows of the thread's column).
 // Optionally (off by default) tiles that do not divide among the SMs are cut into equal K ranges
 // and finished through a global scratch tile.
 // All waits are bounded; a wait that runs out records an error code, raises the CTA's abort flag
@@ -60,6 +65,9 @@ namespace {
 constexpr int kBW        = 128;  // weight rows per tile (UMMA M, the TMEM lanes)
 constexpr int kBK        = 64;   // K per pipeline step: one 128-byte swizzled row of fp16
 constexpr int kF16T      = 3;    // weight "format" of this file only: fp16 values in the reference's 32 x 32 tile order
+constexpr int kPQ4       = 4;    // the reference's permuted super-blocks in the same tile order: Q4_0 (144 bytes),
+constexpr int kPQ8       = 5;    // Q8_0 (272 bytes),
+constexpr int kPIQ4      = 6;    // IQ4_NL values in Q4_0's layout
 constexpr int kNAT       = 8;    // A tiles (32 TMEM columns each) in the tensor-memory ring
 constexpr int kThreads   = 512;
 constexpr int kEpiWarp0  = 4;
@@ -75,20 +83,37 @@ template <>
 struct BlockTraits<3> {  // kF16T: 32 fp16 weights of a row
   static constexpr int kBytes = 64;
 };
+// permuted super-blocks: the bytes per row and 32 of K come to the same 18 / 34 as the row-major blocks
+template <>
+struct BlockTraits<4> {
+  static constexpr int kBytes = 18;
+};
+template <>
+struct BlockTraits<5> {
+  static constexpr int kBytes = 34;
+};
+template <>
+struct BlockTraits<6> {
+  static constexpr int kBytes = 18;
+};
 namespace {
 
 template <int WT, int BT, bool TWO>
 struct GCfg {
   static constexpr bool TILED    = WT == kF16T;
+  static constexpr bool PERM     = WT >= kPQ4;  // permuted super-blocks, four per 32 x 32 tile
   // A raw stage = the bytes of RAWK weights per row, fetched and unpacked as one unit: 256 weights of
-  // the block formats (a 16-byte aligned period of 8 blocks), 128 of the fp16 tile order (four 2 KB
-  // tiles per 32 rows).
-  static constexpr int RAWK      = TILED ? 128 : 256;
+  // the block formats (a 16-byte aligned period of 8 blocks), 128 of the tile-order formats (four
+  // tiles of 2048 / 576 / 1088 bytes per 32 rows).
+  static constexpr int RAWK      = (TILED || PERM) ? 128 : 256;
+  static constexpr int TILE_B    = TILED ? 2048 : (WT == kPQ8 ? 1088 : 576);  // bytes of a tile (tile-order formats)
+  static constexpr int PIECES    = (RAWK / 32) * TILE_B / 16;  // 16-byte pieces of a warp's raw stage (tile-order formats)
+  static_assert(TILE_B % 16 == 0 && PIECES > 0, "tiles are copied in 16-byte pieces");
   static constexpr int Q         = RAWK / kBK;  // K steps per raw stage
   static constexpr int NG        = kNAT / Q;    // raw stages the ring of K steps holds
   static constexpr int BB        = BlockTraits<WT>::kBytes;
   static constexpr int RB        = (RAWK / 32) * BB;  // raw bytes per row and raw stage: 144 / 272 / 256
-  static constexpr int RW        = RB / 16;           // 16-byte words per row: 9 / 17 / 16
+  static constexpr int RW        = RB / 16;           // 16-byte words per row: 9 / 17 / 16 (row-major blocks, fp16 tiles)
   static constexpr int XROWS     = TWO ? BT / 2 : BT;  // activation rows this CTA loads per K step
   static constexpr int X_BYTES   = XROWS * 128;
   static constexpr int RAW_BYTES = kBW * RB;
@@ -316,16 +341,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
   return false;
 }
 
-#ifdef HTP_GEMM_PROF
-__device__ long long g_gemm_prof[32];
-#define PROF_T0() long long _t0 = clock64()
-#define PROF_ADD(i) do { long long _t1 = clock64(); if (blockIdx.x == 0) prof[i] += _t1 - _t0; _t0 = _t1; } while (0)
-#define DBG_SKIP(bit) (p.dbg & (bit))
-#else
-#define PROF_T0()
-#define PROF_ADD(i)
-#define DBG_SKIP(bit) false
-#endif
 
 struct Ring {
   int slot = 0, phase = 0, n;
@@ -551,18 +566,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       unsigned gs = 0;
       int      it = 0;
       bool     ok = true;
-#ifdef HTP_GEMM_PROF
-      long long prof[4] = {0, 0, 0, 0};
-#endif
-      PROF_T0();
       for (int li = 0; li < n_stages && ok; ++it) {
         int t, rs0, rs1;
         segment(li, t, rs0, rs1);
         li += rs1 - rs0;
         // the accumulator must have been read out by the epilogue(s) of the previous segment
-        ok = DBG_SKIP(8) || wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
+        ok = wait_or_abort(&bar->acc_empty, (it & 1) ^ 1, abort_flag, p.err, kGemmErrMma);
         ok = __all_sync(0xffffffffu, ok);
-        PROF_ADD(0);
         if (!ok) {
           break;
         }
@@ -574,7 +584,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int slot = sg * C::Q + q;
             ok = wait_or_abort(&bar->full[slot], gph, abort_flag, p.err, kGemmErrMma);
             ok = __all_sync(0xffffffffu, ok);
-            PROF_ADD(2);
             if (!ok) {
               break;
             }
@@ -590,7 +599,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               umma_commit<TWO>(&bar->empty[slot]);
             }
             __syncwarp();
-            PROF_ADD(3);
           }
         }
         if (ok && elect_one()) {
@@ -598,11 +606,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
       }
-#ifdef HTP_GEMM_PROF
-      if (blockIdx.x == 0 && lane == 0) {
-        for (int i = 0; i < 4; ++i) g_gemm_prof[i] = prof[i];
-      }
-#endif
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + 4) {
     // ---------------- epilogue: TMEM -> registers -> shared memory -> y[token][weight row].
@@ -618,10 +621,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       tma_prefetch_descriptor(&ymaps.m[0]);
     }
-#ifdef HTP_GEMM_PROF
-    long long prof[4] = {0, 0, 0, 0};
-#endif
-    PROF_T0();
     for (int li = 0; li < n_stages && ok; ++it) {
       int t, rs0, rs1;
       segment(li, t, rs0, rs1);
@@ -633,7 +632,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int n0 = (t / t_tiles) * ROWS_TILE + row_off, m0 = (t % t_tiles) * BT;
       ok = wait_or_abort(&bar->acc_full, it & 1, abort_flag, p.err, kGemmErrEpilogue);
       ok = __all_sync(0xffffffffu, ok);  // tensor-memory loads are warp-wide
-      PROF_ADD(0);
       if (!ok) {
         break;
       }
@@ -711,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && !DBG_SKIP(4)) {
+        if (lane == 0) {
           if (is_tail) {
             tma_store_2d(&pmap, row_off + q4 * 32, worker * BT + c0, buf);
           } else if (col_ok) {
@@ -745,9 +743,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
           release_acc();
         }
-        PROF_ADD(1);
         store16(c0, va, adda);
-        PROF_ADD(2);
         if (c0 + 16 < m_end) {
           tmem_ld_wait(vb);
           if (c0 + 32 < m_end) {
@@ -756,9 +752,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           } else {
             release_acc();
           }
-          PROF_ADD(1);
           store16(c0 + 16, vb, addb);
-          PROF_ADD(2);
         }
       }
       if (is_tail) {
@@ -777,7 +771,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           *flag = 0;  // ready for the next launch on this stream
         }
       }
-      PROF_ADD(3);
     }
     if (lane == 0) {
       bulk_wait_all();  // the staging buffers stay valid until the copy engine is done with them
@@ -785,11 +778,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         __threadfence_system();  // stores into other GPUs' memory are ordered before this kernel's end
       }
     }
-#ifdef HTP_GEMM_PROF
-    if (blockIdx.x == 0 && threadIdx.x == kEpiWarp0 * 32) {
-      g_gemm_prof[4] = prof[0], g_gemm_prof[5] = prof[1], g_gemm_prof[6] = prof[2], g_gemm_prof[7] = prof[3];
-    }
-#endif
   } else if (warp >= kDeqWarp0) {
     // ---------------- dequantisation: group g, thread = weight row r of this CTA's 128 rows.
     // Each WARP also fetches the raw stages of its own 32 rows (32 x 144 / 272 bytes) with 16-byte
@@ -818,14 +806,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         return;  // N is a multiple of 32: the warp's rows are all inside or all outside the matrix;
                  // rows outside are computed on whatever the slice holds and never stored
       }
-      if constexpr (C::TILED) {
+      if constexpr (C::TILED || C::PERM) {
         // the warp's 32 rows are ONE column tile of the reference's tile order, and the RAWK / 32
-        // k-tiles of a raw stage are consecutive 2 KB tiles: one contiguous run, copied as it lies
-        const uint8_t *src = p.w + ((row0 >> 5) * (long long) (p.K / 32) + (long long) rs * (C::RAWK / 32)) * 2048 + 16 * lane;
+        // k-tiles of a raw stage are consecutive tiles: one contiguous run, copied as it lies
+        const uint8_t *src = p.w + ((row0 >> 5) * (long long) (p.K / 32) + (long long) rs * (C::RAWK / 32)) * C::TILE_B + 16 * lane;
         uint32_t       dst = warp_smem + 16 * lane;
 #pragma unroll
-        for (int i = 0; i < C::RW; ++i) {
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        for (int i = 0; i < (C::PIECES + 31) / 32; ++i) {
+          if (C::PIECES % 32 == 0 || i * 32 + lane < C::PIECES) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+          }
           src += 512, dst += 512;
         }
       } else {
@@ -847,10 +837,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       fetch(g);
     }
     bool ok = true;
-#ifdef HTP_GEMM_PROF
-    long long prof[5] = {0, 0, 0, 0, 0};
-#endif
-    PROF_T0();
     for (int li = g; li < n_stages; li += 2) {
       const unsigned gs  = (unsigned) li;  // running stage index
       const int      sg = (int) (gs % C::NG), gph = (int) (gs / C::NG) & 1;  // ring position of the raw stage
@@ -860,11 +846,47 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!__all_sync(0xffffffffu, ok)) {
         break;
       }
-      PROF_ADD(0);
       // the thread's row of the raw stage, out of the slice into registers
-      constexpr int RAW_WORDS = C::TILED ? C::RAWK / 2 : C::RW * 4;
+      constexpr int RAW_WORDS = C::PERM ? 64 : (C::TILED ? C::RAWK / 2 : C::RW * 4);
       uint32_t      raw[RAW_WORDS + 1];
-      if constexpr (C::TILED) {
+      if constexpr (C::PERM) {
+        // Super-block sb (0..15: four per tile, four tiles) holds k-rows 8 (sb % 4) .. + 7 of its tile
+        // for all 32 columns.  Its scale for column n and k-row pair v is halfword 2 v + n / 16 of the
+        // 16-byte header: kept as raw[4 sb + 2] = pairs 0, 1 and raw[4 sb + 3] = pairs 2, 3.  Quants:
+        //   Q4_0 / IQ4_NL: ONE word per column, nibbles (low to high) = k-rows 0, 4, 2, 6, 1, 5, 3, 7
+        //                  (raw[4 sb]);
+        //   Q8_0: k-row pair v = bytes 64 v + 2 n, + 1; raw[4 sb] = pairs 0, 1, raw[4 sb + 1] = pairs 2, 3,
+        //         biased to 0..255.
+        constexpr int  SBB  = C::TILE_B / 4;
+        const uint32_t hsel = (lane & 16) ? 0x7632u : 0x5410u;  // the column's half of two scale words
+        const uint32_t qsel = (lane & 1) ? 0x7632u : 0x5410u;   // the column's halfword of two quant words
+#pragma unroll
+        for (int sb = 0; sb < 16; ++sb) {
+          const uint32_t at = warp_smem + sb * SBB;
+          uint32_t       s0, s1, s2, s3;
+          asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(s0), "=r"(s1), "=r"(s2), "=r"(s3)
+                       : "r"(at)
+                       : "memory");
+          raw[4 * sb + 2] = __byte_perm(s0, s1, hsel);
+          raw[4 * sb + 3] = __byte_perm(s2, s3, hsel);
+          if constexpr (WT == kPQ8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              asm volatile("ld.volatile.shared.u32 %0, [%1];"
+                           : "=r"(w[v])
+                           : "r"(at + 16 + 64 * v + (lane >> 1) * 4)
+                           : "memory");
+            }
+            raw[4 * sb]     = __byte_perm(w[0], w[1], qsel) ^ 0x80808080u;
+            raw[4 * sb + 1] = __byte_perm(w[2], w[3], qsel) ^ 0x80808080u;
+          } else {
+            asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(raw[4 * sb]) : "r"(at + 16 + lane * 4) : "memory");
+            raw[4 * sb + 1] = 0;
+          }
+        }
+      } else if constexpr (C::TILED) {
         // tile order: the k-pair (2 kp, 2 kp + 1) of column n of a tile is the 32-bit word kp * 32 + n;
         // a lane's words are the fp16 pairs of its row in K order - what the tensor memory wants
 #pragma unroll
@@ -893,7 +915,45 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the fp16 values of a K step are computed before waiting for their TMEM slot
       uint4 out[8];
       auto  k_step = [&](int q) {
-        if constexpr (C::TILED) {
+        if constexpr (C::PERM) {
+          // K step q = tiles 2 q, 2 q + 1 = super-blocks 8 q .. 8 q + 7; a super-block's eight k-rows are
+          // one 16-byte chunk: pairs (0,1), (2,3), (4,5), (6,7), value * scale rounded once
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int      sb = 8 * q + c;
+            const uint32_t pa = raw[4 * sb + 2], pb = raw[4 * sb + 3];
+            const __half2  d0 = u32_as_h2(__byte_perm(pa, pa, 0x1010)), d1 = u32_as_h2(__byte_perm(pa, pa, 0x3232));
+            const __half2  d2 = u32_as_h2(__byte_perm(pb, pb, 0x1010)), d3 = u32_as_h2(__byte_perm(pb, pb, 0x3232));
+            uint32_t       v0, v1, v2, v3;
+            if constexpr (WT == kPQ8) {
+              const __half2  k1152 = u32_as_h2(0x64806480u);
+              const uint32_t qa = raw[4 * sb], qb = raw[4 * sb + 1];
+              v0 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(qa, 0x64646464u, 0x4140)), k1152), d0));
+              v1 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(qa, 0x64646464u, 0x4342)), k1152), d1));
+              v2 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(qb, 0x64646464u, 0x4140)), k1152), d2));
+              v3 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(qb, 0x64646464u, 0x4342)), k1152), d3));
+            } else if constexpr (WT == kPIQ4) {
+              // table values of nibbles 0..3 (k-rows 0, 4, 2, 6) and 4..7 (k-rows 1, 5, 3, 7), biased
+              const __half2  k1152 = u32_as_h2(0x64806480u);
+              const uint32_t w  = raw[4 * sb];
+              const uint32_t e  = iq4nl_lookup4(w) ^ 0x80808080u, o = iq4nl_lookup4(w >> 16) ^ 0x80808080u;
+              const uint32_t t0 = __byte_perm(e, o, 0x5140);  // k-rows 0, 1, 4, 5
+              const uint32_t t1 = __byte_perm(e, o, 0x7362);  // k-rows 2, 3, 6, 7
+              v0 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(t0, 0x64646464u, 0x4140)), k1152), d0));
+              v1 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(t1, 0x64646464u, 0x4140)), k1152), d1));
+              v2 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(t0, 0x64646464u, 0x4342)), k1152), d2));
+              v3 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(t1, 0x64646464u, 0x4342)), k1152), d3));
+            } else {
+              const __half2  k1032 = u32_as_h2(0x64086408u);  // 1024 + 8
+              const uint32_t w = raw[4 * sb];
+              v0 = h2_as_u32(__hmul2(__hsub2(u32_as_h2((w & 0x000F000Fu) | 0x64006400u), k1032), d0));
+              v1 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(((w >> 8) & 0x000F000Fu) | 0x64006400u), k1032), d1));
+              v2 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(((w >> 4) & 0x000F000Fu) | 0x64006400u), k1032), d2));
+              v3 = h2_as_u32(__hmul2(__hsub2(u32_as_h2(((w >> 12) & 0x000F000Fu) | 0x64006400u), k1032), d3));
+            }
+            out[c] = make_uint4(v0, v1, v2, v3);
+          }
+        } else if constexpr (C::TILED) {
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
             out[c] = make_uint4(raw[32 * q + 4 * c], raw[32 * q + 4 * c + 1], raw[32 * q + 4 * c + 2],
@@ -912,19 +972,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (li + 2 < n_stages) {
         fetch(li + 2);
       }
-      PROF_ADD(1);
 #pragma unroll
       for (int q = 0; q < C::Q; ++q) {
         const int slot = sg * C::Q + q;
         ok = ok && wait_or_abort(&bar->empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
-        PROF_ADD(2);
         ok = __all_sync(0xffffffffu, ok);  // a warp stores to tensor memory as a whole or not at all
         if (ok) {
           tc_fence_after();
           tmem_st32(tlane + slot * 32, out);  // 64 fp16 = 32 columns of this thread's lane
           tmem_st_wait();
           tc_fence_before();
-          PROF_ADD(3);
           __syncwarp();  // every lane's store has completed (wait::st above)
           if (lane == 0) {
             if (TWO && rank != 0) {
@@ -937,15 +994,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (q + 1 < C::Q) {
           k_step(q + 1);
         }
-        PROF_ADD(4);
       }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-#ifdef HTP_GEMM_PROF
-    if (blockIdx.x == 0 && lane == 0 && (warp == kDeqWarp0 || warp == kDeqWarp0 + 4)) {
-      for (int i = 0; i < 5; ++i) g_gemm_prof[8 + 8 * g + i] = prof[i];
-    }
-#endif
   }
 
   // ---------------- teardown
@@ -1074,11 +1125,6 @@ cudaError_t launch(const GemmArgs &a, int sm_count, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef HTP_GEMM_PROF
-extern "C" int htp_b200_gemm_prof(long long *out) {
-  return (int) cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 32);
-}
-#endif
 
 size_t gemm_scratch_bytes(int sm_count) {
   return gemm_part_bytes(sm_count) + (size_t) sm_count * 8 * sizeof(int);
@@ -1086,12 +1132,6 @@ size_t gemm_scratch_bytes(int sm_count) {
 
 cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, cudaStream_t stream) {
   GemmArgs args = args_in;
-#ifdef HTP_GEMM_PROF
-  {
-    const char *d = getenv("HTP_GEMM_DBG");
-    args.dbg      = d ? atoi(d) : 0;
-  }
-#endif
   // up to 128 tokens: single-CTA tiles of 128 tokens; more: CTA pairs on 256 x 256 tiles
   const bool one = g_opt_gemm_tile_n ? g_opt_gemm_tile_n == 128 : args.M <= 128;
   if (wt == kQ4) {
@@ -1102,6 +1142,15 @@ cudaError_t gemm_tcgen05_launch(const GemmArgs &args_in, int wt, int sm_count, c
   }
   if (wt == kGemmWtF16Tiled) {
     return one ? launch<kF16T, 128, false>(args, sm_count, stream) : launch<kF16T, 256, true>(args, sm_count, stream);
+  }
+  if (wt == kGemmWtPermQ4) {
+    return one ? launch<kPQ4, 128, false>(args, sm_count, stream) : launch<kPQ4, 256, true>(args, sm_count, stream);
+  }
+  if (wt == kGemmWtPermQ8) {
+    return one ? launch<kPQ8, 128, false>(args, sm_count, stream) : launch<kPQ8, 256, true>(args, sm_count, stream);
+  }
+  if (wt == kGemmWtPermIQ4) {
+    return one ? launch<kPIQ4, 128, false>(args, sm_count, stream) : launch<kPIQ4, 256, true>(args, sm_count, stream);
   }
   return one ? launch<kQ8, 128, false>(args, sm_count, stream) : launch<kQ8, 256, true>(args, sm_count, stream);
 }

@@ -18,12 +18,18 @@ constexpr int kGemmMaxDst = 8;
 // reference's 32 x 32 tile order (tile (n/32, k/32) at tile number (n/32) * (K/32) + k/32, element
 // (k, n) of a tile at halfword (k & ~1) * 32 + 2 n + (k & 1)); K a multiple of 128.
 constexpr int kGemmWtF16Tiled = 3;
+// The reference's permuted super-blocks (my_block_q4_0 144 bytes / my_block_q8_0 272 bytes, four per
+// tile of the same tile order; include/dsp/quants.h:16-31, expanded slot by slot at
+// src/dsp/ops/mat_mul.c:308-510): Q4_0, Q8_0, IQ4_NL values.  K a multiple of 128.
+constexpr int kGemmWtPermQ4  = 4;
+constexpr int kGemmWtPermQ8  = 5;
+constexpr int kGemmWtPermIQ4 = 6;
 
 struct GemmArgs {
   float         *y;  // [M][N] fp32 (destination 0)
   const void    *x;  // [M][K] fp16
   const uint8_t *w;  // N rows of K/32 blocks, or fp16 tiles
-  int            M, N, K;  // K a multiple of 256 (fp16 tiles: 128), N a multiple of 32
+  int            M, N, K;  // K a multiple of 256 (tile-order formats: 128), N a multiple of 32
   int           *err;      // first error code, 0 when none
   // Scratch for tiles whose K range is split between two workers (gemm_scratch_bytes() bytes at
   // `part`, 256-byte aligned, zero before the first launch; the flags are zero again after every
@@ -41,9 +47,6 @@ struct GemmArgs {
   // Optional per-token output scale (fp32 activations arrive as scaled fp16 copies): output row m is
   // multiplied by tok_scale[m].  Readable up to the next multiple of 256 tokens.  nullptr: none.
   const float   *tok_scale;
-#ifdef HTP_GEMM_PROF
-  int            dbg;      // instrumented builds only: bit mask of waits to skip (timing experiments)
-#endif
 };
 
 // Bytes of split-tile scratch a device with `sm_count` SMs needs (partial tiles, then flags).

@@ -37,8 +37,10 @@ extern "C" {
  *                                my_block_q8_0 (272 B), four per tile (reference
  *                                include/dsp/quants.h:16-31, expanded at mat_mul.c:308-510) - the
  *                                buffers the reference's own ops 2, 3 and 4 consume; type = 2, 8 or 20.
- * These go through htp_b200_mul_mat only (any m, either activation type; a streaming kernel
- * sized for a few tokens); the batch, multi-destination and static-scratch calls reject them.
+ * These go through htp_b200_mul_mat only (any m, either activation type: a streaming kernel for a few
+ * tokens; with k a multiple of 128, the tensor-core GEMM from 9 fp16 / 17 fp32 tokens up, which unpacks
+ * tiles and super-blocks in place, weights rounded to fp16 once as the reference does); the batch,
+ * multi-destination and static-scratch calls reject them.
  */
 #define HTP_B200_WT_F16_TILED 1
 #define HTP_B200_WT_PERMUTED 0x100

@@ -43,10 +43,10 @@ def _raw(dev, x, wq, n, fmt):
 
 
 def _gemm_path(fmt, x) -> bool:
-    """fp16 tiles with many tokens run on the tensor-core GEMM (fp16 activations from 9 tokens, fp32 from
-    17, k % 128 == 0): activations rounded to fp16, gate 1e-3."""
+    """Every tile-order format with many tokens runs on the tensor-core GEMM (fp16 activations from 9
+    tokens, fp32 from 17, k % 128 == 0): weights and activations rounded to fp16, gate 1e-3."""
     m, k = x.shape
-    return fmt == 1 and k % 128 == 0 and m >= (9 if x.dtype == np.float16 else 17)
+    return k % 128 == 0 and m >= (9 if x.dtype == np.float16 else 17)
 
 
 @pytest.mark.parametrize("act_f16", [False, True])
@@ -76,6 +76,37 @@ def test_fp16_tiles_many_tokens_on_the_tensor_cores(dev, oracle, wl, act_f16, m,
     if not act_f16:
         fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
         assert dev.execute(dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W16A32, (fy, 0), (fx, 0), (fw, 0), m, k, n) == 0
+        assert (dev.get(fy, (m, n)) == y).all()
+        dev.free(fw, fx, fy)
+
+
+@pytest.mark.parametrize("act_f16", [False, True])
+@pytest.mark.parametrize("wtype", [Q4, Q8, IQ4])
+@pytest.mark.parametrize("m,k,n", [(17, 128, 32), (64, 1024, 1024), (200, 2176, 480), (512, 4096, 2240), (300, 1152, 19360 // 32 * 32)])
+def test_permuted_super_blocks_many_tokens_on_the_tensor_cores(dev, oracle, wl, wtype, act_f16, m, k, n):
+    """The reference's quantised ops take any m over its permuted super-blocks
+    (src/dsp/ops/mat_mul.c:875-1005, expansion to fp16 at :308-510): many tokens run as ONE tensor-core
+    GEMM launch whose unpack reads the super-blocks as they lie, value * scale rounded to fp16 once as
+    the reference does - full and ragged tiles in M and N, one and many K steps, K a multiple of 128 but
+    not of 256, more tiles than one wave.  Also through op indices 2, 3, 4 with the option set."""
+    fmt = PERM | wtype
+    wq, x = wl.tiled_random_case(70 + m, fmt, act_f16, m, k, n)
+    if not act_f16:
+        x[0] *= 1.0e5  # beyond the fp16 range: absorbed by the per-token scale
+    y = _raw(dev, x, wq, n, fmt)
+    ref = oracle.tiled_mul_mat_f64(x, wq, n, fmt)
+    assert np.isfinite(y).all()
+    for r in range(m):
+        assert np.abs(y[r] - ref[r]).max() <= 1e-3 * np.abs(ref[r]).max(), r
+    if not act_f16 and m <= 200:
+        op = {Q4: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32, Q8: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W8D16A32,
+              IQ4: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL}[wtype]
+        fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
+        old = dev.lib.htp_b200_set_option(b"permuted_weights", 1)
+        try:
+            assert dev.execute(op, (fy, 0), (fx, 0), (fw, 0), m, k, n) == 0
+        finally:
+            dev.lib.htp_b200_set_option(b"permuted_weights", old)
         assert (dev.get(fy, (m, n)) == y).all()
         dev.free(fw, fx, fy)
 
