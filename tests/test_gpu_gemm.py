@@ -152,6 +152,28 @@ def test_gemm_fp32_activations(dev, oracle, wl, wtype, m, k, n):
         assert np.abs(y[r] - ref[r]).max() <= 1e-5 * np.abs(ref[r]).max(), r
 
 
+@pytest.mark.parametrize("wtype,m,k,n", [(2, 1024, 1024, 480), (8, 2500, 512, 256), (20, 4096, 256, 96)])
+def test_gemm_thousands_of_tokens(dev, oracle, wl, wtype, m, k, n):
+    """Token counts at which the reference switches to its pipelined schedule (m >= 1024,
+    src/dsp/ops/mat_mul.c:925, 1006-1139): here the same GEMM launch walks more token tiles - full and
+    ragged - through op indices 2 / 3 / 4 (fp32 activations) and through the fp16-activation entry."""
+    if wtype != 20:  # (IQ4_NL has no fp16-activation op index)
+        assert run(dev, oracle, wl, wtype, m, k, n, seed=5).shape == (m, n)
+    wq, x = wl.random_case(995, wtype, False, m, k, n)
+    fw, fx, fy = dev.put(wq), dev.put(x), dev.buf(m * n * 4)
+    op = {2: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32, 8: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W8D16A32,
+          20: dev.pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32_IQ4_NL}[wtype]
+    before = dev.lib.htp_b200_launch_count()
+    assert dev.execute(op, (fy, 0), (fx, 0), (fw, 0), m, k, n) == 0
+    assert dev.lib.htp_b200_launch_count() == before + 2  # conversion + GEMM
+    y = dev.get(fy, (m, n))
+    dev.free(fw, fx, fy)
+    ref, absdot = oracle.mul_mat_f64(x, wq, n, wtype, want_absdot=True)
+    e = oracle.error_metrics(y, ref, absdot)
+    assert np.isfinite(y).all()
+    assert e["max_rel_to_max"] <= 1e-3 and e["max_cond_rel"] <= 1e-3, e
+
+
 @pytest.mark.parametrize("m", [9, 16, 24, 48, 63])
 def test_gemm_fp16_between_decode_and_full_tiles(dev, oracle, wl, m):
     """9 .. 63 tokens: one GEMM launch on a padded 128-token tile (cheaper than one pass over the
