@@ -947,8 +947,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (p.done_counter) {
       // this CTA's bands are out (both completion warps, each thread's stores fenced at system scope
       // above): count the CTA in; the last CTA of the launch tells every destination that this rank is
-      // done.  The counter's acquire-release and the flags' release stores carry the ordering: no
-      // further fence.
+      // done.  The counter's acquire-release, the warp shuffle and the fence before each flag store
+      // carry the ordering.
       named_bar_sync(2, kReduceThreads);
       if (warp == kReduceWarp0) {
         unsigned last = 0;
@@ -957,13 +957,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.done_counter) : "memory");
           if (old == gridDim.x - 1) {
             *p.done_counter = 0;  // ready for the next launch
-            for (int d = 0; d < p.n_dst; ++d) {
-              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[d]), "r"(p.epoch) : "memory");
-            }
             last = 1;
           }
         }
         last = __shfl_sync(0xffffffffu, last, 0);
+        // Lane d tells destination d: ONE system-scope fence per lane, all lanes at once, then a relaxed
+        // store.  (A release store per destination from one thread is a system-scope fence per
+        // destination, one after the other: about two microseconds each across NVLink.)
+        if (last && lane < p.n_dst) {
+          asm volatile("fence.acq_rel.sys;\n\tst.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.sig_flags[lane]), "r"(p.epoch)
+                       : "memory");
+        }
         // Optionally the launch also WAITS (bounded, about a second) until every rank's flag of this epoch
         // is in this GPU's flag array: the kernel's end is then the end of the step on this GPU - every
         // rank's band has landed here - without a separate wait kernel and its kernel boundary.  The
