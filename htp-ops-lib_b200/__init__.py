@@ -87,6 +87,7 @@ EXPORTS = {
     # include/host/buffers.h
     "htp_buf_alloc": (_i, [_sz]),
     "htp_buf_alloc_host": (_i, [_sz]),
+    "htp_buf_alloc_shared": (_i, [_sz]),
     "htp_buf_wrap": (_i, [_vp, _sz]),
     "htp_buf_free": (_i, [_i]),
     "htp_buf_upload": (_i, [_i, _sz, _vp, _sz]),

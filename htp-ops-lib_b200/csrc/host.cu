@@ -30,7 +30,7 @@
 
 namespace {
 
-enum BufKind { kDeviceBuf = 0, kHostBuf = 1, kWrappedBuf = 2 };
+enum BufKind { kDeviceBuf = 0, kHostBuf = 1, kWrappedBuf = 2, kSharedBuf = 3 };  // shared: pinned host memory the device addresses
 
 struct Buffer {
   uint8_t *ptr  = nullptr;
@@ -464,7 +464,7 @@ void close_dsp_session(void) {
     for (auto &kv : g.bufs) {
       if (kv.second.kind == kDeviceBuf) {
         cudaFree(kv.second.ptr);
-      } else if (kv.second.kind == kHostBuf) {
+      } else if (kv.second.kind == kHostBuf || kv.second.kind == kSharedBuf) {
         cudaFreeHost(kv.second.ptr);
       }
     }
@@ -670,6 +670,28 @@ int htp_buf_alloc_host(size_t size) {
   return register_buffer(b);
 }
 
+int htp_buf_alloc_shared(size_t size) {
+  if (!set_session_device() || size == 0) {
+    return -1;
+  }
+  Buffer b;
+  void  *dp = nullptr;
+  if (cudaHostAlloc(&b.ptr, size, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  // unified addressing: the device reaches the bytes at the host address (anything else is not supported here)
+  if (cudaHostGetDevicePointer(&dp, b.ptr, 0) != cudaSuccess || dp != b.ptr) {
+    cudaGetLastError();
+    cudaFreeHost(b.ptr);
+    return -1;
+  }
+  memset(b.ptr, 0, size);
+  b.size = size;
+  b.kind = kSharedBuf;
+  return register_buffer(b);
+}
+
 int htp_buf_wrap(void *device_ptr, size_t size) {
   if (!g.open || !device_ptr || size == 0) {
     return -1;
@@ -702,6 +724,11 @@ int htp_buf_free(int fd) {
     cudaFree(b.ptr);
   } else if (b.kind == kHostBuf) {
     cudaFreeHost(b.ptr);
+  } else if (b.kind == kSharedBuf) {
+    if (g.stream) {
+      cudaStreamSynchronize(g.stream);  // an operator may still be writing it
+    }
+    cudaFreeHost(b.ptr);
   }
   return 0;
 }
@@ -714,7 +741,10 @@ static int copy_region(int fd, size_t offset, void *host, size_t size, bool uplo
   if (size == 0) {
     return 0;
   }
-  if (b.kind == kHostBuf) {
+  if (b.kind == kHostBuf || b.kind == kSharedBuf) {
+    if (b.kind == kSharedBuf && !upload && wait && set_session_device() && g.stream) {
+      cudaStreamSynchronize(g.stream);  // operators enqueued before may still be writing the bytes
+    }
     if (upload) {
       memcpy(b.ptr + offset, host, size);
     } else {
@@ -760,7 +790,7 @@ void *htp_buf_ptr(int fd) {
 
 int htp_buf_is_host(int fd) {
   Buffer b;
-  return lookup(fd, &b) ? (b.kind == kHostBuf ? 1 : 0) : -1;
+  return lookup(fd, &b) ? (b.kind == kHostBuf ? 1 : (b.kind == kSharedBuf ? 2 : 0)) : -1;
 }
 
 size_t htp_buf_size(int fd) {

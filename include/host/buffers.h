@@ -3,7 +3,8 @@
  * shared memory (rpcmem_alloc, rpcmem_to_fd, fastrpc_mmap: src/host/test.c:30-53), names it by
  * file descriptor in every request, and the DSP side turns fd into pointer through a cache
  * (src/dsp/mmap_mgr.cc:15-37).  Here the "fd" is a small integer handle of a cudaMalloc'd device
- * buffer (or of a pinned host buffer for the message channel); device memory is not host
+ * buffer (or of a pinned host buffer for the message channel, or of a shared buffer - pinned host
+ * memory the device addresses, for results the host reads in place); device memory is not host
  * addressable, so upload/download are explicit.  None of these have a reference counterpart
  * beyond the lines cited.
  *
@@ -22,6 +23,12 @@ extern "C" {
 int htp_buf_alloc(size_t size);
 /* Pinned host buffer (for the message channel; also usable as a staging area).  Handle, or -1. */
 int htp_buf_alloc_host(size_t size);
+/* Pinned host memory that the device addresses directly (mapped; the host pointer is the device
+ * pointer): the closest thing to an rpcmem buffer - operators take it as output, activation or weight,
+ * the host reads results through htp_buf_ptr once the message is done (or after
+ * htp_session_synchronize) without a download.  Every device access crosses PCIe: meant for small
+ * activations and outputs (a token's logits), not for weights.  Handle, or -1. */
+int htp_buf_alloc_shared(size_t size);
 /* Registers caller-owned device memory (for example a tensor of another framework) under a
  * handle; htp_buf_free forgets it without freeing the memory.  Handle, or -1. */
 int htp_buf_wrap(void *device_ptr, size_t size);
@@ -43,7 +50,8 @@ int htp_buf_download_async(int fd, size_t offset, void *dst, size_t size);
 
 /* Base address: device pointer of a device buffer, host pointer of a host buffer; NULL if unknown. */
 void *htp_buf_ptr(int fd);
-/* 1 for a host buffer, 0 for a device buffer, -1 if unknown. */
+/* 1 for a host buffer, 2 for a shared (host memory, device-addressable) buffer, 0 for a device buffer,
+ * -1 if unknown. */
 int htp_buf_is_host(int fd);
 size_t htp_buf_size(int fd);
 

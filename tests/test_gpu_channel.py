@@ -185,3 +185,36 @@ def test_direct_calls_while_messages_are_in_flight(dev, oracle, wl):
     ref = src / np.sqrt((src.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-5)
     assert np.abs(got - ref).max() <= 1e-5
     dev.free(*fw, *fx, *fy, fsrc, fdst, fwd, fxd, fyd)
+
+
+def test_shared_output_buffer_is_read_in_place(dev, oracle, wl):
+    """A shared buffer - pinned host memory the device addresses, the counterpart of the reference's
+    rpcmem buffers (src/host/test.c:30-53) - as the operator's OUTPUT: when the message is done the host
+    reads the results through the buffer's own address, no download.  Decode and GEMM paths, and the
+    buffer as an activation source as well."""
+    import ctypes
+    lib, pkg = dev.lib, dev.pkg
+    for m, k, n, act_f16 in ((1, 1024, 2048, False), (8, 2048, 512, False), (64, 512, 256, True)):
+        wq, x = wl.random_case(3100 + m, 2, act_f16, m, k, n)
+        fw, fx = dev.put(wq), lib.htp_buf_alloc_shared(x.nbytes)
+        fy = lib.htp_buf_alloc_shared(m * n * 4)
+        assert fx > 0 and fy > 0 and lib.htp_buf_is_host(fy) == 2
+        ctypes.memmove(lib.htp_buf_ptr(fx), x.ctypes.data, x.nbytes)  # the host writes the activations in place
+        host_y = np.ctypeslib.as_array(ctypes.cast(lib.htp_buf_ptr(fy), ctypes.POINTER(ctypes.c_float)), shape=(m, n))
+        host_y[:] = np.nan
+        op = pkg.HTP_OPS_MAT_MUL_W4D16A16 if act_f16 else pkg.HTP_OPS_MAT_MUL_PERMUTED_W4D16A32
+        chan = pkg.MessageChannel(4096)
+        try:
+            assert chan.submit([pkg.pack_matmul_request(op, (fy, 0), (fx, 0), (fw, 0), m, k, n)]) == [0]
+        finally:
+            chan.close()
+        ref, absdot = oracle.mul_mat_f64(x, wq, n, 2, want_absdot=True)
+        e = oracle.error_metrics(np.array(host_y), ref, absdot)
+        tol = 1e-3 if act_f16 else 1e-5
+        assert np.isfinite(host_y).all() and e["max_rel_to_max"] <= tol and e["max_cond_rel"] <= tol, e
+        # the synchronous download of a shared buffer is a plain copy of the same bytes
+        back = np.empty((m, n), dtype=np.float32)
+        assert lib.htp_buf_download(fy, 0, back.ctypes.data, back.nbytes) == 0
+        assert (back == host_y).all()
+        dev.free(fw)
+        assert lib.htp_buf_free(fx) == 0 and lib.htp_buf_free(fy) == 0
