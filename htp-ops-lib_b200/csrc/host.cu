@@ -742,8 +742,11 @@ static int copy_region(int fd, size_t offset, void *host, size_t size, bool uplo
     return 0;
   }
   if (b.kind == kHostBuf || b.kind == kSharedBuf) {
-    if (b.kind == kSharedBuf && !upload && wait && set_session_device() && g.stream) {
-      cudaStreamSynchronize(g.stream);  // operators enqueued before may still be writing the bytes
+    if (b.kind == kSharedBuf && set_session_device() && g.stream) {
+      // the copy below is the host's own: operators enqueued before may still be reading or writing the
+      // bytes, so the stream order a device buffer's copy would have is kept by waiting (also in the
+      // "async" forms - a host that wants no wait writes and reads the shared bytes itself)
+      cudaStreamSynchronize(g.stream);
     }
     if (upload) {
       memcpy(b.ptr + offset, host, size);

@@ -27,7 +27,8 @@ int htp_buf_alloc_host(size_t size);
  * pointer): the closest thing to an rpcmem buffer - operators take it as output, activation or weight,
  * the host reads results through htp_buf_ptr once the message is done (or after
  * htp_session_synchronize) without a download.  Every device access crosses PCIe: meant for small
- * activations and outputs (a token's logits), not for weights.  Handle, or -1. */
+ * activations and outputs (a token's logits), not for weights.  htp_buf_upload / htp_buf_download on it
+ * wait for the session stream first and then copy on the host.  Handle, or -1. */
 int htp_buf_alloc_shared(size_t size);
 /* Registers caller-owned device memory (for example a tensor of another framework) under a
  * handle; htp_buf_free forgets it without freeing the memory.  Handle, or -1. */
