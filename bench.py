@@ -575,6 +575,7 @@ def run_ours(args):
     # reproduces the gathered result bit for bit on every rank; otherwise the NCCL all-gather is.
     step, exchange = step_gather, ("none" if world == 1 else "NCCL all-gather of fp32 logits")
     fused_logits = None  # this rank's copy of the logits the fused exchange assembles
+    fused_e2e = None     # two sets of symmetric logits for the end-to-end loop
     if world > 1 and not args.no_fused:
         try:
 
@@ -587,6 +588,12 @@ def run_ours(args):
                 hdlf = symm.rendezvous(symf, dist.group.WORLD)
                 order = [rank] + [r for r in range(world) if r != rank]  # own copy first
                 arr = (ctypes.c_void_p * world)(*[int(hdl.buffer_ptrs[r]) for r in order])
+                # a second set of logits for the end-to-end loop: a rank downloads step e from one set while
+                # its peers' step e + 1 already stores into the other
+                sym_b = symm.empty((m, op.n), dtype=torch.float32, device=dev)
+                hdl_b = symm.rendezvous(sym_b, dist.group.WORLD)
+                arr_b = (ctypes.c_void_p * world)(*[int(hdl_b.buffer_ptrs[r]) for r in order])
+                fused_e2e = {"syms": (sym, sym_b), "arrs": (arr, arr_b)}
                 # this rank's flag word in every destination GPU's flag array
                 farr = (ctypes.c_void_p * world)(*[int(hdlf.buffer_ptrs[r]) + 4 * rank for r in order])
                 epoch = [0]
@@ -722,9 +729,25 @@ def run_ours(args):
             reqs = [[pkg.pack_matmul_request(pkg.HTP_OPS_MAT_MUL_W8D16A16, (fy, 0), (fx, 0), (f, 0), m, op.k, n_loc)]
                     for f in fw]
 
+            use_fused = world > 1 and step is not step_gather and fused_e2e is not None
+            if use_fused:
+                fl = [lib.htp_buf_wrap(t_.data_ptr(), m * op.n * 4) for t_ in fused_e2e["syms"]]
+                ss = lib.htp_session_stream()
+                xs = lib.htp_buf_ptr(fx)
+
             def e2e_step(i):
-                # upload is only enqueued (pinned source): the message that follows is ordered behind it
+                # upload is only enqueued (pinned source): what follows is ordered behind it on the session stream
                 assert lib.htp_buf_upload_async(fx, 0, x_host.data_ptr(), x_host.numel() * 2) == 0
+                if use_fused:
+                    # sharded, fused exchange: ONE library call whose kernel stores this rank's band into every
+                    # rank's logits and ends when all bands are here; then the download of the full logits
+                    epoch[0] += 1
+                    assert lib.htp_b200_mul_mat_gather_step(fused_e2e["arrs"][i & 1], world, op.n, r0, xs,
+                                                            ws[i % copies].data_ptr(), m, op.k, n_loc, op.wtype,
+                                                            pkg.ACT_F16, farr, symf.data_ptr(), epoch[0], ss) == 0
+                    assert lib.htp_buf_download_async(fl[i & 1], 0, out_host.data_ptr(), m * op.n * 4) == 0
+                    assert lib.htp_session_synchronize() == 0
+                    return
                 st = chan.submit(reqs[i % copies])
                 assert st == [0], st
                 if not shared_out:
@@ -755,11 +778,15 @@ def run_ours(args):
                    "ms_per_step_median": round(med * 1e3, 4), "steps": e2e_steps,
                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": m * op.n * 4,
                    "downloaded_logits_match_fixture": bool(e2e_ok),
-                   "path": "htp_buf_upload_async (pinned host memory) -> message channel (1 request) -> "
-                           + ("NCCL all-gather -> download of the fp32 logits; " if world > 1 else
-                              "the kernel stores the fp32 logits into a shared (pinned, device-addressable) output "
-                              "buffer, read in place when the message is done; ")
-                           + "weights stay resident, as the reference's mapped weight buffers do"}
+                   "path": "htp_buf_upload_async (pinned host memory) -> " + (
+                       "htp_b200_mul_mat_gather_step on the session stream (the kernel stores this rank's band into "
+                       "every rank's logits, raises its flags and ends when all bands are here; two sets of logits "
+                       "used in turn) -> htp_buf_download_async of the full fp32 logits -> htp_session_synchronize; "
+                       if use_fused else
+                       "message channel (1 request) -> NCCL all-gather -> download of the fp32 logits; " if world > 1 else
+                       "message channel (1 request) -> the kernel stores the fp32 logits into a shared (pinned, "
+                       "device-addressable) output buffer, read in place when the message is done; ")
+                   + "weights stay resident, as the reference's mapped weight buffers do"}
         finally:
             chan.close()
             lib.close_dsp_session()
