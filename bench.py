@@ -774,10 +774,30 @@ def run_ours(args):
             out_host.zero_()
             e2e_step(e2e_steps)
             e2e_ok = g1 is None or matches_fixture(out_host.numpy(), g1, 1e-3)
+            direct_ms = None
+            if shared_out:
+                # beside it (one GPU): the same step without the message channel - upload, ONE direct library
+                # call on the session stream into the shared output buffer, stream synchronise
+                ss, xs, yo = lib.htp_session_stream(), lib.htp_buf_ptr(fx), lib.htp_buf_ptr(fy)
+
+                def direct_step(i):
+                    assert lib.htp_buf_upload_async(fx, 0, x_host.data_ptr(), x_host.numel() * 2) == 0
+                    assert lib.htp_b200_mul_mat(yo, xs, ws[i % copies].data_ptr(), m, op.k, op.n, op.wtype, pkg.ACT_F16, ss) == 0
+                    assert lib.htp_session_synchronize() == 0
+                for i in range(warm):
+                    direct_step(i)
+                t0 = time.perf_counter()
+                for i in range(e2e_steps):
+                    direct_step(i)
+                direct_ms = (time.perf_counter() - t0) / e2e_steps * 1e3
+                out_host.zero_()
+                direct_step(0)
+                e2e_ok = e2e_ok and (g1 is None or matches_fixture(out_host.numpy(), g1, 1e-3))
             e2e = {"value": round(total_bytes / dt / 1e9, 2), "unit": "GB/s", "ms_per_step": round(dt * 1e3, 4),
                    "ms_per_step_median": round(med * 1e3, 4), "steps": e2e_steps,
                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": m * op.n * 4,
                    "downloaded_logits_match_fixture": bool(e2e_ok),
+                   "ms_per_step_direct_call": None if direct_ms is None else round(direct_ms, 4),
                    "path": "htp_buf_upload_async (pinned host memory) -> " + (
                        "htp_b200_mul_mat_gather_step on the session stream (the kernel stores this rank's band into "
                        "every rank's logits, raises its flags and ends when all bands are here; two sets of logits "
