@@ -22,13 +22,14 @@
 // leader's barriers directly, and tcgen05.commit multicasts its arrival to the pair.
 //
 // K advances in steps of 64 through ONE ring of 8 slots; slot i holds the activation tile
-// (shared memory) and the dequantised weight tile (32 TMEM columns) of one K step, filled behind
-// one `full` barrier and released by one tcgen05.commit on one `empty` barrier.
+// (shared memory) and the dequantised weight tile (32 TMEM columns) of one K step.  Two consecutive
+// slots are filled behind one `full` barrier and released by one tcgen05.commit on one `empty`
+// barrier: the issuing thread's waits and commits cost it hundreds of clocks each.
 //
 // Roles per CTA:
 //   warp 0      TMA producer of the activation tile (128 tokens x 64 fp16, 128-byte swizzle)
 //   warp 1      MMA issuer (leader CTA of a pair only): the whole warp runs the loop, one elected
-//               lane issues; one wait, four MMAs and one commit per K step
+//               lane issues; one wait, eight MMAs and one commit per two K steps
 //   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 the ring of A tiles
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator 16 tokens at a time -> shared-memory
 //               staging -> TMA store to y[token][weight row]; the accumulator is released after
@@ -458,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int  *abort_flag = &bar->abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNAT; ++i) {
+    for (int i = 0; i < kNAT / 2; ++i) {  // one barrier pair per two K steps
       // the TMA producer's expect_tx arrival and the four warps of the writing group, of both CTAs
       // for a pair
       mbar_init(&bar->full[i], TWO ? 1 + 4 + 4 : 1 + 4);
@@ -541,19 +542,27 @@ __global__ void __launch_bounds__(kThreads, 1)
         li += rs1 - rs0;
         const int m0 = (t % t_tiles) * BT + tok_off;
         for (int kb = rs0 * C::Q; kb < rs1 * C::Q; ++kb) {
-          ok = wait_or_abort(&bar->empty[rx.slot], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
-          if (!ok) {
-            break;
+          // TWO K steps share one full / empty barrier pair (a segment holds an even number of steps): the
+          // MMA issuer's waits and commits, which cost it hundreds of clocks each, come once per 128 of K
+          const int hb = rx.slot >> 1;
+          if ((rx.slot & 1) == 0) {
+            ok = wait_or_abort(&bar->empty[hb], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
+            if (!ok) {
+              break;
+            }
+            if constexpr (TWO) {
+              // both halves of both activation tiles complete on the leader's barrier
+              if (rank == 0) {
+                mbar_arrive_expect_tx(&bar->full[hb], 4 * X_BYTES);
+              }
+            } else {
+              mbar_arrive_expect_tx(&bar->full[hb], 2 * X_BYTES);
+            }
           }
           if constexpr (TWO) {
-            // both halves of the activation tile complete on the leader's barrier
-            if (rank == 0) {
-              mbar_arrive_expect_tx(&bar->full[rx.slot], 2 * X_BYTES);
-            }
-            tma_load_2d_pair(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[rx.slot], pol);
+            tma_load_2d_pair(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[hb], pol);
           } else {
-            mbar_arrive_expect_tx(&bar->full[rx.slot], X_BYTES);
-            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[rx.slot], pol);
+            tma_load_2d(sX + rx.slot * X_BYTES, &xmap, kb * kBK, m0, &bar->full[hb], pol);
           }
           rx.next();
         }
@@ -581,13 +590,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int sg = (int) (gs % C::NG), gph = (int) (gs / C::NG) & 1;  // ring position of the raw stage
 #pragma unroll
           for (int q = 0; q < C::Q; ++q) {
-            const int slot = sg * C::Q + q;
-            ok = wait_or_abort(&bar->full[slot], gph, abort_flag, p.err, kGemmErrMma);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-              break;
+            const int slot = sg * C::Q + q;  // (even exactly when q is)
+            if ((q & 1) == 0) {
+              ok = wait_or_abort(&bar->full[slot >> 1], gph, abort_flag, p.err, kGemmErrMma);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) {
+                break;
+              }
+              tc_fence_after();
             }
-            tc_fence_after();
             if (elect_one()) {
               const uint64_t bdesc  = smem_desc_sw128(sX + slot * X_BYTES);
               const uint32_t a_tmem = tmem_base + kTmemA + slot * 32;
@@ -596,7 +607,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
                 umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, ((rs - rs0) | q | s) ? 1u : 0u);
               }
-              umma_commit<TWO>(&bar->empty[slot]);
+              if (q & 1) {
+                umma_commit<TWO>(&bar->empty[slot >> 1]);
+              }
             }
             __syncwarp();
           }
@@ -975,7 +988,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int q = 0; q < C::Q; ++q) {
         const int slot = sg * C::Q + q;
-        ok = ok && wait_or_abort(&bar->empty[slot], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
+        if ((q & 1) == 0) {
+          ok = ok && wait_or_abort(&bar->empty[slot >> 1], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
+        }
         ok = __all_sync(0xffffffffu, ok);  // a warp stores to tensor memory as a whole or not at all
         if (ok) {
           tc_fence_after();
@@ -983,11 +998,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();  // every lane's store has completed (wait::st above)
-          if (lane == 0) {
+          if (lane == 0 && (q & 1)) {  // both K steps of the barrier pair are in tensor memory
             if (TWO && rank != 0) {
-              mbar_arrive_remote(&bar->full[slot], 0);  // the MMA is issued by the leader CTA
+              mbar_arrive_remote(&bar->full[slot >> 1], 0);  // the MMA is issued by the leader CTA
             } else {
-              mbar_arrive(&bar->full[slot]);
+              mbar_arrive(&bar->full[slot >> 1]);
             }
           }
         }
