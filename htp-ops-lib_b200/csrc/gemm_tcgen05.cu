@@ -22,14 +22,15 @@
 // leader's barriers directly, and tcgen05.commit multicasts its arrival to the pair.
 //
 // K advances in steps of 64 through ONE ring of 8 slots; slot i holds the activation tile
-// (shared memory) and the dequantised weight tile (32 TMEM columns) of one K step.  Two consecutive
-// slots are filled behind one `full` barrier and released by one tcgen05.commit on one `empty`
-// barrier: the issuing thread's waits and commits cost it hundreds of clocks each.
+// (shared memory) and the dequantised weight tile (32 TMEM columns) of one K step.  A group of
+// consecutive slots (two for CTA pairs, a raw stage for single-CTA tiles) is filled behind one `full`
+// barrier and released by one tcgen05.commit on one `empty` barrier: the issuing thread's waits and
+// commits cost it hundreds of clocks each.
 //
 // Roles per CTA:
 //   warp 0      TMA producer of the activation tile (128 tokens x 64 fp16, 128-byte swizzle)
 //   warp 1      MMA issuer (leader CTA of a pair only): the whole warp runs the loop, one elected
-//               lane issues; one wait, eight MMAs and one commit per two K steps
+//               lane issues; one wait and one commit per group of K steps, four MMAs per step
 //   warp 2      TMEM allocation: columns 0..255 accumulator, 256..511 the ring of A tiles
 //   warps 4-7   epilogue: tcgen05.ld of the accumulator 16 tokens at a time -> shared-memory
 //               staging -> TMA store to y[token][weight row]; the accumulator is released after
@@ -121,6 +122,11 @@ struct GCfg {
   static constexpr int STAGE_OUT = 4 * 2 * kOutTok * 32 * 4;  // 4 epilogue warps x 2 buffers x 16 tokens x 32 rows
   static constexpr int FIXED     = 2 * ((RAW_BYTES + 127) & ~127) + 1024 + 512 + STAGE_OUT;  // raw ring, slack, barriers, output staging
   static constexpr int NX        = kNAT;  // activation stages: the same ring as the A tiles
+  // K steps that share one full / empty barrier pair: two for CTA pairs (their MMAs take longer than the
+  // issuing thread's wait and commit), a whole raw stage for single-CTA tiles, whose small MMAs leave the
+  // issuing thread as the limit
+  static constexpr int BSTEPS    = TWO ? 2 : Q;
+  static_assert(Q % BSTEPS == 0 && kNAT % BSTEPS == 0, "barrier groups do not straddle raw stages");
   static_assert(NX * X_BYTES + FIXED <= kSmemLimit, "shared memory");
 };
 
@@ -459,7 +465,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int  *abort_flag = &bar->abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNAT / 2; ++i) {  // one barrier pair per two K steps
+    for (int i = 0; i < kNAT / C::BSTEPS; ++i) {  // one barrier pair per group of K steps
       // the TMA producer's expect_tx arrival and the four warps of the writing group, of both CTAs
       // for a pair
       mbar_init(&bar->full[i], TWO ? 1 + 4 + 4 : 1 + 4);
@@ -542,10 +548,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         li += rs1 - rs0;
         const int m0 = (t % t_tiles) * BT + tok_off;
         for (int kb = rs0 * C::Q; kb < rs1 * C::Q; ++kb) {
-          // TWO K steps share one full / empty barrier pair (a segment holds an even number of steps): the
-          // MMA issuer's waits and commits, which cost it hundreds of clocks each, come once per 128 of K
-          const int hb = rx.slot >> 1;
-          if ((rx.slot & 1) == 0) {
+          // BSTEPS K steps share one full / empty barrier pair (a segment holds whole raw stages): the MMA
+          // issuer's waits and commits, which cost it hundreds of clocks each, come once per group
+          const int hb = rx.slot / C::BSTEPS;
+          if (rx.slot % C::BSTEPS == 0) {
             ok = wait_or_abort(&bar->empty[hb], rx.phase ^ 1, abort_flag, p.err, kGemmErrProducer);
             if (!ok) {
               break;
@@ -553,10 +559,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             if constexpr (TWO) {
               // both halves of both activation tiles complete on the leader's barrier
               if (rank == 0) {
-                mbar_arrive_expect_tx(&bar->full[hb], 4 * X_BYTES);
+                mbar_arrive_expect_tx(&bar->full[hb], 2 * C::BSTEPS * X_BYTES);
               }
             } else {
-              mbar_arrive_expect_tx(&bar->full[hb], 2 * X_BYTES);
+              mbar_arrive_expect_tx(&bar->full[hb], C::BSTEPS * X_BYTES);
             }
           }
           if constexpr (TWO) {
@@ -590,9 +596,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int sg = (int) (gs % C::NG), gph = (int) (gs / C::NG) & 1;  // ring position of the raw stage
 #pragma unroll
           for (int q = 0; q < C::Q; ++q) {
-            const int slot = sg * C::Q + q;  // (even exactly when q is)
-            if ((q & 1) == 0) {
-              ok = wait_or_abort(&bar->full[slot >> 1], gph, abort_flag, p.err, kGemmErrMma);
+            const int slot = sg * C::Q + q;  // (slot % BSTEPS == q % BSTEPS)
+            if (q % C::BSTEPS == 0) {
+              ok = wait_or_abort(&bar->full[slot / C::BSTEPS], gph, abort_flag, p.err, kGemmErrMma);
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) {
                 break;
@@ -607,8 +613,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 // A: 16 fp16 per lane = 8 TMEM columns per step; B: +32 bytes inside the swizzled row
                 umma_f16_ts<TWO>(tmem_base, a_tmem + 8 * s, bdesc + 2 * s, IDESC, ((rs - rs0) | q | s) ? 1u : 0u);
               }
-              if (q & 1) {
-                umma_commit<TWO>(&bar->empty[slot >> 1]);
+              if (q % C::BSTEPS == C::BSTEPS - 1) {
+                umma_commit<TWO>(&bar->empty[slot / C::BSTEPS]);
               }
             }
             __syncwarp();
@@ -988,8 +994,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
       for (int q = 0; q < C::Q; ++q) {
         const int slot = sg * C::Q + q;
-        if ((q & 1) == 0) {
-          ok = ok && wait_or_abort(&bar->empty[slot >> 1], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
+        if (q % C::BSTEPS == 0) {
+          ok = ok && wait_or_abort(&bar->empty[slot / C::BSTEPS], gph ^ 1, abort_flag, p.err, kGemmErrDequant);
         }
         ok = __all_sync(0xffffffffu, ok);  // a warp stores to tensor memory as a whole or not at all
         if (ok) {
@@ -998,11 +1004,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();  // every lane's store has completed (wait::st above)
-          if (lane == 0 && (q & 1)) {  // both K steps of the barrier pair are in tensor memory
+          if (lane == 0 && q % C::BSTEPS == C::BSTEPS - 1) {  // the group's K steps are all in tensor memory
             if (TWO && rank != 0) {
-              mbar_arrive_remote(&bar->full[slot >> 1], 0);  // the MMA is issued by the leader CTA
+              mbar_arrive_remote(&bar->full[slot / C::BSTEPS], 0);  // the MMA is issued by the leader CTA
             } else {
-              mbar_arrive(&bar->full[slot >> 1]);
+              mbar_arrive(&bar->full[slot / C::BSTEPS]);
             }
           }
         }
